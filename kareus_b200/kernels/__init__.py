@@ -1,0 +1,173 @@
+"""Kernel entry points used by the operators.
+
+Every function takes torch tensors.  CUDA tensors go to the hand-written sm_100a kernels in
+``libkareus_b200.so`` (built from ``kernels/csrc`` and loaded through :mod:`.cuda`); CPU tensors
+go to the PyTorch statements in :mod:`.ref`.  There is no silent fallback on a GPU: if the
+library is missing the call raises.  ``KAREUS_B200_LIBRARY_BASELINE=1`` switches GEMM and attention
+to the vendor libraries (cuBLAS through ``torch.matmul``, the flash-attention wheel or SDPA); that
+is the A/B baseline configured like the reference, never the default.
+"""
+from __future__ import annotations
+
+import os
+from typing import Optional
+
+import torch
+
+from . import ref
+
+_LAUNCHES = [0]
+
+
+def launch_count() -> int:
+    """Number of kernels of this package launched so far in this process."""
+    return _LAUNCHES[0]
+
+
+def _count(n: int = 1) -> None:
+    _LAUNCHES[0] += n
+
+
+def library_baseline() -> bool:
+    return os.environ.get("KAREUS_B200_LIBRARY_BASELINE", "0") == "1"
+
+
+def _cuda():
+    from . import cuda
+    return cuda
+
+
+def is_cuda(t) -> bool:
+    return isinstance(t, torch.Tensor) and t.is_cuda
+
+
+# ----------------------------------------------------------------------------- norm
+def rmsnorm_fwd(x, w, eps):
+    if is_cuda(x):
+        return _cuda().rmsnorm_fwd(x, w, eps)
+    return ref.rmsnorm_fwd(x, w, eps)
+
+
+def rmsnorm_bwd(dy, x, rstd, w):
+    if is_cuda(x):
+        return _cuda().rmsnorm_bwd(dy, x, rstd, w)
+    return ref.rmsnorm_bwd(dy, x, rstd, w)
+
+
+# ----------------------------------------------------------------------------- rope
+def rope_inplace(q, k, freqs, inverse=False):
+    """Rotate ``q`` and ``k`` (views are fine) in place."""
+    if is_cuda(q):
+        return _cuda().rope_inplace(q, k, freqs, inverse)
+    q.copy_(ref.rope_apply(q, freqs, inverse))
+    if k is not None:
+        k.copy_(ref.rope_apply(k, freqs, inverse))
+
+
+# ----------------------------------------------------------------------------- swiglu
+def swiglu_fwd(x):
+    if is_cuda(x):
+        return _cuda().swiglu_fwd(x)
+    return ref.swiglu_fwd(x)
+
+
+def swiglu_bwd(dy, x):
+    if is_cuda(x):
+        return _cuda().swiglu_bwd(dy, x)
+    return ref.swiglu_bwd(dy, x)
+
+
+# ----------------------------------------------------------------------------- dropout-add
+def dropout_add_fwd(x, residual, p, seed):
+    if is_cuda(x):
+        return _cuda().dropout_add_fwd(x, residual, p, seed)
+    return ref.dropout_add_fwd(x, residual, p, seed)
+
+
+def dropout_add_bwd(dy, p, seed):
+    if is_cuda(dy):
+        return _cuda().dropout_add_bwd(dy, p, seed)
+    return ref.dropout_add_bwd(dy, p, seed)
+
+
+def add(a, b):
+    if is_cuda(a):
+        return _cuda().add(a, b)
+    return a + b
+
+
+# ----------------------------------------------------------------------------- GEMM
+def gemm(a, b, trans_a=False, trans_b=True, out_dtype=None, accumulate=None, out=None):
+    """``op(a) @ op(b)``.  ``accumulate`` is an fp32 tensor that receives ``+=``."""
+    if is_cuda(a):
+        if library_baseline():
+            return _cuda().gemm_library(a, b, trans_a, trans_b, out_dtype, accumulate, out)
+        return _cuda().gemm(a, b, trans_a, trans_b, out_dtype, accumulate, out)
+    r = ref.gemm(a, b, trans_a, trans_b, out_dtype, accumulate)
+    if out is not None:
+        out.copy_(r)
+        return out
+    return r
+
+
+# ----------------------------------------------------------------------------- attention
+def attention_fwd(q, k, v, scale, causal=True, q_offset=0, kv_len=None):
+    if is_cuda(q):
+        if library_baseline():
+            return _cuda().attention_fwd_library(q, k, v, scale, causal, q_offset, kv_len)
+        return _cuda().attention_fwd(q, k, v, scale, causal, q_offset, kv_len)
+    return ref.attention_fwd(q, k, v, scale, causal, q_offset, kv_len)
+
+
+def attention_bwd(do, q, k, v, o, lse, scale, causal=True, q_offset=0, kv_len=None, out=None):
+    """Returns ``(dq, dk, dv)``; ``out`` may provide preallocated (strided) destinations."""
+    if is_cuda(q):
+        if library_baseline():
+            return _cuda().attention_bwd_library(do, q, k, v, o, lse, scale, causal, q_offset, kv_len, out)
+        return _cuda().attention_bwd(do, q, k, v, o, lse, scale, causal, q_offset, kv_len, out)
+    dq, dk, dv = ref.attention_bwd(do, q, k, v, o, lse, scale, causal, q_offset, kv_len)
+    if out is not None:
+        out[0].copy_(dq.reshape(out[0].shape))
+        out[1].copy_(dk)
+        out[2].copy_(dv)
+        return out
+    return dq, dk, dv
+
+
+# ----------------------------------------------------------------------------- cross entropy
+def cross_entropy_local_stats(logits, targets, vocab_start):
+    if is_cuda(logits):
+        return _cuda().cross_entropy_local_stats(logits, targets, vocab_start)
+    return ref.cross_entropy_local_stats(logits, targets, vocab_start)
+
+
+def cross_entropy_finish(logits, targets, vocab_start, gmax, gsum, grad_scale):
+    if is_cuda(logits):
+        return _cuda().cross_entropy_finish(logits, targets, vocab_start, gmax, gsum, grad_scale)
+    return ref.cross_entropy_finish(logits, targets, vocab_start, gmax, gsum, grad_scale)
+
+
+# ----------------------------------------------------------------------------- embedding
+def embedding_fwd(tokens, weight, vocab_start):
+    if is_cuda(weight):
+        return _cuda().embedding_fwd(tokens, weight, vocab_start)
+    return ref.embedding_fwd(tokens, weight, vocab_start)
+
+
+def embedding_bwd(dout, tokens, grad_weight, vocab_start):
+    if is_cuda(dout):
+        return _cuda().embedding_bwd(dout, tokens, grad_weight, vocab_start)
+    return ref.embedding_bwd(dout, tokens, grad_weight, vocab_start)
+
+
+# ----------------------------------------------------------------------------- optimizer
+def adamw_step(p, g, m, v, master, lr, beta1, beta2, eps, wd, step, grad_scale=1.0):
+    if is_cuda(master):
+        return _cuda().adamw_step(p, g, m, v, master, lr, beta1, beta2, eps, wd, step, grad_scale)
+    return ref.adamw_step(p, g, m, v, master, lr, beta1, beta2, eps, wd, step, grad_scale)
+
+
+def sumsq(t):
+    if is_cuda(t):
+        return _cuda().sumsq(t)
+    return ref.sumsq(t)

@@ -62,6 +62,8 @@ def resolve_slot(slots: Dict[str, int], name) -> int:
         return name
     if name == "none":
         return -1
+    if name == "first":
+        return 0
     if name not in slots:
         raise KeyError(f"unknown overlap slot {name!r}; this step offers {sorted(slots)}")
     return slots[name]

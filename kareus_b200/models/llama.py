@@ -169,6 +169,9 @@ class _HeadLossFn(torch.autograd.Function):
     def forward(ctx, x, module, labels, loss_weight, want_grad):
         # x: [s, b, h] (full sequence); labels, loss_weight: [s, b]
         w = module.weight
+        in_shape = x.shape
+        if module.fwd_gather is not None:                                 # sequence shard → full sequence
+            (x,) = module.fwd_gather.run((x.contiguous(),))
         s, b, h = x.shape
         x2 = x.reshape(-1, h)
         logits = K.gemm(x2, w, trans_b=True)                            # [T, V_local]
@@ -176,8 +179,9 @@ class _HeadLossFn(torch.autograd.Function):
         m, se, tl = K.cross_entropy_local_stats(logits, tgt, module.vocab_start)
         if module.tp > 1:
             stats = torch.stack([m, se, tl], dim=0)                        # [3, T]
-            gathered = torch.empty((module.tp,) + tuple(stats.shape), dtype=stats.dtype, device=stats.device)
-            dist.all_gather_into_tensor(gathered, stats.contiguous(), group=module.group)
+            flat = torch.empty((module.tp * 3, stats.shape[1]), dtype=stats.dtype, device=stats.device)
+            dist.all_gather_into_tensor(flat, stats.contiguous(), group=module.group)
+            gathered = flat.view(module.tp, 3, -1)
             gm = gathered[:, 0].max(dim=0).values
             gs = (gathered[:, 1] * torch.exp(gathered[:, 0] - gm)).sum(0)
             gt = gathered[:, 2].sum(0)
@@ -192,6 +196,7 @@ class _HeadLossFn(torch.autograd.Function):
             K.gemm(logits, x2, trans_a=True, trans_b=False, accumulate=ensure_main_grad(w))
             ctx.save_for_backward(dx)
             ctx.shape = x.shape
+            ctx.in_shape = in_shape
             ctx.module = module
         return loss
 
@@ -229,21 +234,7 @@ class OutputHead(nn.Module):
         self.bwd_scatter = comm.make(ReduceScatter, "tp", "head.bwd_rs") if self.tp > 1 and self.sp else None
 
     def forward(self, x, labels, loss_weight):
-        if self.fwd_gather is not None:
-            x = _GatherFn.apply(x, self.fwd_gather)
-            # gradient returns through _HeadLossFn's own reduce-scatter, so the gather is identity in bwd
         return _HeadLossFn.apply(x, self, labels, loss_weight, torch.is_grad_enabled())
-
-
-class _GatherFn(torch.autograd.Function):
-    @staticmethod
-    def forward(ctx, x, op):
-        (y,) = op.run((x.contiguous(),))
-        return y
-
-    @staticmethod
-    def backward(ctx, g):
-        return g, None
 
 
 class _NormFn(torch.autograd.Function):

@@ -109,7 +109,9 @@ class ScheduleItem:
             return TRAIL_CONFIG
         parent = _INHERIT.get(key)
         if parent is not None and d.get(parent) is not None:
-            return d[parent]
+            # the parent's slot names belong to another segment: keep its launch shape and start
+            # the collective with the first operator of this one
+            return CommConfig(("first", "none"), d[parent].resource_shape)
         return default
 
     def __getattr__(self, name: str):

@@ -1,0 +1,229 @@
+"""Headline benchmark: Llama-3.2-3B training throughput (tokens/s) and energy (J/iteration).
+
+    python bench.py --gpus 1 --steps 3 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29500 bench.py --gpus 8 --steps 3 --warmup 3
+
+Config (the reference's headline run, ``tests/artifact/conf/megatron_llama3.2_3b_config.yaml``):
+Llama-3.2-3B, bf16, micro batch 8, sequence 4096, global batch 64 (8 microbatches per step),
+activation recompute, AdamW with fp32 master weights, TP = number of GPUs, synthetic uniform-random
+tokens and random-init weights.  The global batch is fixed, so scaling over GPUs is strong scaling.
+
+Two measurements are reported: ``value`` times K steps on the device (CUDA events, inputs staged
+on the device beforehand, max over ranks); ``e2e`` times K calls of ``Trainer.train_step`` with
+pinned host inputs copied every step and the loss read back every step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+BASELINE_TOKENS_PER_S = 60200.0   # planner-predicted max-throughput plan of the reference, 16 x A100
+
+
+def _reference_arm(args) -> int:
+    print(json.dumps({
+        "impl": "reference",
+        "unavailable": "kareus installs from /root/reference only with --no-deps (pure Python); its training "
+                       "path imports megatron.core, transformer_engine, nemo, apex, mscclpp, cupy and zeus, none "
+                       "of which is in the image or the offline wheelhouse",
+    }))
+    return 0
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock, power and throttle reasons of one GPU through NVML while a region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.2):
+        super().__init__(daemon=True)
+        self.index, self.period = index, period_s
+        self.samples, self.reasons, self.power = [], set(), []
+        self.max_mhz = None
+        self._stop_evt = threading.Event()
+        self.ok = False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            self.nv = None
+
+    _NAMES = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap",
+              0x80: "hw_power_brake_slowdown", 0x2: "applications_clocks_setting", 0x10: "sync_boost"}
+
+    def run(self):
+        if not self.ok:
+            return
+        nv = self.nv
+        while not self._stop_evt.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                self.power.append(nv.nvmlDeviceGetPowerUsage(self.h) / 1000.0)
+                r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h) if hasattr(nv, "nvmlDeviceGetCurrentClocksEventReasons") \
+                    else nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in self._NAMES.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop_evt.wait(self.period)
+
+    def energy_mj(self):
+        try:
+            return self.nv.nvmlDeviceGetTotalEnergyConsumption(self.h)
+        except Exception:
+            return None
+
+    def stop(self):
+        self._stop_evt.set()
+
+    def summary(self):
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz,
+                "power_w_max": max(self.power) if self.power else None, "reasons": sorted(self.reasons)}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="llama3.2_3b")
+    ap.add_argument("--mbs", type=int, default=8)
+    ap.add_argument("--gbs", type=int, default=64)
+    ap.add_argument("--seq", type=int, default=4096)
+    ap.add_argument("--nano", type=int, default=int(os.environ.get("KAREUS_NANOBATCHES", "2")))
+    ap.add_argument("--tp-comm", default=os.environ.get("KAREUS_TP_COMM", "allreduce"))
+    ap.add_argument("--comm-backend", default=os.environ.get("KAREUS_COMM_BACKEND", "nccl"))
+    ap.add_argument("--recompute-layers", type=int, default=int(os.environ.get("KAREUS_RECOMPUTE_LAYERS", "4")))
+    ap.add_argument("--skip-e2e", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return _reference_arm(args)
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    import torch.distributed as dist
+    from kareus_b200.config import ParallelConfig, TrainConfig, get_model_config
+    from kareus_b200.kernels import cuda as KC, launch_count
+    from kareus_b200.parallel.mesh import Mesh, init_distributed
+    from kareus_b200.train.trainer import Trainer, synthetic_batch
+
+    rank, world, local = init_distributed()
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    KC.lib()
+
+    cfg = get_model_config(args.model)
+    tc = TrainConfig(micro_batch_size=args.mbs, global_batch_size=args.gbs, seq_len=args.seq, dtype="bf16")
+    par = ParallelConfig(tp=world, num_nanobatches=args.nano, tp_comm=args.tp_comm if world > 1 else "allreduce",
+                         comm_backend=args.comm_backend, recompute=True)
+    mesh = Mesh(tp=world)
+    heap = None
+    if world > 1 and (par.comm_backend == "kernel" or par.tp_comm == "sp_fused"):
+        from kareus_b200.parallel.symm_heap import SymmetricHeap
+        heap = SymmetricHeap.create(mesh.group("tp"), device)
+    trainer = Trainer(cfg, par, tc, mesh=mesh, device=device, heap=heap, recompute_layers=args.recompute_layers)
+    M = trainer.num_microbatches
+    host_batches = [synthetic_batch(cfg, tc, M, seed=1000 + i) for i in range(2)]
+    tokens_per_step = args.gbs * args.seq
+    denom = float(tokens_per_step)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    # ------------------------------------------------------------- device-timed region
+    dev_batches = [trainer.to_device(b) for b in host_batches]
+    for i in range(args.warmup):
+        trainer.optimizer.zero_grad()
+        trainer.forward_backward(dev_batches[i % 2], denom)
+        trainer.model.finalize_grads()
+        trainer.optimizer.step()
+    sync_all()
+    KC.check_status()
+    sampler = ClockSampler(local)
+    sampler.start()
+    e0 = sampler.energy_mj()
+    l0 = launch_count()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(args.steps):
+        trainer.optimizer.zero_grad()
+        loss = trainer.forward_backward(dev_batches[i % 2], denom)
+        trainer.model.finalize_grads()
+        trainer.optimizer.step()
+    end.record()
+    sync_all()
+    e1 = sampler.energy_mj()
+    launches = launch_count() - l0
+    sampler.stop()
+    KC.check_status()
+    ms = start.elapsed_time(end)
+    t = torch.tensor([ms], device=device, dtype=torch.float64)
+    en = torch.tensor([(e1 - e0) / 1000.0 if (e0 is not None and e1 is not None) else 0.0], device=device,
+                      dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(en, op=dist.ReduceOp.SUM)
+    ms = float(t.item())
+    value = tokens_per_step * args.steps / (ms / 1000.0)
+    final_loss = trainer.reduce_loss(loss)
+
+    # ------------------------------------------------------------- end-to-end region
+    e2e = None
+    if not args.skip_e2e:
+        for i in range(2):
+            trainer.train_step(host_batches[i % 2], loss_denominator=denom)
+        sync_all()
+        t0 = time.perf_counter()
+        for i in range(args.steps):
+            final_loss = trainer.train_step(host_batches[i % 2], loss_denominator=denom)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        tt = torch.tensor([dt], device=device, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        dt = float(tt.item())
+        h2d = sum(v.numel() * v.element_size() for v in host_batches[0].values())
+        e2e = {"value": tokens_per_step * args.steps / dt, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": 4, "ms_per_step": dt * 1000.0 / args.steps}
+        KC.check_status()
+
+    if rank == 0:
+        out = {
+            "metric": "tokens/s (Llama-3.2-3B training throughput)", "value": value, "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": value / BASELINE_TOKENS_PER_S,
+            "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights",
+            "config": {"model": args.model, "global_batch": args.gbs, "micro_batch": args.mbs, "seq_len": args.seq,
+                       "parallelism": f"tp{world}", "nanobatches": args.nano, "tp_comm": par.tp_comm,
+                       "comm_backend": par.comm_backend, "recompute": f"full, {args.recompute_layers} layers per chunk",
+                       "optimizer": "AdamW fp32 master, in the timed region",
+                       "l2": "inputs larger than L2 (6.4 GB of weights and multi-GB activations per step)"},
+            "energy_j_per_step": float(en.item()) / args.steps,
+            "clocks": sampler.summary(), "e2e": e2e, "gpu_launches": launches, "loss": final_loss,
+            "impl": "ours",
+        }
+        print(json.dumps(out))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

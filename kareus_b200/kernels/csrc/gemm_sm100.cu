@@ -1,0 +1,287 @@
+// bf16 GEMM for sm_100a: C[M,N] (+)= A[M,K] * B[N,K]^T with fp32 accumulation in tensor memory.
+//
+// Persistent, warp-specialised kernel, one CTA per SM:
+//   warp 0      TMA producer   (cp.async.bulk.tensor into a 4-stage, 128B-swizzled smem ring)
+//   warp 1      MMA issuer     (tcgen05.mma 128xBNx16, one thread; TMEM allocation)
+//   warps 2..5  epilogue       (tcgen05.ld of the accumulator, convert, store / accumulate)
+// Two accumulator buffers in TMEM let the epilogue of tile i overlap the main loop of tile i+1.
+//
+// Both operands may be K-major (row = output index, K contiguous) or MN-major (row = K, output
+// index contiguous), which covers fprop (x·Wᵀ), dgrad (dy·W) and wgrad (dyᵀ·x) without
+// transposing anything in memory.  This is the role of the reference's cuBLASLt wrapper
+// (3rdparty/TransformerEngine/transformer_engine/common/gemm/cublaslt_gemm.cu; layouts TN/NN/NT
+// at kareus/transformer_engine/pytorch/ops/basic/basic_linear.py:572-582,848-859,899-909).
+#include "sm100.cuh"
+#include "host_utils.h"
+
+namespace kb {
+
+constexpr int GEMM_BM = 128;
+constexpr int GEMM_BK = 64;
+constexpr int GEMM_STAGES = 4;
+constexpr int GEMM_THREADS = 192;
+
+template <int BN>
+struct GemmSmem {
+  static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
+  static constexpr int B_BYTES = BN * GEMM_BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int TILE_BYTES = STAGE_BYTES * GEMM_STAGES;
+  static constexpr int BAR_BYTES = 256;
+  static constexpr int TOTAL = TILE_BYTES + BAR_BYTES + 1024;  // + alignment slack
+};
+
+template <int BN, bool A_MN, bool B_MN, bool OUT_F32, bool ACCUM>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 void* __restrict__ Cout, int M, int N, int K, int ldc, int* status) {
+  using S = GemmSmem<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + S::TILE_BYTES);
+  uint64_t* empty = full + GEMM_STAGES;
+  uint64_t* tfull = empty + GEMM_STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int tiles_m = (M + GEMM_BM - 1) / GEMM_BM;
+  const int tiles_n = (N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int nk = (K + GEMM_BK - 1) / GEMM_BK;
+  constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : 2 * BN;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < GEMM_STAGES; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tfull[i], 1);
+      mbar_init(&tempty[i], 4);   // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      prefetch_tmap(&tmA);
+      prefetch_tmap(&tmB);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        const int m0 = (t % tiles_m) * GEMM_BM;
+        const int n0 = (t / tiles_m) * BN;
+        for (int kb_ = 0; kb_ < nk; ++kb_, ++it) {
+          const int s = it % GEMM_STAGES;
+          const uint32_t ph = (it / GEMM_STAGES) & 1u;
+          if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag, status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
+          uint8_t* a_dst = smem + s * S::STAGE_BYTES;
+          uint8_t* b_dst = a_dst + S::A_BYTES;
+          mbar_expect_tx(&full[s], S::STAGE_BYTES);
+          const int k0 = kb_ * GEMM_BK;
+          if constexpr (!A_MN) {
+            tma_load_2d(a_dst, &tmA, &full[s], k0, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < GEMM_BM / 64; ++j) tma_load_2d(a_dst + j * 8192, &tmA, &full[s], m0 + 64 * j, k0);
+          }
+          if constexpr (!B_MN) {
+            tma_load_2d(b_dst, &tmB, &full[s], k0, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * 8192, &tmB, &full[s], n0 + 64 * j, k0);
+          }
+        }
+      }
+      if (!ok) {
+        // leave no copy in flight: tile loads land within microseconds, give them 200 us
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) {}
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    constexpr uint32_t idesc = make_idesc_bf16(GEMM_BM, BN, A_MN, B_MN);
+    uint32_t it = 0;
+    uint32_t tile_i = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_i) {
+      const uint32_t buf = tile_i & 1u;
+      const uint32_t bph = (tile_i >> 1) & 1u;
+      if (!mbar_wait(&tempty[buf], bph ^ 1u, abort_flag, status, ST_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + buf * BN;
+      for (int kb_ = 0; kb_ < nk; ++kb_, ++it) {
+        const int s = it % GEMM_STAGES;
+        const uint32_t ph = (it / GEMM_STAGES) & 1u;
+        if (!mbar_wait(&full[s], ph, abort_flag, status, ST_TIMEOUT_FULL)) { ok = false; break; }
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t a_addr = smem_u32(smem + s * S::STAGE_BYTES);
+          const uint32_t b_addr = a_addr + S::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < GEMM_BK / 16; ++k) {
+            const uint64_t ad = A_MN ? make_smem_desc(a_addr + k * 2048, 8192, 1024)
+                                     : make_smem_desc(a_addr + k * 32, 16, 1024);
+            const uint64_t bd = B_MN ? make_smem_desc(b_addr + k * 2048, 8192, 1024)
+                                     : make_smem_desc(b_addr + k * 32, 16, 1024);
+            umma_ss(d_tmem, ad, bd, idesc, (kb_ > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty[s]);                       // stage reusable once these MMAs retire
+          if (kb_ == nk - 1) umma_commit(&tfull[buf]);  // accumulator complete
+        }
+        __syncwarp();
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;                 // TMEM lane quarter this warp may read
+    uint32_t tile_i = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_i) {
+      const uint32_t buf = tile_i & 1u;
+      const uint32_t bph = (tile_i >> 1) & 1u;
+      const int m0 = (t % tiles_m) * GEMM_BM;
+      const int n0 = (t / tiles_m) * BN;
+      if (!mbar_wait(&tfull[buf], bph, abort_flag, status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      const uint32_t taddr = tmem_base + buf * BN + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(taddr + c * 32, v);
+        tmem_ld_wait();
+        const int col = n0 + c * 32;
+        if (row < M && col < N) {
+          if constexpr (OUT_F32) {
+            float* crow = reinterpret_cast<float*>(Cout) + static_cast<size_t>(row) * ldc + col;
+            if (col + 32 <= N && (ldc & 3) == 0) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                float4 o = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                       __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+                float4* p = reinterpret_cast<float4*>(crow) + j;
+                if constexpr (ACCUM) {
+                  float4 old = *p;
+                  o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                }
+                *p = o;
+              }
+            } else {
+              for (int j = 0; j < 32 && col + j < N; ++j) {
+                float o = __uint_as_float(v[j]);
+                if constexpr (ACCUM) o += crow[j];
+                crow[j] = o;
+              }
+            }
+          } else {
+            __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(Cout) + static_cast<size_t>(row) * ldc + col;
+            if (col + 32 <= N && (ldc & 7) == 0) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint4 o;
+                o.x = pack_bf16x2(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
+                o.y = pack_bf16x2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
+                o.z = pack_bf16x2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
+                o.w = pack_bf16x2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
+                reinterpret_cast<uint4*>(crow)[j] = o;
+              }
+            } else {
+              for (int j = 0; j < 32 && col + j < N; ++j) crow[j] = __float2bfloat16(__uint_as_float(v[j]));
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[buf]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ----------------------------------------------------------------------------- host side
+template <int BN, bool A_MN, bool B_MN, bool OUT_F32, bool ACCUM>
+static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
+                       int num_sms, int* status, cudaStream_t stream) {
+  CUtensorMap tmA, tmB;
+  int rc;
+  // K-major operand: dims (K, rows), box (64, tile rows).  MN-major: dims (rows, K), box (64, 64).
+  if (!A_MN) rc = make_tmap_2d_bf16(&tmA, A, K, M, lda, GEMM_BK, GEMM_BM);
+  else       rc = make_tmap_2d_bf16(&tmA, A, M, K, lda, 64, GEMM_BK);
+  if (rc) return rc;
+  if (!B_MN) rc = make_tmap_2d_bf16(&tmB, B, K, N, ldb, GEMM_BK, BN);
+  else       rc = make_tmap_2d_bf16(&tmB, B, N, K, ldb, 64, GEMM_BK);
+  if (rc) return rc;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, OUT_F32, ACCUM>;
+  constexpr int smem = GemmSmem<BN>::TOTAL;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return 1000 + static_cast<int>(e);
+    configured = true;
+  }
+  const int tiles = ((M + GEMM_BM - 1) / GEMM_BM) * ((N + BN - 1) / BN);
+  int grid = tiles < num_sms ? tiles : num_sms;
+  if (grid < 1) grid = 1;
+  kern<<<grid, GEMM_THREADS, smem, stream>>>(tmA, tmB, C, M, N, K, ldc, status);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 2000 + static_cast<int>(e);
+}
+
+template <int BN, bool A_MN, bool B_MN>
+static int dispatch_out(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
+                        int out_f32, int accumulate, int num_sms, int* status, cudaStream_t stream) {
+  if (out_f32 && accumulate)
+    return launch_gemm<BN, A_MN, B_MN, true, true>(A, B, C, M, N, K, lda, ldb, ldc, num_sms, status, stream);
+  if (out_f32)
+    return launch_gemm<BN, A_MN, B_MN, true, false>(A, B, C, M, N, K, lda, ldb, ldc, num_sms, status, stream);
+  if (accumulate) return ST_BAD_ARG;
+  return launch_gemm<BN, A_MN, B_MN, false, false>(A, B, C, M, N, K, lda, ldb, ldc, num_sms, status, stream);
+}
+
+}  // namespace kb
+
+// C[M,N] (+)= op(A) * op(B)^T.
+//   a_mn = 0: A is [M, K] row-major (lda = row stride in elements); a_mn = 1: A is stored [K, M].
+//   b_mn = 0: B is [N, K] row-major;                                b_mn = 1: B is stored [K, N].
+//   out_f32: C is fp32 (else bf16); accumulate: C += (fp32 only).  num_sms limits the grid.
+// Strides must be multiples of 8 elements and base pointers 16-byte aligned (TMA rules).
+extern "C" int kb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int a_mn, int lda,
+                            int b_mn, int ldb, int ldc, int out_f32, int accumulate, int num_sms, int* status,
+                            cudaStream_t stream) {
+  using namespace kb;
+  if (M <= 0 || N <= 0 || K <= 0) return ST_BAD_ARG;
+  if ((lda & 7) || (ldb & 7) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
+    return ST_BAD_ARG;
+  if (num_sms <= 0) num_sms = device_sm_count();
+  // narrow outputs waste less of the last wave with the 128-wide tile
+  const bool narrow = (N <= 128) || (N % 256 != 0 && N % 256 <= 128);
+#define KB_GO(BN_)                                                                                         \
+  do {                                                                                                     \
+    if (!a_mn && !b_mn) return dispatch_out<BN_, false, false>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, accumulate, num_sms, status, stream); \
+    if (!a_mn && b_mn) return dispatch_out<BN_, false, true>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, accumulate, num_sms, status, stream);   \
+    if (a_mn && !b_mn) return dispatch_out<BN_, true, false>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, accumulate, num_sms, status, stream);   \
+    return dispatch_out<BN_, true, true>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, accumulate, num_sms, status, stream);                       \
+  } while (0)
+  if (narrow) KB_GO(128);
+  KB_GO(256);
+#undef KB_GO
+}

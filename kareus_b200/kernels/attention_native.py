@@ -1,0 +1,72 @@
+"""Wrappers of the hand-written sm_100a flash-attention kernels.
+
+Inputs may be strided views: ``q`` is ``[sq, b, h, d]`` or ``[sq, b, g, rep, d]``, ``k``/``v`` are
+``[skv, b, g, d]``, all with a contiguous head dimension of 128 and 16-byte aligned strides (views
+of the packed QKV projection qualify).  ``q_offset`` is the absolute position of query row 0
+relative to key 0 and ``kv_len`` limits the visible keys; together they express the causal masks of
+context-parallel chunks.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_long, c_void_p
+
+import torch
+
+from . import cuda as KC
+
+_DECLARED = False
+
+
+def _lib():
+    global _DECLARED
+    L = KC.lib()
+    if not _DECLARED:
+        P, I, LNG, F = c_void_p, c_int, c_long, c_float
+        L.kb_flash_attn_fwd.argtypes = [P, LNG, LNG, LNG, LNG, P, LNG, LNG, LNG, P, LNG, LNG, LNG, P, P,
+                                        I, I, I, I, I, I, F, I, I, P, P]
+        L.kb_flash_attn_fwd.restype = c_int
+        if hasattr(L, "kb_flash_attn_bwd"):
+            L.kb_flash_attn_bwd.restype = c_int
+        _DECLARED = True
+    return L
+
+
+def _q_geometry(q):
+    if q.dim() == 5:
+        s, b, g, rep, d = q.shape
+        return s, b, g, rep, d, (q.stride(0), q.stride(1), q.stride(2), q.stride(3))
+    s, b, h, d = q.shape
+    return s, b, 1, h, d, (q.stride(0), q.stride(1), 0, q.stride(2))
+
+
+def _usable(t) -> bool:
+    return t.stride(-1) == 1 and t.data_ptr() % 16 == 0 and all(st % 8 == 0 for st in t.stride()[:-1])
+
+
+def forward(q, k, v, scale, causal=True, q_offset=0, kv_len=None):
+    sq, b, g, rep, d, qs = _q_geometry(q)
+    kg = k.shape[2]
+    if q.dim() == 4:
+        # [s,b,h,d] with h = kg*rep heads laid out group-major: reinterpret as (g, rep)
+        rep = q.shape[2] // kg
+        g = kg
+        qs = (q.stride(0), q.stride(1), q.stride(2) * rep, q.stride(2))
+    if d != 128 or not (_usable(q) and _usable(k) and _usable(v)) or g != kg:
+        return KC.attention_fwd_library(q, k, v, scale, causal, q_offset, kv_len)
+    skv = k.shape[0] if kv_len is None else int(kv_len)
+    out = torch.empty(sq, b, g * rep, d, dtype=q.dtype, device=q.device)
+    lse = torch.empty(b, g * rep, sq, dtype=torch.float32, device=q.device)
+    st = KC.status_word(q.device)
+    rc = _lib().kb_flash_attn_fwd(q.data_ptr(), *qs, k.data_ptr(), k.stride(0), k.stride(1), k.stride(2),
+                                  v.data_ptr(), v.stride(0), v.stride(1), v.stride(2), out.data_ptr(),
+                                  lse.data_ptr(), sq, skv, b, g, rep, d, float(scale), 1 if causal else 0,
+                                  int(q_offset), st.data_ptr(), KC._stream())
+    KC._check(rc, "flash_attn_fwd")
+    KC._count()
+    return out, lse
+
+
+def backward(do, q, k, v, o, lse, scale, causal=True, q_offset=0, kv_len=None, out=None):
+    from . import attention_bwd_native
+    return attention_bwd_native.backward(do, q, k, v, o, lse, scale, causal, q_offset, kv_len, out)

@@ -1,0 +1,391 @@
+// Causal GQA flash-attention forward for sm_100a, head dim 128, bf16 in / bf16 out, fp32 softmax.
+//
+// One CTA owns a tile of 128 query rows of one (batch, head) and walks the visible key tiles:
+//   warp 0      TMA producer: Q once, then K and V tiles into a 2-stage ring (128B swizzle)
+//   warp 1      MMA issuer:   S = Q·Kᵀ (tcgen05, accumulator in TMEM, double buffered) and
+//                             O += P·V (P from shared memory, V as an MN-major operand)
+//   warps 2..5  softmax:      one thread per query row; S row from TMEM → scale, mask, running
+//                             max/sum in the log2 domain → P (bf16) into swizzled shared memory.
+// The S of tile j+1 is issued before the softmax of tile j finishes, so tensor cores and the
+// exponent units overlap.  O stays in TMEM for the whole row tile; it is rescaled only when the
+// running maximum moves by more than 2^8 ("lazy rescale"), which happens on the first tiles only.
+//
+// Q, K and V are read through TMA from strided views of the packed QKV projection
+// ([s, b, groups, (rep+2)·d]), so no transpose or copy precedes the kernel (the reference
+// transposes sbhd→bshd and calls the FlashAttention-2 wheel:
+// kareus/transformer_engine/pytorch/attention/dot_product_attention/backends.py:179-186,328-333).
+#include "sm100.cuh"
+#include "host_utils.h"
+
+namespace kb {
+
+constexpr int FA_BM = 128;      // query rows per CTA
+constexpr int FA_BN = 128;      // keys per tile
+constexpr int FA_D = 128;       // head dim
+constexpr int FA_THREADS = 192;
+constexpr int FA_TILE_BYTES = FA_BN * FA_D * 2;   // 32 KB: two 64-wide swizzled chunks of 16 KB
+constexpr int FA_CHUNK = 16384;
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+struct FwdParams {
+  __nv_bfloat16* out;   // [sq, b, hq, d] contiguous
+  float* lse;           // [b, hq, sq]
+  int sq, skv, b, hq, rep;
+  int q_offset;         // absolute position of query row 0 relative to key 0
+  float scale_log2;     // softmax scale * log2(e)
+  int causal;
+  int* status;
+};
+
+struct FaSmem {
+  static constexpr int Q_OFF = 0;
+  static constexpr int K_OFF = Q_OFF + FA_TILE_BYTES;               // 2 stages
+  static constexpr int V_OFF = K_OFF + 2 * FA_TILE_BYTES;           // 2 stages
+  static constexpr int P_OFF = V_OFF + 2 * FA_TILE_BYTES;
+  static constexpr int BAR_OFF = P_OFF + FA_TILE_BYTES;
+  static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+};
+
+__global__ void __launch_bounds__(FA_THREADS, 1)
+flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                      const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FaSmem::BAR_OFF);
+  uint64_t* q_full = bars + 0;
+  uint64_t* k_full = bars + 1;    // [2]
+  uint64_t* v_full = bars + 3;    // [2]
+  uint64_t* kv_empty = bars + 5;  // [2]
+  uint64_t* s_full = bars + 7;    // [2]
+  uint64_t* s_empty = bars + 9;   // [2]
+  uint64_t* p_full = bars + 11;
+  uint64_t* pv_done = bars + 12;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // heavy (late) query tiles first
+  const int n_qtiles = (p.sq + FA_BM - 1) / FA_BM;
+  const int qt = n_qtiles - 1 - static_cast<int>(blockIdx.x);
+  const int head = blockIdx.y;
+  const int batch = blockIdx.z;
+  const int g = head / p.rep, r = head % p.rep;
+  const int q0 = qt * FA_BM;
+  // keys visible to this tile: [0, kv_end)
+  int kv_end = p.skv;
+  if (p.causal) {
+    const int last_q = p.q_offset + min(q0 + FA_BM, p.sq) - 1;
+    kv_end = min(p.skv, last_q + 1);
+  }
+  const int n_kv = kv_end > 0 ? (kv_end + FA_BN - 1) / FA_BN : 0;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&kv_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_empty[i], 4);
+    }
+    mbar_init(p_full, 4);
+    mbar_init(pv_done, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_s = tmem_base;         // 2 x 128 columns
+  const uint32_t tmem_o = tmem_base + 256;   // 128 columns
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0 && n_kv > 0) {
+      prefetch_tmap(&tmQ);
+      prefetch_tmap(&tmK);
+      prefetch_tmap(&tmV);
+      mbar_expect_tx(q_full, FA_TILE_BYTES);
+      tma_load_5d(smem + FaSmem::Q_OFF, &tmQ, q_full, 0, r, g, batch, q0);
+      tma_load_5d(smem + FaSmem::Q_OFF + FA_CHUNK, &tmQ, q_full, 64, r, g, batch, q0);
+      for (int j = 0; j < n_kv; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1u;
+        if (!mbar_wait(&kv_empty[s], ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_EMPTY)) break;
+        uint8_t* kd = smem + FaSmem::K_OFF + s * FA_TILE_BYTES;
+        uint8_t* vd = smem + FaSmem::V_OFF + s * FA_TILE_BYTES;
+        mbar_expect_tx(&k_full[s], FA_TILE_BYTES);
+        tma_load_4d(kd, &tmK, &k_full[s], 0, g, batch, j * FA_BN);
+        tma_load_4d(kd + FA_CHUNK, &tmK, &k_full[s], 64, g, batch, j * FA_BN);
+        mbar_expect_tx(&v_full[s], FA_TILE_BYTES);
+        tma_load_4d(vd, &tmV, &v_full[s], 0, g, batch, j * FA_BN);
+        tma_load_4d(vd + FA_CHUNK, &tmV, &v_full[s], 64, g, batch, j * FA_BN);
+      }
+      if (*abort_flag) {
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) {}
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    constexpr uint32_t idesc_s = make_idesc_bf16(FA_BM, FA_BN, false, false);  // Q K-major, K K-major
+    constexpr uint32_t idesc_o = make_idesc_bf16(FA_BM, FA_D, false, true);    // P K-major, V MN-major
+    const uint32_t q_addr = smem_u32(smem + FaSmem::Q_OFF);
+    const uint32_t p_addr = smem_u32(smem + FaSmem::P_OFF);
+    bool ok = n_kv > 0;
+    auto issue_s = [&](int j) {
+      const int s = j & 1;
+      const uint32_t k_addr = smem_u32(smem + FaSmem::K_OFF + s * FA_TILE_BYTES);
+      if (lane == 0) {
+#pragma unroll
+        for (int k = 0; k < FA_D / 16; ++k) {
+          const uint32_t off = (k >> 2) * FA_CHUNK + (k & 3) * 32;
+          umma_ss(tmem_s + s * FA_BN, make_smem_desc(q_addr + off, 16, 1024), make_smem_desc(k_addr + off, 16, 1024),
+                  idesc_s, k > 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[s]);
+      }
+      __syncwarp();
+    };
+    if (ok) ok = mbar_wait(q_full, 0, abort_flag, p.status, ST_TIMEOUT_FULL);
+    if (ok) ok = mbar_wait(&k_full[0], 0, abort_flag, p.status, ST_TIMEOUT_FULL);
+    if (ok) {
+      tc_fence_after();
+      issue_s(0);
+    }
+    for (int j = 0; j < n_kv && ok; ++j) {
+      const int s = j & 1;
+      if (j + 1 < n_kv) {
+        const int s1 = (j + 1) & 1;
+        const uint32_t ph1 = ((j + 1) >> 1) & 1u;
+        if (!mbar_wait(&k_full[s1], ph1, abort_flag, p.status, ST_TIMEOUT_FULL)) { ok = false; break; }
+        if (!mbar_wait(&s_empty[s1], ph1 ^ 1u, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+        tc_fence_after();
+        issue_s(j + 1);
+      }
+      if (!mbar_wait(p_full, j & 1u, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      if (!mbar_wait(&v_full[s], (j >> 1) & 1u, abort_flag, p.status, ST_TIMEOUT_FULL)) { ok = false; break; }
+      tc_fence_after();
+      if (lane == 0) {
+        const uint32_t v_addr = smem_u32(smem + FaSmem::V_OFF + s * FA_TILE_BYTES);
+#pragma unroll
+        for (int k = 0; k < FA_BN / 16; ++k) {
+          // A = P [128 rows][128 keys] K-major: two 64-key chunks; B = V [keys][d] MN-major
+          const uint32_t a_off = (k >> 2) * FA_CHUNK + (k & 3) * 32;
+          umma_ss(tmem_o, make_smem_desc(p_addr + a_off, 16, 1024),
+                  make_smem_desc(v_addr + k * 2048, FA_CHUNK, 1024), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(&kv_empty[s]);
+        umma_commit(pv_done);
+      }
+      __syncwarp();
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax + epilogue
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;           // row inside the tile = TMEM lane
+    const int qpos = p.q_offset + q0 + row;        // absolute position of this query
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    float m_ref = -INFINITY;   // reference maximum (log2 domain) used for the exponentials
+    float l_sum = 0.f;
+    bool ok = n_kv > 0;
+    uint8_t* p_row = smem + FaSmem::P_OFF + row * 128;
+    for (int j = 0; j < n_kv && ok; ++j) {
+      const int s = j & 1;
+      if (!mbar_wait(&s_full[s], (j >> 1) & 1u, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t v[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32(tmem_s + s * FA_BN + lane_addr + c * 32, v[c]);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[s]);
+
+      const int key0 = j * FA_BN;
+      const bool need_mask = (p.causal && key0 + FA_BN - 1 > qpos) || (key0 + FA_BN > p.skv);
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float x = __uint_as_float(v[c][i]) * p.scale_log2;
+          if (need_mask) {
+            const int key = key0 + c * 32 + i;
+            if ((p.causal && key > qpos) || key >= p.skv) x = -INFINITY;
+          }
+          v[c][i] = __float_as_uint(x);
+          mx = fmaxf(mx, x);
+        }
+      }
+      float rescale = 1.f;
+      bool do_rescale = false;
+      if (mx > m_ref + 8.f) {       // also true on the first tile (m_ref = -inf)
+        if (j > 0 && m_ref != -INFINITY) {
+          rescale = fast_exp2(m_ref - mx);
+          do_rescale = true;
+        }
+        m_ref = mx;
+      }
+      const float mref = (m_ref == -INFINITY) ? 0.f : m_ref;
+      float psum = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float e = fast_exp2(__uint_as_float(v[c][i]) - mref);
+          psum += e;
+          v[c][i] = __float_as_uint(e);
+        }
+      }
+      l_sum = l_sum * rescale + psum;
+
+      // P buffer and O are free once the previous P·V has completed
+      if (j > 0) {
+        if (!mbar_wait(pv_done, (j - 1) & 1u, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+        tc_fence_after();
+      }
+      // warp-uniform decision so the .aligned TMEM accesses stay converged
+      const bool any_rescale = __any_sync(0xffffffffu, do_rescale);
+      if (any_rescale) {
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t o[32];
+          tmem_ld_32x32(tmem_o + lane_addr + c * 32, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * rescale);
+          tmem_st_32x32(tmem_o + lane_addr + c * 32, o);
+        }
+        tmem_st_wait();
+      }
+      // P (bf16) into the K-major, 128B-swizzled operand layout: 16-byte unit u of row r goes to
+      // unit (u ^ (r & 7)) of that row inside its 64-key chunk
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          uint4 w;
+          w.x = pack_bf16x2(__uint_as_float(v[c][8 * u + 0]), __uint_as_float(v[c][8 * u + 1]));
+          w.y = pack_bf16x2(__uint_as_float(v[c][8 * u + 2]), __uint_as_float(v[c][8 * u + 3]));
+          w.z = pack_bf16x2(__uint_as_float(v[c][8 * u + 4]), __uint_as_float(v[c][8 * u + 5]));
+          w.w = pack_bf16x2(__uint_as_float(v[c][8 * u + 6]), __uint_as_float(v[c][8 * u + 7]));
+          const int unit = (c & 1) * 4 + u;              // 16-byte unit inside the 64-key chunk
+          uint8_t* dst = p_row + (c >> 1) * FA_CHUNK + ((unit ^ (row & 7)) << 4);
+          *reinterpret_cast<uint4*>(dst) = w;
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+    }
+    // ---- epilogue: O / l → global, LSE
+    if (ok && n_kv > 0) ok = mbar_wait(pv_done, (n_kv - 1) & 1u, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
+    if (n_kv > 0) {
+      tc_fence_after();
+      const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
+      const int qrow = q0 + row;
+      __nv_bfloat16* orow = p.out + ((static_cast<size_t>(qrow) * p.b + batch) * p.hq + head) * FA_D;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t o[32];
+        tmem_ld_32x32(tmem_o + lane_addr + c * 32, o);
+        tmem_ld_wait();
+        if (ok && qrow < p.sq) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(o[8 * u + 0]) * inv, __uint_as_float(o[8 * u + 1]) * inv);
+            w.y = pack_bf16x2(__uint_as_float(o[8 * u + 2]) * inv, __uint_as_float(o[8 * u + 3]) * inv);
+            w.z = pack_bf16x2(__uint_as_float(o[8 * u + 4]) * inv, __uint_as_float(o[8 * u + 5]) * inv);
+            w.w = pack_bf16x2(__uint_as_float(o[8 * u + 6]) * inv, __uint_as_float(o[8 * u + 7]) * inv);
+            reinterpret_cast<uint4*>(orow + c * 32)[u] = w;
+          }
+        }
+      }
+      if (ok && qrow < p.sq)
+        p.lse[(static_cast<size_t>(batch) * p.hq + head) * p.sq + qrow] =
+            (l_sum > 0.f) ? (m_ref + log2f(l_sum)) * 0.6931471805599453f : -INFINITY;
+    } else {
+      // no visible key at all (only possible with a negative q_offset): zero output
+      const int qrow = q0 + row;
+      if (qrow < p.sq) {
+        __nv_bfloat16* orow = p.out + ((static_cast<size_t>(qrow) * p.b + batch) * p.hq + head) * FA_D;
+        for (int i = 0; i < FA_D / 8; ++i) reinterpret_cast<uint4*>(orow)[i] = make_uint4(0, 0, 0, 0);
+        p.lse[(static_cast<size_t>(batch) * p.hq + head) * p.sq + qrow] = -INFINITY;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace kb
+
+// q: view [sq, b, g, rep, d] (strides in elements, d contiguous); k, v: views [skv, b, g, d];
+// out: [sq, b, g*rep, d] contiguous; lse: [b, g*rep, sq] fp32.
+extern "C" int kb_flash_attn_fwd(const void* q, long qs_s, long qs_b, long qs_g, long qs_r, const void* k, long ks_s,
+                                 long ks_b, long ks_g, const void* v, long vs_s, long vs_b, long vs_g, void* out,
+                                 float* lse, int sq, int skv, int b, int g, int rep, int d, float scale, int causal,
+                                 int q_offset, int* status, cudaStream_t stream) {
+  using namespace kb;
+  if (d != FA_D || sq <= 0 || skv <= 0) return ST_BAD_ARG;
+  CUtensorMap tmQ, tmK, tmV;
+  {
+    uint64_t dims[5] = {(uint64_t)d, (uint64_t)rep, (uint64_t)g, (uint64_t)b, (uint64_t)sq};
+    uint64_t str[4] = {(uint64_t)qs_r * 2, (uint64_t)qs_g * 2, (uint64_t)qs_b * 2, (uint64_t)qs_s * 2};
+    uint32_t box[5] = {64, 1, 1, 1, FA_BM};
+    // a size-1 dimension may carry any stride; TMA still wants it to be a multiple of 16 bytes
+    for (int i = 0; i < 4; ++i) if (str[i] == 0 || (str[i] & 15)) str[i] = (uint64_t)d * 2;
+    int rc = make_tmap(&tmQ, q, 2, 5, dims, str, box, 3);
+    if (rc) return rc;
+  }
+  {
+    uint64_t dims[4] = {(uint64_t)d, (uint64_t)g, (uint64_t)b, (uint64_t)skv};
+    uint32_t box[4] = {64, 1, 1, FA_BN};
+    uint64_t strk[3] = {(uint64_t)ks_g * 2, (uint64_t)ks_b * 2, (uint64_t)ks_s * 2};
+    uint64_t strv[3] = {(uint64_t)vs_g * 2, (uint64_t)vs_b * 2, (uint64_t)vs_s * 2};
+    for (int i = 0; i < 3; ++i) {
+      if (strk[i] == 0 || (strk[i] & 15)) strk[i] = (uint64_t)d * 2;
+      if (strv[i] == 0 || (strv[i] & 15)) strv[i] = (uint64_t)d * 2;
+    }
+    int rc = make_tmap(&tmK, k, 2, 4, dims, strk, box, 3);
+    if (rc) return rc;
+    rc = make_tmap(&tmV, v, 2, 4, dims, strv, box, 3);
+    if (rc) return rc;
+  }
+  FwdParams p;
+  p.out = reinterpret_cast<__nv_bfloat16*>(out);
+  p.lse = lse;
+  p.sq = sq; p.skv = skv; p.b = b; p.hq = g * rep; p.rep = rep;
+  p.q_offset = q_offset;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.causal = causal;
+  p.status = status;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(flash_attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         FaSmem::TOTAL);
+    if (e != cudaSuccess) return 1000 + (int)e;
+    configured = true;
+  }
+  dim3 grid((sq + FA_BM - 1) / FA_BM, g * rep, b);
+  flash_attn_fwd_kernel<<<grid, FA_THREADS, FaSmem::TOTAL, stream>>>(tmQ, tmK, tmV, p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 2000 + (int)e;
+}

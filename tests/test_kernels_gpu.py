@@ -164,3 +164,39 @@ def test_bounded_wait_reports_timeout_status():
         KC.check_status()
     KC.check_status()      # reset by the failed check
     assert torch.ones(4, device="cuda").sum().item() == 4
+
+
+@pytest.mark.parametrize("s,b,g,rep", [(256, 1, 1, 1), (512, 2, 2, 3), (1000, 1, 1, 3), (4096, 1, 1, 2)])
+def test_flash_attention_forward(s, b, g, rep):
+    KC = _K()
+    from kareus_b200.kernels import attention_cuda, ref
+    if not attention_cuda.have_native():
+        pytest.skip("native attention kernel not built")
+    d = 128
+    packed = torch.randn(s, b, g, (rep + 2) * d, device="cuda").bfloat16()
+    q = packed[..., : rep * d].unflatten(-1, (rep, d))
+    k = packed[..., rep * d:(rep + 1) * d]
+    v = packed[..., (rep + 1) * d:]
+    out, lse = attention_cuda.forward(q, k, v, d ** -0.5, True, 0, None)
+    KC.check_status()
+    want, lse_w = ref.attention_fwd(q.float(), k.float(), v.float(), d ** -0.5, True)
+    assert _rel(out, want) < 1e-2
+    torch.testing.assert_close(lse, lse_w, rtol=1e-3, atol=1e-3)
+
+
+def test_flash_attention_forward_offsets():
+    """Context-parallel style masks: query chunk at an offset against a key prefix."""
+    KC = _K()
+    from kareus_b200.kernels import attention_cuda, ref
+    if not attention_cuda.have_native():
+        pytest.skip("native attention kernel not built")
+    d, c = 128, 192
+    q = torch.randn(c, 2, 2, 2, d, device="cuda").bfloat16()
+    k = torch.randn(4 * c, 2, 2, d, device="cuda").bfloat16()
+    v = torch.randn(4 * c, 2, 2, d, device="cuda").bfloat16()
+    for cid in (0, 2, 3):
+        out, lse = attention_cuda.forward(q, k, v, d ** -0.5, True, cid * c, (cid + 1) * c)
+        KC.check_status()
+        want, lse_w = ref.attention_fwd(q.float(), k.float(), v.float(), d ** -0.5, True, cid * c, (cid + 1) * c)
+        assert _rel(out, want) < 1e-2
+        torch.testing.assert_close(lse, lse_w, rtol=1e-3, atol=1e-3)

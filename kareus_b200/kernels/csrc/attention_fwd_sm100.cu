@@ -42,11 +42,14 @@ struct FwdParams {
   int* status;
 };
 
+constexpr int FA_KSTAGES = 3;   // K tiles are released as soon as their S MMA retires
+constexpr int FA_VSTAGES = 2;   // V tiles after their P·V MMA
+
 struct FaSmem {
   static constexpr int Q_OFF = 0;
-  static constexpr int K_OFF = Q_OFF + FA_TILE_BYTES;               // 2 stages
-  static constexpr int V_OFF = K_OFF + 2 * FA_TILE_BYTES;           // 2 stages
-  static constexpr int P_OFF = V_OFF + 2 * FA_TILE_BYTES;
+  static constexpr int K_OFF = Q_OFF + FA_TILE_BYTES;
+  static constexpr int V_OFF = K_OFF + FA_KSTAGES * FA_TILE_BYTES;
+  static constexpr int P_OFF = V_OFF + FA_VSTAGES * FA_TILE_BYTES;
   static constexpr int BAR_OFF = P_OFF + FA_TILE_BYTES;
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
@@ -58,14 +61,15 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FaSmem::BAR_OFF);
   uint64_t* q_full = bars + 0;
-  uint64_t* k_full = bars + 1;    // [2]
-  uint64_t* v_full = bars + 3;    // [2]
-  uint64_t* kv_empty = bars + 5;  // [2]
-  uint64_t* s_full = bars + 7;    // [2]
-  uint64_t* s_empty = bars + 9;   // [2]
-  uint64_t* p_full = bars + 11;
-  uint64_t* pv_done = bars + 12;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  uint64_t* k_full = bars + 1;    // [3]
+  uint64_t* k_empty = bars + 4;   // [3]
+  uint64_t* v_full = bars + 7;    // [2]
+  uint64_t* v_empty = bars + 9;   // [2]
+  uint64_t* s_full = bars + 11;   // [2]
+  uint64_t* s_empty = bars + 13;  // [2]
+  uint64_t* p_full = bars + 15;
+  uint64_t* pv_done = bars + 16;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -88,10 +92,13 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < FA_KSTAGES; ++i) {
       mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
       mbar_init(&v_full[i], 1);
-      mbar_init(&kv_empty[i], 1);
+      mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
       mbar_init(&s_empty[i], 4);
     }
@@ -117,15 +124,25 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       mbar_expect_tx(q_full, FA_TILE_BYTES);
       tma_load_5d(smem + FaSmem::Q_OFF, &tmQ, q_full, 0, r, g, batch, q0);
       tma_load_5d(smem + FaSmem::Q_OFF + FA_CHUNK, &tmQ, q_full, 64, r, g, batch, q0);
-      for (int j = 0; j < n_kv; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1u;
-        if (!mbar_wait(&kv_empty[s], ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_EMPTY)) break;
+      bool okp = true;
+      auto load_k = [&](int j) {
+        const int s = j % FA_KSTAGES;
+        const uint32_t ph = (j / FA_KSTAGES) & 1u;
+        if (!mbar_wait(&k_empty[s], ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_EMPTY)) { okp = false; return; }
         uint8_t* kd = smem + FaSmem::K_OFF + s * FA_TILE_BYTES;
-        uint8_t* vd = smem + FaSmem::V_OFF + s * FA_TILE_BYTES;
         mbar_expect_tx(&k_full[s], FA_TILE_BYTES);
         tma_load_4d(kd, &tmK, &k_full[s], 0, g, batch, j * FA_BN);
         tma_load_4d(kd + FA_CHUNK, &tmK, &k_full[s], 64, g, batch, j * FA_BN);
+      };
+      load_k(0);
+      // K runs one tile ahead of V: K(j+1) is requested before V(j)
+      for (int j = 0; j < n_kv && okp; ++j) {
+        if (j + 1 < n_kv) load_k(j + 1);
+        if (!okp) break;
+        const int s = j % FA_VSTAGES;
+        const uint32_t ph = (j / FA_VSTAGES) & 1u;
+        if (!mbar_wait(&v_empty[s], ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_EMPTY)) break;
+        uint8_t* vd = smem + FaSmem::V_OFF + s * FA_TILE_BYTES;
         mbar_expect_tx(&v_full[s], FA_TILE_BYTES);
         tma_load_4d(vd, &tmV, &v_full[s], 0, g, batch, j * FA_BN);
         tma_load_4d(vd + FA_CHUNK, &tmV, &v_full[s], 64, g, batch, j * FA_BN);
@@ -144,7 +161,8 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     bool ok = n_kv > 0;
     auto issue_s = [&](int j) {
       const int s = j & 1;
-      const uint32_t k_addr = smem_u32(smem + FaSmem::K_OFF + s * FA_TILE_BYTES);
+      const int ks = j % FA_KSTAGES;
+      const uint32_t k_addr = smem_u32(smem + FaSmem::K_OFF + ks * FA_TILE_BYTES);
       if (lane == 0) {
 #pragma unroll
         for (int k = 0; k < FA_D / 16; ++k) {
@@ -152,6 +170,7 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           umma_ss(tmem_s + s * FA_BN, make_smem_desc(q_addr + off, 16, 1024), make_smem_desc(k_addr + off, 16, 1024),
                   idesc_s, k > 0 ? 1u : 0u);
         }
+        umma_commit(&k_empty[ks]);
         umma_commit(&s_full[s]);
       }
       __syncwarp();
@@ -167,7 +186,8 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       if (j + 1 < n_kv) {
         const int s1 = (j + 1) & 1;
         const uint32_t ph1 = ((j + 1) >> 1) & 1u;
-        if (!mbar_wait(&k_full[s1], ph1, abort_flag, p.status, ST_TIMEOUT_FULL)) { ok = false; break; }
+        if (!mbar_wait(&k_full[(j + 1) % FA_KSTAGES], ((j + 1) / FA_KSTAGES) & 1u, abort_flag, p.status,
+                       ST_TIMEOUT_FULL)) { ok = false; break; }
         if (!mbar_wait(&s_empty[s1], ph1 ^ 1u, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
         tc_fence_after();
         issue_s(j + 1);
@@ -184,7 +204,7 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           umma_ss(tmem_o, make_smem_desc(p_addr + a_off, 16, 1024),
                   make_smem_desc(v_addr + k * 2048, FA_CHUNK, 1024), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
         }
-        umma_commit(&kv_empty[s]);
+        umma_commit(&v_empty[s]);
         umma_commit(pv_done);
       }
       __syncwarp();

@@ -28,7 +28,7 @@ constexpr int FA_CHUNK = 16384;
 
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
-  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
 
@@ -233,7 +233,9 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 
       const int key0 = j * FA_BN;
       const bool need_mask = (p.causal && key0 + FA_BN - 1 > qpos) || (key0 + FA_BN > p.skv);
-      float mx = -INFINITY;
+      // four independent running maxima / sums per thread: with one warp per scheduler there is
+      // nothing else to hide ALU latency, so the reductions must not be one serial chain
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
 #pragma unroll
@@ -244,9 +246,10 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             if ((p.causal && key > qpos) || key >= p.skv) x = -INFINITY;
           }
           v[c][i] = __float_as_uint(x);
-          mx = fmaxf(mx, x);
+          mx4[i & 3] = fmaxf(mx4[i & 3], x);
         }
       }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       float rescale = 1.f;
       bool do_rescale = false;
       if (mx > m_ref + 8.f) {       // also true on the first tile (m_ref = -inf)
@@ -257,16 +260,17 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         m_ref = mx;
       }
       const float mref = (m_ref == -INFINITY) ? 0.f : m_ref;
-      float psum = 0.f;
+      float ps4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           const float e = fast_exp2(__uint_as_float(v[c][i]) - mref);
-          psum += e;
+          ps4[i & 3] += e;
           v[c][i] = __float_as_uint(e);
         }
       }
+      const float psum = (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
       l_sum = l_sum * rescale + psum;
 
       // P buffer and O are free once the previous P·V has completed

@@ -1,0 +1,179 @@
+"""Composer arithmetic, Pareto filter, the time–cost solver and plan emission on synthetic profiles."""
+import json
+import math
+import random
+
+import pytest
+
+from kareus_b200.compose import (ExecutionOption, compare_frontiers, compose, dominates, frontier_from_plans,
+                                 generate_profile_csv, pareto_optimal, plan_pipeline, run_optimization, summarize_run)
+from kareus_b200.compose.composer import layers_per_stage
+from kareus_b200.compose.mincut import bounded_min_cut
+from kareus_b200.plan import (PipelineCommScheduler, parse_freqs_file, parse_schedule_file, sample_frontier,
+                              select_max_throughput)
+
+FREQS = [1500, 1350, 1200, 1050, 900]     # five clock levels
+
+
+def _points(base_t, base_e, rng):
+    """Synthetic partition profile: slower clock → longer, cheaper (dynamic) but static power adds up."""
+    out = {}
+    for f in FREQS:
+        pts = []
+        for sm in (6, 12, 18):
+            for slot in ("norm_0", "linear_0"):
+                t = base_t * (1500 / f) * (1 + 0.05 * (sm == 6) + 0.02 * rng.random())
+                e = base_e * (f / 1500) ** 2 * (1 + 0.03 * (sm == 18)) + 190.0 * t
+                pts.append(((slot, "none", sm, 1024), (t, e)))
+        out[f] = pts
+    return out
+
+
+def _prepost():
+    return {f: {k: (1e-3 * 1500 / f, 0.5) for k in ("forward-embedding", "forward-output", "loss-func",
+                                                   "backward-embedding", "backward-output")} for f in FREQS}
+
+
+def test_pareto_and_layers():
+    pts = [(("a",), (1.0, 300.0)), (("b",), (1.1, 295.0)), (("c",), (1.2, 400.0)), (("d",), (0.9, 500.0))]
+    keep = pareto_optimal(pts, p2p_power=100.0)
+    assert [c[0][0] for c in keep] == ["d", "a", "b"]
+    assert layers_per_stage(28, 2, 15, 13) == [15, 13]
+    assert layers_per_stage(28, 1) == [28]
+    assert sum(layers_per_stage(32, 4)) == 32
+
+
+def test_compose_arithmetic():
+    rng = random.Random(0)
+    maps = {"fwd_attn": _points(2e-3, 1.0, rng), "fwd_mlp": _points(3e-3, 1.5, rng),
+            "bwd_attn": _points(4e-3, 2.0, rng), "bwd_mlp": _points(6e-3, 3.0, rng)}
+    cands = compose(maps, _prepost(), [15, 13], p2p_power=190.0)
+    assert set(cands) == {0, 1}
+    # one hand-computed candidate at 1500 MHz: fastest attn + fastest mlp config
+    fa = min(maps["fwd_attn"][1500], key=lambda p: p[1][0])
+    fm = min(maps["fwd_mlp"][1500], key=lambda p: p[1][0])
+    want_t = (fa[1][0] + fm[1][0]) * 1.15 * 15 * 2 + 1e-3
+    fastest = min(cands[0]["forward"], key=lambda p: p[1][0])
+    assert fastest[0][0] == 1500
+    assert fastest[1][0] == pytest.approx(want_t, rel=1e-9)
+    # Pareto: sorted by time, effective energy strictly decreasing
+    for kind in ("forward", "backward"):
+        eff = [e - 190.0 * t for _, (t, e) in cands[1][kind]]
+        assert all(a > b for a, b in zip(eff, eff[1:]))
+    assert len(cands[0]["backward"][0][0]) == 5      # (freq, rec_attn, rec_mlp, attn, mlp)
+
+
+def test_bounded_min_cut_native_matches_python():
+    edges = [(0, 1, 1.0, 4.0), (0, 2, 0.0, 2.0), (1, 3, 0.5, 3.0), (2, 3, 0.0, 5.0), (1, 2, 0.0, 1e18)]
+    py = bounded_min_cut(4, edges, 0, 3, use_native=False)
+    assert py is not None and py[0] == 1 and py[3] == 0
+    try:
+        nat = bounded_min_cut(4, edges, 0, 3, use_native=True)
+    except RuntimeError:
+        pytest.skip("library not built")
+    def cut(side):
+        return sum(ub for u, v, lb, ub in edges if side[u] and not side[v]) - \
+            sum(lb for u, v, lb, ub in edges if side[v] and not side[u])
+    assert cut(nat) == pytest.approx(cut(py))
+    # infeasible lower bounds
+    assert bounded_min_cut(3, [(0, 1, 5.0, 6.0), (1, 2, 0.0, 1.0)], 0, 2, use_native=False) is None
+
+
+def _options(unit):
+    opts = {}
+    for s in range(2):
+        opts[s] = {}
+        for kind, base in (("forward", 0.020), ("backward", 0.045)):
+            lst = []
+            for f in FREQS:
+                t = base * (1500 / f) * (1.0 + 0.1 * s)
+                e = 40.0 * base * (f / 1500) ** 2
+                lst.append(ExecutionOption(t, unit, e, (f,)))
+            opts[s][kind] = lst
+    return opts
+
+
+def test_solver_walks_a_monotone_frontier():
+    unit = 1e-3
+    results = []
+    for res, stages in plan_pipeline(2, 4, _options(unit), unit, use_native=False):
+        results.append((res.quant_time, res.cost, res.cost_change,
+                        [[(i.kind, i.assigned_knob[0], i.duration) for i in st] for st in stages]))
+    assert len(results) > 20
+    times = [r[0] for r in results]
+    costs = [r[1] for r in results]
+    assert all(a - b == 1 for a, b in zip(times, times[1:])), "each iteration removes exactly one time unit"
+    assert all(b >= a - 1e-9 for a, b in zip(costs, costs[1:])), "energy grows as time shrinks"
+    assert all(c >= -1e-9 for c in (r[2] for r in results))
+    # ends at the all-fastest critical path: stage-0 warm-up F + 4x(F,B) chain at max clock
+    last = results[-1][3]
+    assert last[1][0][1] == 1500 and all(k in ("forward", "backward") for k, _, _ in last[0])
+    # marginal cost is non-decreasing (convex frontier)
+    ch = [r[2] for r in results]
+    assert ch[-1] >= ch[0] - 1e-9
+
+
+def test_driver_writes_compatible_plan_files(tmp_path):
+    rng = random.Random(1)
+    base = tmp_path / "bo" / "logs" / "llama3.2_3b" / "cp1-tp8-bs8-seq4096"
+    for part, (t, e) in {"fwd_attn": (2e-3, 1.0), "fwd_mlp": (3e-3, 1.5), "bwd_attn": (4e-3, 2.0),
+                         "bwd_mlp": (6e-3, 3.0)}.items():
+        d = base / part
+        d.mkdir(parents=True)
+        with (d / "eval_results.jsonl").open("w") as f:
+            for freq, pts in _points(t, e, rng).items():
+                for (s0, s1, sm, blk), (tt, ee) in pts:
+                    f.write(json.dumps({"freq": freq, "overlap_start": s0, "overlap_end": s1, "sm": sm, "block": blk,
+                                        "time_s": tt, "energy_j": ee}) + "\n")
+            f.write("not json\n")
+    for freq, d in _prepost().items():
+        nd = base / "nonpartition" / str(freq)
+        nd.mkdir(parents=True)
+        for key, fname in {"forward-embedding": "preprocess_energy.csv", "forward-output": "postprocess_energy.csv",
+                           "loss-func": "loss_energy.csv", "backward-embedding": "preprocess_backward_energy.csv",
+                           "backward-output": "postprocess_backward_energy.csv"}.items():
+            (nd / fname).write_text(f"time (s),total_energy (J),per_rank_energy (J)\n{d[key][0]},{d[key][1] * 8},{d[key][1]}\n")
+    csv_path = generate_profile_csv("llama3.2_3b", 8, 1, 2, 8, 4096, bayesian_profile_dir=str(tmp_path / "bo"),
+                                    output_dir=str(tmp_path), gpu_type="B200")
+    assert csv_path.read_text().splitlines()[0] == ("stage,instruction,frequency,recompute_attention_configs,"
+                                                    "recompute_mlp_configs,attention_configs,mlp_configs,time,energy")
+    out = tmp_path / "lowtime"
+    summary = run_optimization(csv_path, out, num_stages=2, num_mbs=8, gpu_type="B200", use_native=False,
+                               max_iterations=60)
+    assert len(summary) == 60
+    names = sorted(p.name for p in out.glob("freqs_pipeline_*.py"))
+    assert names[0] == "freqs_pipeline_00000.py" and len(names) == 60
+    best = select_max_throughput(names)
+    freqs = parse_freqs_file(out / best)
+    assert len(freqs) == 2 and len(freqs[0]) == 16 and freqs[0][0][0] == "forward"
+    sched = parse_schedule_file(out / best.replace("freqs", "scheds"), True, False)
+    s = PipelineCommScheduler.from_parsed(sched, 1, 8, use_activation_checkpointing=True)
+    s.on_instruction_begin("forward")
+    assert s.current_schedule.get("fwd_attn").block_size == 1024
+    trailer = (out / best).read_text().splitlines()[-1]
+    assert trailer.startswith(f"# Iteration {int(best[-8:-3])} total cost with P2P:")
+    kept = sample_frontier(names)
+    assert len(kept) == 10 and kept[-1] == names[-1]
+    fr = frontier_from_plans(out, 2, 190.0)
+    assert len(fr) == 60 and fr[0][0] > fr[-1][0]
+
+
+def test_compare_methods(tmp_path):
+    def write_run(d, t, e):
+        d.mkdir(parents=True)
+        for r in range(2):
+            rows = ["start_time,window_name,elapsed_time,gpu0_energy"]
+            for i in range(30):
+                rows.append(f"{i},training_step,{t + 1},{e + 5}")
+                rows.append(f"{i},training_step_fwd_bwd_step_call,{t + 0.01 * r},{e}")
+            (d / f"zeus_monitor_global_rank-{r}_local_rank-{r}.txt").write_text("\n".join(rows) + "\n")
+    write_run(tmp_path / "megatron", 5.0, 1000.0)
+    write_run(tmp_path / "kareus", 4.0, 900.0)
+    a, b = summarize_run(tmp_path / "megatron"), summarize_run(tmp_path / "kareus")
+    assert a["time_s"] == pytest.approx(5.01) and a["energy_j"] == pytest.approx(2000.0) and a["iterations"] == 20
+    assert b["time_s"] < a["time_s"]
+    ours = [(4.0, 2700.0), (5.0, 2300.0), (6.0, 2250.0)]
+    base = [(4.5, 2800.0), (5.5, 2400.0)]
+    assert dominates(ours, base)
+    cmp = compare_frontiers(ours, base)
+    assert cmp["iso_time_energy_reduction_pct"] > 0

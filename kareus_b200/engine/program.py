@@ -167,6 +167,7 @@ class PartitionProgram:
         self.steps = self._form_steps()
         self._last_use = self._compute_last_use()
         self.keep_ids: set = set(graph.final.values())
+        self.free_dead = True      # profilers re-run single steps and switch this off
 
     # ------------------------------------------------------------------ formation
     def _form_steps(self) -> List[Step]:
@@ -204,12 +205,18 @@ class PartitionProgram:
             grad_enabled: bool = True, release_saved: bool = True,
             default_shape: Tuple[Optional[int], Optional[int]] = (None, None)) -> None:
         """Execute all steps.  ``ctxs[i].store`` must already hold the graph's external tensors."""
+        self.run_steps(ctxs, self.steps, schedule, streams, grad_enabled, release_saved, default_shape)
+
+    def run_steps(self, ctxs: Sequence[NanoBatchContext], steps: Sequence[Step], schedule=None,
+                  streams: Optional[StreamSet] = None, grad_enabled: bool = True, release_saved: bool = True,
+                  default_shape: Tuple[Optional[int], Optional[int]] = (None, None)) -> None:
+        """Execute a contiguous run of steps (the whole program, or one step for a profiler)."""
         if len(ctxs) != self.n:
             raise ValueError(f"program was formed for {self.n} nanobatches, got {len(ctxs)} contexts")
         streams = streams or StreamSet(None)
         pending: List[Tuple[Node, int, object]] = []  # (comm node, nb, done event) not yet waited
 
-        for st in self.steps:
+        for st in steps:
             cfg = schedule.get(st.key) if schedule is not None else None
             if cfg is not None:
                 start = resolve_slot(st.slots, cfg.start) if st.compute else -1
@@ -266,6 +273,8 @@ class PartitionProgram:
         self._free_dead(node, store)
 
     def _free_dead(self, node: Node, store) -> None:
+        if not self.free_dead:
+            return
         for p in node.inputs:
             tid = p.tensor_id
             if self._last_use.get(tid) == node.index and tid not in self.keep_ids \

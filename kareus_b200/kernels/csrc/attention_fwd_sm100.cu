@@ -32,6 +32,12 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 struct FwdParams {
   __nv_bfloat16* out;   // [sq, b, hq, d] contiguous
   float* lse;           // [b, hq, sq]
@@ -42,7 +48,7 @@ struct FwdParams {
   int* status;
 };
 
-constexpr int FA_KSTAGES = 3;   // K tiles are released as soon as their S MMA retires
+constexpr int FA_KSTAGES = 2;   // K tiles are released as soon as their S MMA retires
 constexpr int FA_VSTAGES = 2;   // V tiles after their P·V MMA
 
 struct FaSmem {
@@ -50,7 +56,7 @@ struct FaSmem {
   static constexpr int K_OFF = Q_OFF + FA_TILE_BYTES;
   static constexpr int V_OFF = K_OFF + FA_KSTAGES * FA_TILE_BYTES;
   static constexpr int P_OFF = V_OFF + FA_VSTAGES * FA_TILE_BYTES;
-  static constexpr int BAR_OFF = P_OFF + FA_TILE_BYTES;
+  static constexpr int BAR_OFF = P_OFF + 2 * FA_TILE_BYTES;   // P is double buffered
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
 
@@ -61,15 +67,15 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FaSmem::BAR_OFF);
   uint64_t* q_full = bars + 0;
-  uint64_t* k_full = bars + 1;    // [3]
-  uint64_t* k_empty = bars + 4;   // [3]
+  uint64_t* k_full = bars + 1;    // [FA_KSTAGES]
+  uint64_t* k_empty = bars + 4;   // [FA_KSTAGES]
   uint64_t* v_full = bars + 7;    // [2]
   uint64_t* v_empty = bars + 9;   // [2]
   uint64_t* s_full = bars + 11;   // [2]
   uint64_t* s_empty = bars + 13;  // [2]
-  uint64_t* p_full = bars + 15;
-  uint64_t* pv_done = bars + 16;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
+  uint64_t* p_full = bars + 15;   // [2]
+  uint64_t* pv_done = bars + 17;  // [2]  P·V of the tile that used P buffer b has retired
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -102,8 +108,10 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       mbar_init(&s_full[i], 1);
       mbar_init(&s_empty[i], 4);
     }
-    mbar_init(p_full, 4);
-    mbar_init(pv_done, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&p_full[i], 4);
+      mbar_init(&pv_done[i], 1);
+    }
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -192,7 +200,7 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         tc_fence_after();
         issue_s(j + 1);
       }
-      if (!mbar_wait(p_full, j & 1u, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      if (!mbar_wait(&p_full[s], (j >> 1) & 1u, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       if (!mbar_wait(&v_full[s], (j >> 1) & 1u, abort_flag, p.status, ST_TIMEOUT_FULL)) { ok = false; break; }
       tc_fence_after();
       if (lane == 0) {
@@ -201,55 +209,57 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         for (int k = 0; k < FA_BN / 16; ++k) {
           // A = P [128 rows][128 keys] K-major: two 64-key chunks; B = V [keys][d] MN-major
           const uint32_t a_off = (k >> 2) * FA_CHUNK + (k & 3) * 32;
-          umma_ss(tmem_o, make_smem_desc(p_addr + a_off, 16, 1024),
+          umma_ss(tmem_o, make_smem_desc(p_addr + s * FA_TILE_BYTES + a_off, 16, 1024),
                   make_smem_desc(v_addr + k * 2048, FA_CHUNK, 1024), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
         }
         umma_commit(&v_empty[s]);
-        umma_commit(pv_done);
+        umma_commit(&pv_done[s]);
       }
       __syncwarp();
     }
   } else {
     // ------------------------------------------------------------------ softmax + epilogue
+    // Two passes over the S row straight out of tensor memory (max, then exp/sum/pack), 32 columns
+    // at a time with rolled outer loops: the code stays small enough for the instruction cache and
+    // needs few registers; packed f32x2 FMA/ADD halve the ALU work next to the exponentials.
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;           // row inside the tile = TMEM lane
     const int qpos = p.q_offset + q0 + row;        // absolute position of this query
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-    float m_ref = -INFINITY;   // reference maximum (log2 domain) used for the exponentials
+    float m_ref = -INFINITY;   // reference maximum (scaled, log2 domain) used for the exponentials
     float l_sum = 0.f;
     bool ok = n_kv > 0;
-    uint8_t* p_row = smem + FaSmem::P_OFF + row * 128;
     for (int j = 0; j < n_kv && ok; ++j) {
       const int s = j & 1;
       if (!mbar_wait(&s_full[s], (j >> 1) & 1u, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
-      uint32_t v[4][32];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld_32x32(tmem_s + s * FA_BN + lane_addr + c * 32, v[c]);
-      tmem_ld_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_empty[s]);
-
       const int key0 = j * FA_BN;
-      const bool need_mask = (p.causal && key0 + FA_BN - 1 > qpos) || (key0 + FA_BN > p.skv);
-      // four independent running maxima / sums per thread: with one warp per scheduler there is
-      // nothing else to hide ALU latency, so the reductions must not be one serial chain
+      // warp-uniform: does any row of this tile need masking?
+      const bool tile_mask = (p.causal && key0 + FA_BN - 1 > p.q_offset + q0) || (key0 + FA_BN > p.skv);
+      const uint32_t s_addr = tmem_s + s * FA_BN + lane_addr;
+      // ---- pass 1: row maximum of the raw scores
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
+#pragma unroll 1
       for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(s_addr + c * 32, v);
+        tmem_ld_wait();
+        if (tile_mask) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float x = __uint_as_float(v[c][i]) * p.scale_log2;
-          if (need_mask) {
+          for (int i = 0; i < 32; ++i) {
             const int key = key0 + c * 32 + i;
-            if ((p.causal && key > qpos) || key >= p.skv) x = -INFINITY;
+            if ((p.causal && key > qpos) || key >= p.skv) v[i] = 0xff800000u;   // -inf
           }
-          v[c][i] = __float_as_uint(x);
-          mx4[i & 3] = fmaxf(mx4[i & 3], x);
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+          mx4[0] = fmax3(mx4[0], __uint_as_float(v[i + 0]), __uint_as_float(v[i + 1]));
+          mx4[1] = fmax3(mx4[1], __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+          mx4[2] = fmax3(mx4[2], __uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
+          mx4[3] = fmax3(mx4[3], __uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
         }
       }
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
       float rescale = 1.f;
       bool do_rescale = false;
       if (mx > m_ref + 8.f) {       // also true on the first tile (m_ref = -inf)
@@ -260,27 +270,14 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         m_ref = mx;
       }
       const float mref = (m_ref == -INFINITY) ? 0.f : m_ref;
-      float ps4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float e = fast_exp2(__uint_as_float(v[c][i]) - mref);
-          ps4[i & 3] += e;
-          v[c][i] = __float_as_uint(e);
+      // O may only be touched once the previous P·V has retired (rare path: the running maximum
+      // moved by more than 2^8); the decision is made warp-uniform for the .aligned TMEM accesses
+      if (__any_sync(0xffffffffu, do_rescale)) {
+        if (!mbar_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1u, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) {
+          ok = false;
+          break;
         }
-      }
-      const float psum = (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
-      l_sum = l_sum * rescale + psum;
-
-      // P buffer and O are free once the previous P·V has completed
-      if (j > 0) {
-        if (!mbar_wait(pv_done, (j - 1) & 1u, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
         tc_fence_after();
-      }
-      // warp-uniform decision so the .aligned TMEM accesses stay converged
-      const bool any_rescale = __any_sync(0xffffffffu, do_rescale);
-      if (any_rescale) {
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
           uint32_t o[32];
@@ -292,29 +289,60 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         }
         tmem_st_wait();
       }
-      // P (bf16) into the K-major, 128B-swizzled operand layout: 16-byte unit u of row r goes to
-      // unit (u ^ (r & 7)) of that row inside its 64-key chunk
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          uint4 w;
-          w.x = pack_bf16x2(__uint_as_float(v[c][8 * u + 0]), __uint_as_float(v[c][8 * u + 1]));
-          w.y = pack_bf16x2(__uint_as_float(v[c][8 * u + 2]), __uint_as_float(v[c][8 * u + 3]));
-          w.z = pack_bf16x2(__uint_as_float(v[c][8 * u + 4]), __uint_as_float(v[c][8 * u + 5]));
-          w.w = pack_bf16x2(__uint_as_float(v[c][8 * u + 6]), __uint_as_float(v[c][8 * u + 7]));
-          const int unit = (c & 1) * 4 + u;              // 16-byte unit inside the 64-key chunk
-          uint8_t* dst = p_row + (c >> 1) * FA_CHUNK + ((unit ^ (row & 7)) << 4);
-          *reinterpret_cast<uint4*>(dst) = w;
+      // the P buffer of this parity was last read by the P·V of tile j-2
+      if (j >= 2) {
+        if (!mbar_wait(&pv_done[s], ((j >> 1) & 1u) ^ 1u, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) {
+          ok = false;
+          break;
         }
       }
-      fence_proxy_async_smem();
+      // ---- pass 2: P = exp2(S·scale − m), row sum, bf16 pack into the swizzled operand layout
+      // (16-byte unit u of row r goes to unit (u ^ (r & 7)) of that row inside its 64-key chunk)
+      uint8_t* p_row = smem + FaSmem::P_OFF + s * FA_TILE_BYTES + row * 128;
+      const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
+      const float2 nm2 = make_float2(-mref, -mref);
+      float2 ps2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(s_addr + c * 32, v);
+        tmem_ld_wait();
+        if (tile_mask) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int key = key0 + c * 32 + i;
+            if ((p.causal && key > qpos) || key >= p.skv) v[i] = 0xff800000u;
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          uint32_t w[4];
+#pragma unroll
+          for (int h2 = 0; h2 < 4; ++h2) {
+            const int i = 8 * u + 2 * h2;
+            float2 x = __ffma2_rn(make_float2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])), sc2, nm2);
+            x.x = fast_exp2(x.x);
+            x.y = fast_exp2(x.y);
+            ps2[h2 & 1] = __fadd2_rn(ps2[h2 & 1], x);
+            w[h2] = pack_bf16x2(x.x, x.y);
+          }
+          const int unit = (c & 1) * 4 + u;              // 16-byte unit inside the 64-key chunk
+          uint8_t* dst = p_row + (c >> 1) * FA_CHUNK + ((unit ^ (row & 7)) << 4);
+          *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+      l_sum = l_sum * rescale + (ps2[0].x + ps2[0].y) + (ps2[1].x + ps2[1].y);
       tc_fence_before();
+      fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
+      if (lane == 0) {
+        mbar_arrive(&s_empty[s]);
+        mbar_arrive(&p_full[s]);
+      }
     }
     // ---- epilogue: O / l → global, LSE
-    if (ok && n_kv > 0) ok = mbar_wait(pv_done, (n_kv - 1) & 1u, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
+    if (ok && n_kv > 0)
+      ok = mbar_wait(&pv_done[(n_kv - 1) & 1], ((n_kv - 1) >> 1) & 1u, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
     if (n_kv > 0) {
       tc_fence_after();
       const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;

@@ -1,0 +1,51 @@
+"""Single-partition executor and the hardware evaluator on CPU with a simulated NVML."""
+import pytest
+import torch
+
+from kareus_b200.config import ParallelConfig, get_model_config
+from kareus_b200.energy import EnergyMonitor, FakeNVML, FrequencyController
+from kareus_b200.profile.hardware import HardwareEvaluator
+from kareus_b200.profile.nonpartition import build_cases, profile_nonpartition
+from kareus_b200.profile.partition_executor import PartitionExecutor
+from kareus_b200.profile.space import Config
+
+
+@pytest.mark.parametrize("key", ["fwd_trail", "bwd_trail"])
+def test_executor_runs_one_partition_repeatedly(key):
+    cfg = get_model_config("tiny")
+    ex = PartitionExecutor(cfg, ParallelConfig(num_nanobatches=2, recompute=False), key, 4, 32, dtype="fp32")
+    assert "norm_0" in ex.slots() and "linear_0" in ex.slots()
+    for _ in range(3):
+        ex.execute(("linear_0", "none"), (8, 1024))
+    with pytest.raises(KeyError):
+        PartitionExecutor(cfg, ParallelConfig(num_nanobatches=2), "fwd_attn", 4, 32, dtype="fp32")  # needs tp > 1
+
+
+def test_evaluator_and_nonpartition(tmp_path):
+    class Clock:
+        t = 0.0
+        def __call__(self): return self.t
+    clk = Clock()
+    nv = FakeNVML(n=1, time_fn=clk)
+    mon = EnergyMonitor([0], nvml=nv, sync_fn=lambda i: None, time_fn=clk)
+    ctl = FrequencyController(0, "locked", nvml=nv)
+
+    class Ex:
+        def execute(self, ow, shape):
+            clk.t += 0.01 * 1965 / (nv.sm_clock(0))
+
+    ev = HardwareEvaluator(lambda nano: Ex(), mon, ctl, measurement_duration=0.2, cooldown_duration=0.0, settle_s=0.0,
+                           sleep_fn=lambda s: None)
+    res = ev([Config(1965, 6, ("norm_0", "none")), Config(1200, 6, ("norm_0", "none"))])
+    ev.close()
+    assert res[1][0] > res[0][0] and res[1][1] < res[0][1]       # slower and cheaper at the lower clock
+    assert ev.samples[1]["sm_clock"] == 1200 and nv.calls[-1] == ("reset", 0)
+
+    from kareus_b200.models.llama import GPTModel
+    model = GPTModel(get_model_config("tiny"), ParallelConfig(), dtype="fp32")
+    cases = build_cases(model, 4, 32, "cpu")
+    wrapped = {k: (lambda f=f: (f(), setattr(clk, "t", clk.t + 0.001))[0]) for k, f in cases.items()}
+    profile_nonpartition(wrapped, [1500, 1200], tmp_path, mon, measurement_duration=0.01, cooldown_duration=0.0,
+                         sleep_fn=lambda s: None)
+    txt = (tmp_path / "nonpartition" / "1500" / "loss_energy.csv").read_text().splitlines()
+    assert txt[0] == "time (s),total_energy (J),per_rank_energy (J)" and len(txt[1].split(",")) == 3

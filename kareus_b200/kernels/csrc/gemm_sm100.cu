@@ -31,10 +31,23 @@ struct GemmSmem {
   static constexpr int TOTAL = TILE_BYTES + BAR_BYTES + 1024;  // + alignment slack
 };
 
+// Tile rasterisation: m-tiles are taken in groups of `group_m`; inside a group the m index runs
+// fastest.  The 148 tiles in flight then cover a near-square patch of C whose A and B panels fit in
+// L2 together, instead of streaming the whole of A once per wave.
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int group_m, int& tm, int& tn) {
+  const int per_group = group_m * tiles_n;
+  const int g = t / per_group;
+  const int first_m = g * group_m;
+  const int gsz = min(group_m, tiles_m - first_m);
+  const int r = t - g * per_group;
+  tm = first_m + r % gsz;
+  tn = r / gsz;
+}
+
 template <int BN, bool A_MN, bool B_MN, bool OUT_F32, bool ACCUM>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 void* __restrict__ Cout, int M, int N, int K, int ldc, int* status) {
+                 void* __restrict__ Cout, int M, int N, int K, int ldc, int group_m, int* status) {
   using S = GemmSmem<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -79,8 +92,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t it = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        const int m0 = (t % tiles_m) * GEMM_BM;
-        const int n0 = (t / tiles_m) * BN;
+        int tm, tn;
+        tile_coords(t, tiles_m, tiles_n, group_m, tm, tn);
+        const int m0 = tm * GEMM_BM;
+        const int n0 = tn * BN;
         for (int kb_ = 0; kb_ < nk; ++kb_, ++it) {
           const int s = it % GEMM_STAGES;
           const uint32_t ph = (it / GEMM_STAGES) & 1u;
@@ -151,8 +166,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_i) {
       const uint32_t buf = tile_i & 1u;
       const uint32_t bph = (tile_i >> 1) & 1u;
-      const int m0 = (t % tiles_m) * GEMM_BM;
-      const int n0 = (t / tiles_m) * BN;
+      int tm, tn;
+      tile_coords(t, tiles_m, tiles_n, group_m, tm, tn);
+      const int m0 = tm * GEMM_BM;
+      const int n0 = tn * BN;
       if (!mbar_wait(&tfull[buf], bph, abort_flag, status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
@@ -241,7 +258,13 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
   const int tiles = ((M + GEMM_BM - 1) / GEMM_BM) * ((N + BN - 1) / BN);
   int grid = tiles < num_sms ? tiles : num_sms;
   if (grid < 1) grid = 1;
-  kern<<<grid, GEMM_THREADS, smem, stream>>>(tmA, tmB, C, M, N, K, ldc, status);
+  // m-tiles per group: keep the group's A panel near 40 MB so A and B panels share the 126 MB L2
+  int tiles_m = (M + GEMM_BM - 1) / GEMM_BM;
+  long panel = (long)GEMM_BM * K * 2;
+  int group_m = (int)((40L << 20) / (panel > 0 ? panel : 1));
+  if (group_m < 4) group_m = 4;
+  if (group_m > tiles_m) group_m = tiles_m;
+  kern<<<grid, GEMM_THREADS, smem, stream>>>(tmA, tmB, C, M, N, K, ldc, group_m, status);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 2000 + static_cast<int>(e);
 }

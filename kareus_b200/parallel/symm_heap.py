@@ -1,0 +1,204 @@
+"""Symmetric heap: one device allocation per rank, mapped into every peer of the group.
+
+Every buffer carved out of the heap has the same byte offset on every rank, so a kernel can reach
+rank ``p``'s copy of a buffer as ``base[p] + offset`` with plain loads and stores over NVLink.
+This replaces the reference's registered-memory exchange and memory channels
+(``kareus/msccl/msccl_comm.py:44-206``; ``3rdparty/mscclpp/src/registered_memory.cc``): handles
+are CUDA IPC handles exchanged with ``torch.distributed.all_gather_object``.
+
+Layout: ``[flag region | data region]``.  Each *channel* (one per collective call site and
+nanobatch) owns a block of 64-bit flag slots and its data buffers; buffers are allocated once
+(bump allocator, identical call order on all ranks) and reused, which is what gives every
+nanobatch its own staging memory.  Tokens written into flag slots grow monotonically with the
+channel's call count, so nothing is ever reset.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_int, c_long, c_size_t, c_uint64, c_void_p
+from typing import Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..kernels import cuda as KC
+
+MAX_PEERS = 8
+MAX_SIGNAL_CTAS = 64
+FLAG_BLOCK = MAX_PEERS * MAX_SIGNAL_CTAS * 8          # bytes of one channel's barrier flags
+FLAG_REGION = 4 << 20
+
+
+class _Raw:
+    """Exposes a raw device pointer through ``__cuda_array_interface__``."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3,
+                                         "strides": None}
+
+
+class Channel:
+    def __init__(self, index: int, flag_off: int):
+        self.index, self.flag_off = index, flag_off
+        self.epoch = 0
+        self.buffers: Dict[str, Tuple[int, int]] = {}     # name -> (offset, nbytes)
+
+
+class SymmetricHeap:
+    def __init__(self, group, rank: int, world: int, device, size_bytes: int):
+        self.group, self.rank, self.world = group, rank, world
+        self.device = torch.device(device)
+        self.size = int(size_bytes)
+        self.lib = KC.lib()
+        self._declare()
+        ptr = c_void_p()
+        KC._check(self.lib.kb_heap_alloc(c_size_t(self.size), ctypes.byref(ptr)), "heap alloc")
+        self.local_ptr = ptr.value
+        handle = (ctypes.c_ubyte * 64)()
+        KC._check(self.lib.kb_ipc_get_handle(c_void_p(self.local_ptr), handle), "ipc handle")
+        handles: List[Optional[bytes]] = [None] * world
+        if world > 1:
+            dist.all_gather_object(handles, bytes(handle), group=group)
+        else:
+            handles = [bytes(handle)]
+        self.bases: List[int] = []
+        for r, h in enumerate(handles):
+            if r == rank:
+                self.bases.append(self.local_ptr)
+                continue
+            buf = (ctypes.c_ubyte * 64).from_buffer_copy(h)
+            p = c_void_p()
+            KC._check(self.lib.kb_ipc_open(buf, ctypes.byref(p)), f"ipc open rank {r}")
+            self.bases.append(p.value)
+        self._bases_arr = (c_void_p * MAX_PEERS)(*(self.bases + [None] * (MAX_PEERS - world)))
+        self.local = torch.as_tensor(_Raw(self.local_ptr, self.size), device=self.device)
+        self._flag_top = 0
+        self._data_top = FLAG_REGION
+        self.channels: Dict[str, Channel] = {}
+        self.closed = False
+        if world > 1:
+            dist.barrier(group=group)
+
+    @classmethod
+    def create(cls, group, device, size_bytes: int = 6 << 30) -> "SymmetricHeap":
+        rank = dist.get_rank(group) if dist.is_initialized() else 0
+        world = dist.get_world_size(group) if dist.is_initialized() else 1
+        if world > MAX_PEERS:
+            raise ValueError(f"at most {MAX_PEERS} ranks per heap")
+        return cls(group, rank, world, device, size_bytes)
+
+    def _declare(self) -> None:
+        L = self.lib
+        P, I, LNG, U64 = c_void_p, c_int, c_long, c_uint64
+        L.kb_heap_alloc.argtypes = [c_size_t, ctypes.POINTER(c_void_p)]
+        L.kb_ipc_get_handle.argtypes = [P, P]
+        L.kb_ipc_open.argtypes = [P, ctypes.POINTER(c_void_p)]
+        L.kb_ipc_close.argtypes = [P]
+        L.kb_heap_free.argtypes = [P]
+        L.kb_allreduce.argtypes = [P, I, I, U64, U64, LNG, U64, I, I, P, P]
+        L.kb_allgather.argtypes = [P, I, I, U64, U64, LNG, U64, I, I, P, P]
+        L.kb_reducescatter.argtypes = [P, I, I, U64, U64, LNG, P, U64, I, I, P, P]
+        L.kb_wait_flag.argtypes = [P, U64, U64, P, P]
+        for n in ("kb_heap_alloc", "kb_ipc_get_handle", "kb_ipc_open", "kb_ipc_close", "kb_heap_free", "kb_allreduce",
+                  "kb_allgather", "kb_reducescatter", "kb_wait_flag"):
+            getattr(L, n).restype = c_int
+
+    # ------------------------------------------------------------------ allocation
+    def channel(self, name: str, flag_bytes: int = FLAG_BLOCK) -> Channel:
+        ch = self.channels.get(name)
+        if ch is None:
+            need = (flag_bytes + 255) // 256 * 256
+            if self._flag_top + need > FLAG_REGION:
+                raise MemoryError("symmetric heap: flag region exhausted")
+            ch = Channel(len(self.channels), self._flag_top)
+            self._flag_top += need
+            self.channels[name] = ch
+        return ch
+
+    def buffer(self, ch: Channel, name: str, nbytes: int) -> Tuple[int, torch.Tensor]:
+        """Persistent buffer of a channel: ``(byte offset, uint8 view)``.  Grows by reallocation at the
+        top of the heap if a later call needs more (all ranks make the same calls)."""
+        cur = ch.buffers.get(name)
+        if cur is None or cur[1] < nbytes:
+            off = (self._data_top + 1023) // 1024 * 1024
+            if off + nbytes > self.size:
+                raise MemoryError(f"symmetric heap of {self.size >> 20} MiB is full (asked {nbytes >> 20} MiB for {name})")
+            self._data_top = off + nbytes
+            ch.buffers[name] = (off, nbytes)
+            cur = (off, nbytes)
+        return cur[0], self.local[cur[0]:cur[0] + nbytes]
+
+    def view(self, off: int, shape, dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= s
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        return self.local[off:off + nbytes].view(dtype).view(shape)
+
+    # ------------------------------------------------------------------ collectives
+    def _launch_shape(self, sm_num, block_size):
+        return int(sm_num or 16), int(block_size or 1024)
+
+    def all_reduce(self, x: torch.Tensor, nb: int = 0, sm_num=None, block_size=None, tag: str = "ar") -> torch.Tensor:
+        ch = self.channel(f"{tag}/{nb}")
+        n = x.numel()
+        off, _ = self.buffer(ch, "x", n * 2)
+        buf = self.view(off, x.shape, x.dtype)
+        if x.data_ptr() != buf.data_ptr():
+            buf.copy_(x)
+        ch.epoch += 1
+        sm, blk = self._launch_shape(sm_num, block_size)
+        st = KC.status_word(self.device)
+        KC._check(self.lib.kb_allreduce(self._bases_arr, self.rank, self.world, ch.flag_off, off, n, ch.epoch, sm, blk,
+                                        st.data_ptr(), KC._stream()), "allreduce")
+        KC._count()
+        return buf
+
+    def all_gather(self, x: torch.Tensor, nb: int = 0, sm_num=None, block_size=None, tag: str = "ag") -> torch.Tensor:
+        ch = self.channel(f"{tag}/{nb}")
+        shard = x.numel() * x.element_size()
+        off, _ = self.buffer(ch, "x", shard * self.world)
+        out = self.view(off, (x.shape[0] * self.world,) + tuple(x.shape[1:]), x.dtype)
+        out[self.rank * x.shape[0]:(self.rank + 1) * x.shape[0]].copy_(x)
+        ch.epoch += 1
+        sm, blk = self._launch_shape(sm_num, block_size)
+        st = KC.status_word(self.device)
+        KC._check(self.lib.kb_allgather(self._bases_arr, self.rank, self.world, ch.flag_off, off, shard, ch.epoch, sm,
+                                        blk, st.data_ptr(), KC._stream()), "allgather")
+        KC._count()
+        return out
+
+    def reduce_scatter(self, x: torch.Tensor, nb: int = 0, sm_num=None, block_size=None, tag: str = "rs") -> torch.Tensor:
+        ch = self.channel(f"{tag}/{nb}")
+        n = x.numel()
+        off, _ = self.buffer(ch, "x", n * 2)
+        buf = self.view(off, x.shape, x.dtype)
+        if x.data_ptr() != buf.data_ptr():
+            buf.copy_(x)
+        out = torch.empty((x.shape[0] // self.world,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        ch.epoch += 1
+        sm, blk = self._launch_shape(sm_num, block_size)
+        st = KC.status_word(self.device)
+        KC._check(self.lib.kb_reducescatter(self._bases_arr, self.rank, self.world, ch.flag_off, off, n // self.world,
+                                            out.data_ptr(), ch.epoch, sm, blk, st.data_ptr(), KC._stream()),
+                  "reducescatter")
+        KC._count()
+        return out
+
+    def wait_flag_probe(self, limit_ns: int = 200_000_000) -> None:
+        """Launch a kernel that waits (bounded) on a flag nobody sets; the status word then holds the
+        peer-timeout code.  Used to test the bounded-wait path without any peer."""
+        ch = self.channel("__probe__")
+        st = KC.status_word(self.device)
+        slot = self.local_ptr + ch.flag_off
+        KC._check(self.lib.kb_wait_flag(c_void_p(slot), 1 << 62, limit_ns, st.data_ptr(), KC._stream()), "wait_flag")
+
+    def close(self) -> None:
+        if self.closed:
+            return
+        self.closed = True
+        torch.cuda.synchronize(self.device)
+        for r, b in enumerate(self.bases):
+            if r != self.rank:
+                self.lib.kb_ipc_close(c_void_p(b))
+        self.lib.kb_heap_free(c_void_p(self.local_ptr))

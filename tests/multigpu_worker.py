@@ -1,0 +1,110 @@
+"""Worker of the multi-GPU tests; launched with torch.distributed.run, one rank per GPU."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def rel(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+
+def test_heap_collectives(heap, rank, world, dev):
+    g = torch.Generator(device=dev).manual_seed(100 + rank)
+    for shape in [(1024, 2, 512), (4096, 1, 3072), (333, 1, 8)]:
+        x = torch.randn(shape, device=dev, generator=g).bfloat16()
+        want = x.clone()
+        dist.all_reduce(want)
+        got = heap.all_reduce(x.clone(), nb=0, sm_num=8, block_size=512, tag=f"t_ar{shape[0]}")
+        torch.cuda.synchronize()
+        assert rel(got, want) < 2e-2, ("all_reduce", shape, rel(got, want))
+        wg = torch.empty((shape[0] * world,) + shape[1:], device=dev, dtype=torch.bfloat16)
+        dist.all_gather_into_tensor(wg, x)
+        gg = heap.all_gather(x, nb=1, sm_num=4, block_size=1024, tag=f"t_ag{shape[0]}")
+        torch.cuda.synchronize()
+        assert torch.equal(gg, wg), ("all_gather", shape)
+        if shape[0] % world == 0:
+            ws = torch.empty((shape[0] // world,) + shape[1:], device=dev, dtype=torch.bfloat16)
+            dist.reduce_scatter_tensor(ws, x.clone())
+            gs = heap.reduce_scatter(x, nb=0, sm_num=6, block_size=1024, tag=f"t_rs{shape[0]}")
+            torch.cuda.synchronize()
+            assert rel(gs, ws) < 2e-2, ("reduce_scatter", shape, rel(gs, ws))
+    # repeated calls reuse buffers and flags (epochs grow)
+    x = torch.ones(2048, 8, device=dev).bfloat16()
+    for i in range(5):
+        y = heap.all_reduce(x.clone(), nb=0, sm_num=3, tag="rep")
+    torch.cuda.synchronize()
+    assert torch.all(y == world)
+
+
+def test_bounded_wait(heap, dev):
+    from kareus_b200.kernels import cuda as KC
+    heap.wait_flag_probe(limit_ns=100_000_000)
+    torch.cuda.synchronize()
+    try:
+        KC.check_status()
+        raise AssertionError("expected a peer-timeout status")
+    except KC.KernelError as e:
+        assert "peer" in str(e)
+    assert torch.ones(3, device=dev).sum().item() == 3      # context still usable
+
+
+def test_model_modes(heap, rank, world, dev):
+    from kareus_b200.config import ParallelConfig, TrainConfig, get_model_config
+    from kareus_b200.parallel.mesh import Mesh
+    from kareus_b200.train.trainer import Trainer, synthetic_batch
+    from kareus_b200.kernels import cuda as KC
+    cfg = get_model_config("tiny128").replace(num_attention_heads=8, num_query_groups=4)
+    tc = TrainConfig(micro_batch_size=4, global_batch_size=8, seq_len=512, warmup_steps=0, lr=1e-3)
+    mesh = Mesh(tp=world)
+    losses = {}
+    for tp_comm, backend in [("allreduce", "nccl"), ("allreduce", "kernel"), ("sp", "nccl"), ("sp", "kernel"),
+                             ("sp_fused", "kernel")]:
+        par = ParallelConfig(tp=world, num_nanobatches=2, tp_comm=tp_comm, comm_backend=backend, recompute=True)
+        try:
+            tr = Trainer(cfg, par, tc, mesh=mesh, device=dev, heap=heap)
+        except NotImplementedError:
+            continue
+        tr.model.decoder.engine.default_shape = (8, 1024)
+        batch = synthetic_batch(cfg, tc, tr.num_microbatches, seed=7)
+        l = [tr.train_step(batch) for _ in range(3)]
+        torch.cuda.synchronize()
+        KC.check_status()
+        losses[(tp_comm, backend)] = l
+        del tr
+    base = losses[("allreduce", "nccl")]
+    if rank == 0:
+        print("losses:", {k: [round(x, 4) for x in v] for k, v in losses.items()}, flush=True)
+    assert base[-1] < base[0]
+    for k, v in losses.items():
+        for a, b in zip(v, base):
+            assert abs(a - b) < 0.05, (k, v, base)
+
+
+def main():
+    from kareus_b200.parallel.mesh import init_distributed
+    from kareus_b200.parallel.symm_heap import SymmetricHeap
+    rank, world, local = init_distributed()
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    which = sys.argv[1] if len(sys.argv) > 1 else "all"
+    heap = SymmetricHeap.create(dist.group.WORLD, dev, size_bytes=1 << 30)
+    if which in ("all", "collectives"):
+        test_heap_collectives(heap, rank, world, dev)
+    if which in ("all", "wait"):
+        test_bounded_wait(heap, dev)
+    if which in ("all", "model"):
+        test_model_modes(heap, rank, world, dev)
+    dist.barrier()
+    torch.cuda.synchronize()
+    if rank == 0:
+        print(f"multigpu worker ok ({which}, world {world})", flush=True)
+    heap.close()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

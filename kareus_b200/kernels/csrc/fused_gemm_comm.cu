@@ -1,0 +1,495 @@
+// Tensor-parallel GEMMs fused with their sequence-parallel collective (sm_100a, bf16):
+//
+//   ag_gemm:  Y[M,N] = AllGather_rows(X_shard)[M,K] · W[N,K]ᵀ      (QKV, FC1 forward)
+//   gemm_rs:  Y_shard[M/tp,N] = ReduceScatter_rows(A[M,K] · W[N,K]ᵀ) (out-proj, FC2 forward)
+//
+// One kernel does the math and moves the collective's bytes over NVLink, tile by tile:
+//
+// * ag_gemm — CTAs 0..n_comm-1 are copy drivers: one thread per CTA streams the peers' shards with
+//   bulk asynchronous copies (peer global → shared-memory ring → local gathered buffer) and, after
+//   every 128-row tile, publishes a per-tile flag.  The remaining CTAs run the tcgen05 GEMM; they
+//   visit row tiles in arrival order (own shard first, then rank+1, rank+2, …) and the TMA producer
+//   waits for a tile's flag only if the tile is remote.  No tile crosses NVLink more than once, no
+//   TMA multicast is used, and the gathered activations stay in the buffer for the wgrad GEMM.
+// * gemm_rs — the GEMM CTAs visit row tiles in owner order (rank+1 first, own rows last); the
+//   epilogue stores each bf16 tile straight into the owner's staging slot through its peer pointer
+//   and bumps a per-tile counter there; extra reducer CTAs on the owner wait for the counters of a
+//   tile from all ranks, sum the partial tiles in fp32 and write the sequence shard.
+//
+// `n_comm` (copy drivers / reducer CTAs) is the plan's "SMs given to the collective" knob.  Every
+// wait is bounded (status word + return).  Role of the reference's separate cuBLASLt GEMM followed
+// or preceded by an all-reduce kernel (kareus/megatron/core/extensions/ops/te_linear.py:303-445,
+// 3rdparty/mscclpp/python/mscclpp_benchmark/allreduce.cu:155-246).
+#include "sm100.cuh"
+#include "peer.cuh"
+#include "host_utils.h"
+
+namespace kb {
+
+constexpr int FG_BM = 128;
+constexpr int FG_BK = 64;
+constexpr int FG_STAGES = 4;
+constexpr int FG_THREADS = 192;
+constexpr int FG_CHUNK = 32768;      // bytes per bulk copy of a copy driver
+constexpr int FG_SLOTS = 6;          // copy ring depth (6 x 32 KB)
+
+enum { MODE_AG = 1, MODE_RS = 2 };
+
+struct FusedParams {
+  PeerCtx peer;
+  int mode;
+  int n_first;            // AG: copy-driver CTAs in front of the GEMM CTAs
+  int n_gemm;             // GEMM CTAs
+  int n_last;             // RS: reducer CTAs behind the GEMM CTAs
+  int rows_per_rank;      // Ms
+  uint32_t epoch;
+  // AG
+  uint64_t xg_off;        // gathered buffer [M, K] in every heap
+  uint32_t* ready;        // local flags, one per 128-row tile of the gathered buffer
+  // RS
+  uint64_t stage_off;     // staging [world][Ms][N] in every heap
+  uint64_t cnt_off;       // counters [world][Ms/128][tiles_n] (uint32) in every heap
+  uint32_t* go;           // local flag: peers have entered this call
+  __nv_bfloat16* out;     // [Ms, N]
+};
+
+template <int BN>
+struct FgSmem {
+  static constexpr int A_BYTES = FG_BM * FG_BK * 2;
+  static constexpr int B_BYTES = BN * FG_BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int TILE_BYTES = STAGE_BYTES * FG_STAGES;
+  static constexpr int TOTAL = TILE_BYTES + 256 + 1024;
+};
+
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void bulk_s2g(void* dst, const void* src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(smem_u32(src)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+// ----------------------------------------------------------------------------- copy driver (AG)
+__device__ void ag_copy_role(const FusedParams& p, int K, uint8_t* smem, uint64_t* bars, volatile int* abort_flag,
+                             int* ok_slot) {
+  const PeerCtx& c = p.peer;
+  const int cta = blockIdx.x;
+  if (!peer_barrier(c, cta, static_cast<uint64_t>(p.epoch) * 4 + 1, ok_slot)) return;
+  if (threadIdx.x == 0) {
+    uint64_t* full = bars;                  // [FG_SLOTS], placed behind the ring
+    const long tile_bytes = static_cast<long>(FG_BM) * K * 2;
+    const int tiles_per_rank = p.rows_per_rank / FG_BM;
+    const int remote_tiles = tiles_per_rank * (c.world - 1);
+    uint32_t issued = 0;                    // chunks loaded so far by this driver (ring position)
+    bool ok = true;
+    // remote tiles in arrival order: all tiles of rank+1, then rank+2, ...; drivers take them round-robin
+    for (int rt = cta; rt < remote_tiles && ok; rt += p.n_first) {
+      const int src = (c.rank + 1 + rt / tiles_per_rank) % c.world;
+      const int tile = src * tiles_per_rank + rt % tiles_per_rank;     // tile index in the gathered buffer
+      const uint8_t* from = c.base[src] + p.xg_off + tile * tile_bytes;
+      uint8_t* to = c.base[c.rank] + p.xg_off + tile * tile_bytes;
+      const int nchunks = static_cast<int>((tile_bytes + FG_CHUNK - 1) / FG_CHUNK);
+      int loaded = 0, stored = 0;
+      while (stored < nchunks && ok) {
+        // keep the ring full
+        // a slot is refilled only after the store that used it has read it: with at most one
+        // store still reading, loads may run FG_SLOTS-2 chunks ahead of the stores
+        while (loaded < nchunks && loaded - stored < FG_SLOTS - 2) {
+          const int slot = (issued + loaded) % FG_SLOTS;
+          const long o = static_cast<long>(loaded) * FG_CHUNK;
+          const uint32_t bytes = static_cast<uint32_t>(min(static_cast<long>(FG_CHUNK), tile_bytes - o));
+          mbar_expect_tx(&full[slot], bytes);
+          bulk_g2s(smem + slot * FG_CHUNK, from + o, bytes, &full[slot]);
+          ++loaded;
+        }
+        const int slot = (issued + stored) % FG_SLOTS;
+        const uint32_t ph = ((issued + stored) / FG_SLOTS) & 1u;
+        if (!mbar_wait(&full[slot], ph, abort_flag, c.status, ST_TIMEOUT_PEER)) { ok = false; break; }
+        const long o = static_cast<long>(stored) * FG_CHUNK;
+        const uint32_t bytes = static_cast<uint32_t>(min(static_cast<long>(FG_CHUNK), tile_bytes - o));
+        bulk_s2g(to + o, smem + slot * FG_CHUNK, bytes);
+        tma_store_commit();
+        ++stored;
+        tma_store_wait_read<1>();
+      }
+      issued += nchunks;
+      tma_store_wait<0>();                  // the tile's bytes are in local memory
+      __threadfence();
+      st_release_gpu_u32(&p.ready[tile], p.epoch);
+    }
+    tma_store_wait<0>();
+  }
+  // peers may still be reading this rank's shard: do not let the kernel (and the next writer of the
+  // shard) get ahead of them
+  peer_barrier(c, cta, static_cast<uint64_t>(p.epoch) * 4 + 2, ok_slot);
+}
+
+// ----------------------------------------------------------------------------- reducer (RS)
+// Work items are (row tile, column tile) pairs of this rank's shard, dealt round-robin to ALL CTAs of
+// the kernel: the dedicated reducer CTAs start on them at once, the GEMM CTAs join when their tiles
+// are done, so the tail of the reduction runs on the whole chip.
+__device__ void rs_reduce_items(const FusedParams& p, int N, int tiles_n, int BN, int* ok_slot) {
+  const PeerCtx& c = p.peer;
+  const int tiles_m = p.rows_per_rank / FG_BM;
+  const uint32_t want = p.epoch * 4u;                         // 4 epilogue warps per tile per call
+  const uint32_t* cnt = reinterpret_cast<const uint32_t*>(c.base[c.rank] + p.cnt_off);
+  const __nv_bfloat16* stage = reinterpret_cast<const __nv_bfloat16*>(c.base[c.rank] + p.stage_off);
+  const long slot_elems = static_cast<long>(p.rows_per_rank) * N;
+  for (int item = blockIdx.x; item < tiles_m * tiles_n; item += gridDim.x) {
+    const int tm = item % tiles_m, tn = item / tiles_m;
+    if (threadIdx.x < c.world) {
+      const uint32_t* q = cnt + (static_cast<long>(threadIdx.x) * tiles_m + tm) * tiles_n + tn;
+      if (!wait_u32_ge(q, want, true, c.status, ST_TIMEOUT_PEER)) *ok_slot = 0;
+    }
+    __syncthreads();
+    if (*ok_slot == 0) return;
+    const int cols = min(BN, N - tn * BN);
+    const int vec_per_row = cols >> 3;
+    for (int v = threadIdx.x; v < FG_BM * vec_per_row; v += blockDim.x) {
+      const int row = tm * FG_BM + v / vec_per_row;
+      const int col = tn * BN + (v % vec_per_row) * 8;
+      float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (int s = 0; s < c.world; ++s) {
+        const uint4 u = *reinterpret_cast<const uint4*>(stage + s * slot_elems + static_cast<long>(row) * N + col);
+        const __nv_bfloat162* x = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 t = __bfloat1622float2(x[i]);
+          f[2 * i] += t.x;
+          f[2 * i + 1] += t.y;
+        }
+      }
+      uint4 o;
+      o.x = pack_bf16x2(f[0], f[1]); o.y = pack_bf16x2(f[2], f[3]);
+      o.z = pack_bf16x2(f[4], f[5]); o.w = pack_bf16x2(f[6], f[7]);
+      *reinterpret_cast<uint4*>(p.out + static_cast<long>(row) * N + col) = o;
+    }
+    __syncthreads();
+  }
+}
+
+// ----------------------------------------------------------------------------- kernel
+template <int BN>
+__global__ void __launch_bounds__(FG_THREADS, 1)
+fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                  const FusedParams p, int M, int N, int K) {
+  using S = FgSmem<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + S::TILE_BYTES);
+  uint64_t* empty = full + FG_STAGES;
+  uint64_t* tfull = empty + FG_STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* ok_slot = const_cast<int*>(abort_flag) + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int tiles_m = (M + FG_BM - 1) / FG_BM;
+  const int tiles_n = (N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int nk = (K + FG_BK - 1) / FG_BK;
+  const PeerCtx& c = p.peer;
+  int* status = c.status;
+
+  // ---- non-GEMM roles
+  if (static_cast<int>(blockIdx.x) < p.n_first) {
+    uint64_t* ring_bars = reinterpret_cast<uint64_t*>(smem + FG_SLOTS * FG_CHUNK);
+    volatile int* ring_abort = reinterpret_cast<volatile int*>(ring_bars + FG_SLOTS);
+    int* ring_ok = const_cast<int*>(ring_abort) + 1;
+    if (threadIdx.x == 0) {
+      for (int i = 0; i < FG_SLOTS; ++i) mbar_init(&ring_bars[i], 1);
+      *ring_abort = 0;
+      *ring_ok = 1;
+      mbar_fence_init();
+    }
+    __syncthreads();
+    ag_copy_role(p, K, smem, ring_bars, ring_abort, ring_ok);
+    return;
+  }
+  if (static_cast<int>(blockIdx.x) >= p.n_first + p.n_gemm) {
+    if (threadIdx.x == 0) *ok_slot = 1;
+    __syncthreads();
+    if (static_cast<int>(blockIdx.x) == p.n_first + p.n_gemm) {
+      // tell this rank's epilogues that every peer has entered the call (their staging is free)
+      const bool ok = peer_barrier(c, 0, static_cast<uint64_t>(p.epoch) * 4 + 1, ok_slot);
+      if (threadIdx.x == 0 && ok) st_release_gpu_u32(p.go, p.epoch);
+      if (!ok) return;
+    }
+    rs_reduce_items(p, N, tiles_n, BN, ok_slot);
+    return;
+  }
+
+  // ---- GEMM role
+  const int cta = blockIdx.x - p.n_first;
+  constexpr uint32_t TMEM_COLS = 2 * BN;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < FG_STAGES; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tfull[i], 1);
+      mbar_init(&tempty[i], 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // tile t -> (row tile, column tile): rank-rotated blocks of rows, m fastest inside a block
+  const int tiles_per_rank = p.rows_per_rank / FG_BM;
+  const int per_owner = tiles_per_rank * tiles_n;
+  auto coords = [&](int t, int& tm, int& tn) {
+    const int blk = t / per_owner;
+    const int owner = (c.rank + (p.mode == MODE_RS ? 1 : 0) + blk) % c.world;
+    const int r = t - blk * per_owner;
+    tm = owner * tiles_per_rank + r % tiles_per_rank;
+    tn = r / tiles_per_rank;
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      prefetch_tmap(&tmA);
+      prefetch_tmap(&tmB);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = cta; t < num_tiles && ok; t += p.n_gemm) {
+        int tm, tn;
+        coords(t, tm, tn);
+        if (p.mode == MODE_AG && tm / tiles_per_rank != c.rank) {
+          // remote rows: wait until the copy drivers have landed this tile in local memory
+          if (!wait_u32_ge(&p.ready[tm], p.epoch, false, status, ST_TIMEOUT_PEER, abort_flag)) { ok = false; break; }
+          fence_proxy_async_all();
+        }
+        const int m0 = tm * FG_BM, n0 = tn * BN;
+        for (int kb_ = 0; kb_ < nk; ++kb_, ++it) {
+          const int s = it % FG_STAGES;
+          const uint32_t ph = (it / FG_STAGES) & 1u;
+          if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag, status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
+          uint8_t* a_dst = smem + s * S::STAGE_BYTES;
+          mbar_expect_tx(&full[s], S::STAGE_BYTES);
+          tma_load_2d(a_dst, &tmA, &full[s], kb_ * FG_BK, m0);
+          tma_load_2d(a_dst + S::A_BYTES, &tmB, &full[s], kb_ * FG_BK, n0);
+        }
+      }
+      if (!ok) {
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) {}
+      }
+    }
+  } else if (warp == 1) {
+    constexpr uint32_t idesc = make_idesc_bf16(FG_BM, BN, false, false);
+    uint32_t it = 0, tile_i = 0;
+    bool ok = true;
+    for (int t = cta; t < num_tiles && ok; t += p.n_gemm, ++tile_i) {
+      const uint32_t buf = tile_i & 1u, bph = (tile_i >> 1) & 1u;
+      if (!mbar_wait(&tempty[buf], bph ^ 1u, abort_flag, status, ST_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + buf * BN;
+      for (int kb_ = 0; kb_ < nk; ++kb_, ++it) {
+        const int s = it % FG_STAGES;
+        const uint32_t ph = (it / FG_STAGES) & 1u;
+        if (!mbar_wait(&full[s], ph, abort_flag, status, ST_TIMEOUT_FULL)) { ok = false; break; }
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t a_addr = smem_u32(smem + s * S::STAGE_BYTES);
+          const uint32_t b_addr = a_addr + S::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < FG_BK / 16; ++k)
+            umma_ss(d_tmem, make_smem_desc(a_addr + k * 32, 16, 1024), make_smem_desc(b_addr + k * 32, 16, 1024),
+                    idesc, (kb_ > 0 || k > 0) ? 1u : 0u);
+          umma_commit(&empty[s]);
+          if (kb_ == nk - 1) umma_commit(&tfull[buf]);
+        }
+        __syncwarp();
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    uint32_t tile_i = 0;
+    bool ok = true;
+    bool go_seen = false;
+    for (int t = cta; t < num_tiles && ok; t += p.n_gemm, ++tile_i) {
+      const uint32_t buf = tile_i & 1u, bph = (tile_i >> 1) & 1u;
+      int tm, tn;
+      coords(t, tm, tn);
+      const int m0 = tm * FG_BM, n0 = tn * BN;
+      if (!mbar_wait(&tfull[buf], bph, abort_flag, status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      const uint32_t taddr = tmem_base + buf * BN + (static_cast<uint32_t>(q * 32) << 16);
+      __nv_bfloat16* crow;
+      if (p.mode == MODE_RS) {
+        if (!go_seen) {
+          if (!wait_u32_ge(p.go, p.epoch, false, status, ST_TIMEOUT_PEER, abort_flag)) { ok = false; break; }
+          go_seen = true;
+        }
+        const int owner = tm / tiles_per_rank;
+        __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(c.base[owner] + p.stage_off) +
+                               static_cast<long>(c.rank) * p.rows_per_rank * N;
+        crow = stage + static_cast<long>(row - owner * p.rows_per_rank) * N;
+      } else {
+        crow = p.out + static_cast<long>(row) * N;
+      }
+#pragma unroll 1
+      for (int cc = 0; cc < BN / 32; ++cc) {
+        uint32_t v[32];
+        tmem_ld_32x32(taddr + cc * 32, v);
+        tmem_ld_wait();
+        const int col = n0 + cc * 32;
+        if (row < M && col < N) {
+          if (col + 32 <= N && (N & 7) == 0) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 o;
+              o.x = pack_bf16x2(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
+              o.y = pack_bf16x2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
+              o.z = pack_bf16x2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
+              o.w = pack_bf16x2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
+              reinterpret_cast<uint4*>(crow + col)[j] = o;
+            }
+          } else {
+            for (int j = 0; j < 32 && col + j < N; ++j) crow[col + j] = __float2bfloat16(__uint_as_float(v[j]));
+          }
+        }
+      }
+      tc_fence_before();
+      if (p.mode == MODE_RS) {
+        // publish this warp's 32 rows of the tile to the owner
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) {
+          const int owner = tm / tiles_per_rank;
+          uint32_t* cnt = reinterpret_cast<uint32_t*>(c.base[owner] + p.cnt_off) +
+                          (static_cast<long>(c.rank) * tiles_per_rank + (tm - owner * tiles_per_rank)) * tiles_n + tn;
+          red_release_sys_add_u32(cnt, 1u);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[buf]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  if (p.mode == MODE_RS && *abort_flag == 0) {
+    if (threadIdx.x == 0) *ok_slot = 1;
+    __syncthreads();
+    rs_reduce_items(p, N, tiles_n, BN, ok_slot);
+  }
+}
+
+template <int BN>
+static int launch_fused(const void* A, const void* W, const FusedParams& p, int M, int N, int K, int lda, int ldw,
+                        cudaStream_t stream) {
+  CUtensorMap tmA, tmB;
+  int rc = make_tmap_2d_bf16(&tmA, A, K, M, lda, FG_BK, FG_BM);
+  if (rc) return rc;
+  rc = make_tmap_2d_bf16(&tmB, W, K, N, ldw, FG_BK, BN);
+  if (rc) return rc;
+  auto kern = fused_gemm_kernel<BN>;
+  constexpr int smem = FgSmem<BN>::TOTAL > (FG_SLOTS * FG_CHUNK + 2048) ? FgSmem<BN>::TOTAL : (FG_SLOTS * FG_CHUNK + 2048);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return 1000 + (int)e;
+    configured = true;
+  }
+  const int grid = p.n_first + p.n_gemm + p.n_last;
+  kern<<<grid, FG_THREADS, smem, stream>>>(tmA, tmB, p, M, N, K);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 2000 + (int)e;
+}
+
+static PeerCtx fused_ctx(void* const* bases, int rank, int world, uint64_t flag_off, int* status) {
+  PeerCtx c;
+  for (int i = 0; i < MAX_PEERS; ++i) c.base[i] = i < world ? reinterpret_cast<uint8_t*>(bases[i]) : nullptr;
+  c.rank = rank; c.world = world; c.flag_off = flag_off; c.status = status;
+  return c;
+}
+
+}  // namespace kb
+
+using namespace kb;
+
+// Y[M,N] = gathered(X)[M,K] · W[N,K]ᵀ where this rank's shard already sits at rows
+// [rank*Ms, (rank+1)*Ms) of the gathered buffer at heap offset xg_off (same offset on all ranks).
+// ready: local uint32[M/128] flags (persist across calls, epoch-valued).  n_comm copy-driver CTAs.
+extern "C" int kb_ag_gemm_bf16(void* const* bases, int rank, int world, uint64_t flag_off, uint64_t xg_off,
+                               const void* W, void* Y, int M, int N, int K, int ldw, uint32_t* ready, uint32_t epoch,
+                               int n_comm, int num_sms, int* status, cudaStream_t stream) {
+  if (world < 2 || world > MAX_PEERS || M % (world * FG_BM) || (K & 7) || (xg_off & 1023)) return ST_BAD_ARG;
+  if (num_sms <= 0) num_sms = device_sm_count();
+  if (n_comm < 1) n_comm = 1;
+  if (n_comm > MAX_SIGNAL_CTAS) n_comm = MAX_SIGNAL_CTAS;
+  if (n_comm > num_sms / 2) n_comm = num_sms / 2;
+  FusedParams p{};
+  p.peer = fused_ctx(bases, rank, world, flag_off, status);
+  p.mode = MODE_AG;
+  p.n_first = n_comm;
+  p.n_last = 0;
+  p.rows_per_rank = M / world;
+  p.epoch = epoch;
+  p.xg_off = xg_off;
+  p.ready = ready;
+  p.out = reinterpret_cast<__nv_bfloat16*>(Y);
+  const void* A = reinterpret_cast<const uint8_t*>(bases[rank]) + xg_off;
+  const bool narrow = (N <= 128) || (N % 256 != 0 && N % 256 <= 128);
+  const int bn = narrow ? 128 : 256;
+  const int tiles = (M / FG_BM) * ((N + bn - 1) / bn);
+  p.n_gemm = num_sms - n_comm < tiles ? num_sms - n_comm : tiles;
+  if (narrow) return launch_fused<128>(A, W, p, M, N, K, K, ldw, stream);
+  return launch_fused<256>(A, W, p, M, N, K, K, ldw, stream);
+}
+
+// out[M/world, N] = rows owned by this rank of sum over ranks of (A[M,K] · W[N,K]ᵀ).
+// stage_off: staging [world][M/world][N] bf16; cnt_off: uint32 counters [world][M/world/128][tiles_n];
+// go: local uint32 flag.  n_comm reducer CTAs run next to the GEMM CTAs.
+extern "C" int kb_gemm_rs_bf16(void* const* bases, int rank, int world, uint64_t flag_off, uint64_t stage_off,
+                               uint64_t cnt_off, const void* A, int lda, const void* W, int ldw, void* out, int M, int N,
+                               int K, uint32_t* go, uint32_t epoch, int n_comm, int num_sms, int* status,
+                               cudaStream_t stream) {
+  if (world < 2 || world > MAX_PEERS || M % (world * FG_BM) || (K & 7) || (N & 7) || (lda & 7)) return ST_BAD_ARG;
+  if (num_sms <= 0) num_sms = device_sm_count();
+  if (n_comm < 1) n_comm = 1;
+  FusedParams p{};
+  p.peer = fused_ctx(bases, rank, world, flag_off, status);
+  p.mode = MODE_RS;
+  p.n_first = 0;
+  p.n_last = n_comm;
+  p.rows_per_rank = M / world;
+  p.epoch = epoch;
+  p.stage_off = stage_off;
+  p.cnt_off = cnt_off;
+  p.go = go;
+  p.out = reinterpret_cast<__nv_bfloat16*>(out);
+  const bool narrow = (N <= 128) || (N % 256 != 0 && N % 256 <= 128);
+  const int bn = narrow ? 128 : 256;
+  const int tiles = (M / FG_BM) * ((N + bn - 1) / bn);
+  if (n_comm > num_sms / 2) n_comm = num_sms / 2;
+  p.n_last = n_comm;
+  p.n_gemm = num_sms - n_comm < tiles ? num_sms - n_comm : tiles;   // reducers get SMs of their own
+  if (narrow) return launch_fused<128>(A, W, p, M, N, K, lda, ldw, stream);
+  return launch_fused<256>(A, W, p, M, N, K, lda, ldw, stream);
+}
+
+// Number of column tiles the fused kernels use for a given N (sizes the counter array).
+extern "C" int kb_fused_tiles_n(int N) {
+  const bool narrow = (N <= 128) || (N % 256 != 0 && N % 256 <= 128);
+  const int bn = narrow ? 128 : 256;
+  return (N + bn - 1) / bn;
+}

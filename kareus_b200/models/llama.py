@@ -71,6 +71,10 @@ class TransformerLayer(nn.Module):
         self.fc2 = RowParallelLinear(f, h, f"{n}.mlp.linear_fc2", "mlp", par.tp_comm, comm,
                                      init_std=out_std, seed=seed * 16 + 5, **kw)
         self.mlp_bda = DropoutAddOp(cfg.hidden_dropout, f"{n}.mlp_bda", base_seed=seed * 16 + 6)
+        if par.tp_comm == "sp_fused" and tp > 1 and getattr(comm, "heap", None) is not None \
+                and dtype == torch.bfloat16 and torch.device(device or "cpu").type == "cuda":
+            from ..ops.fused import attach_fused
+            attach_fused(self, comm.heap)
 
     def operators(self):
         return [self.attn_fork, self.input_norm, self.qkv, self.qkv_post, self.rope, self.core_attn,

@@ -40,6 +40,41 @@ def test_heap_collectives(heap, rank, world, dev):
     assert torch.all(y == world)
 
 
+def test_fused_gemm_collectives(heap, rank, world, dev):
+    """all-gather→GEMM and GEMM→reduce-scatter kernels vs NCCL + fp32 matmul."""
+    from types import SimpleNamespace
+    from kareus_b200.engine.context import OpContext
+    from kareus_b200.kernels import cuda as KC
+    from kareus_b200.ops.fused import FusedAGGemm, FusedGemmRS
+    g = torch.Generator(device=dev).manual_seed(5 + rank)
+    for (ms, k, n, sm) in [(256, 512, 384, 4), (1024, 3072, 640, 12), (512, 1024, 3072, 8)]:
+        w = (torch.randn(n, k, device=dev, generator=g) * 0.05).bfloat16()
+        lin = SimpleNamespace(name=f"lin{ms}_{n}", out_features=n, weight=w)
+        x = torch.randn(ms, 1, k, device=dev, generator=g).bfloat16()
+        xs = torch.empty(ms * world, 1, k, device=dev, dtype=torch.bfloat16)
+        dist.all_gather_into_tensor(xs, x)
+        want = xs.float().reshape(-1, k) @ w.float().t()
+        op = FusedAGGemm(lin, heap, 8)
+        for rep in range(3):
+            ctx = OpContext()
+            (y,) = op.run((x,), sm_num=sm, nb=0, ctx=ctx)
+            torch.cuda.synchronize()
+            KC.check_status()
+            assert rel(y.reshape(-1, n), want) < 1e-2, ("ag_gemm", ms, k, n, rep, rel(y.reshape(-1, n), want))
+            assert torch.equal(ctx.saved_tensors[0], xs.reshape(-1, k))
+        a = torch.randn(ms * world, 1, k, device=dev, generator=g).bfloat16()
+        part = (a.float().reshape(-1, k) @ w.float().t())
+        full = part.clone()
+        dist.all_reduce(full)
+        want_rs = full[rank * ms:(rank + 1) * ms]
+        op2 = FusedGemmRS(lin, heap, 8)
+        for rep in range(3):
+            (o,) = op2.run((a,), sm_num=sm, nb=1, ctx=OpContext())
+            torch.cuda.synchronize()
+            KC.check_status()
+            assert rel(o.reshape(-1, n), want_rs) < 2e-2, ("gemm_rs", ms, k, n, rep, rel(o.reshape(-1, n), want_rs))
+
+
 def test_bounded_wait(heap, dev):
     from kareus_b200.kernels import cuda as KC
     heap.wait_flag_probe(limit_ns=100_000_000)
@@ -91,9 +126,11 @@ def main():
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
     which = sys.argv[1] if len(sys.argv) > 1 else "all"
-    heap = SymmetricHeap.create(dist.group.WORLD, dev, size_bytes=1 << 30)
+    heap = SymmetricHeap.create(dist.group.WORLD, dev, size_bytes=2 << 30)
     if which in ("all", "collectives"):
         test_heap_collectives(heap, rank, world, dev)
+    if which in ("all", "fused"):
+        test_fused_gemm_collectives(heap, rank, world, dev)
     if which in ("all", "wait"):
         test_bounded_wait(heap, dev)
     if which in ("all", "model"):

@@ -1,0 +1,74 @@
+"""Wrapper of the sm_100a flash-attention backward kernel (see ``csrc/attention_bwd_sm100.cu``)."""
+from __future__ import annotations
+
+from ctypes import c_float, c_int, c_long, c_void_p
+
+import torch
+
+from . import cuda as KC
+
+_DECLARED = False
+
+
+def _lib():
+    global _DECLARED
+    L = KC.lib()
+    if not _DECLARED:
+        P, I, LNG, F = c_void_p, c_int, c_long, c_float
+        L.kb_flash_attn_bwd.argtypes = ([P, LNG, LNG, LNG, LNG, P, LNG, LNG, LNG, P, LNG, LNG, LNG, P, P, P,
+                                         P, LNG, LNG, LNG, LNG, P, LNG, LNG, LNG, P, LNG, LNG, LNG, P] +
+                                        [I] * 6 + [F, I, I, P, P])
+        L.kb_flash_attn_bwd.restype = c_int
+        L.kb_flash_attn_bwd_scratch_floats.argtypes = [I] * 6
+        L.kb_flash_attn_bwd_scratch_floats.restype = c_long
+        _DECLARED = True
+    return L
+
+
+def _geom5(t, kg):
+    """(s, b, g, rep, d, strides(s, b, g, r)) of a query-like view."""
+    if t.dim() == 5:
+        s, b, g, rep, d = t.shape
+        return s, b, g, rep, d, (t.stride(0), t.stride(1), t.stride(2), t.stride(3))
+    s, b, h, d = t.shape
+    rep = h // kg
+    return s, b, kg, rep, d, (t.stride(0), t.stride(1), t.stride(2) * rep, t.stride(2))
+
+
+def _ok(t):
+    return t.stride(-1) == 1 and t.data_ptr() % 16 == 0 and all(st % 8 == 0 for st in t.stride()[:-1])
+
+
+def backward(do, q, k, v, o, lse, scale, causal=True, q_offset=0, kv_len=None, out=None):
+    kg = k.shape[2]
+    sq, b, g, rep, d, qs = _geom5(q, kg)
+    if d != 128 or not (_ok(q) and _ok(k) and _ok(v)):
+        return KC.attention_bwd_library(do, q, k, v, o, lse, scale, causal, q_offset, kv_len, out)
+    skv = k.shape[0] if kv_len is None else int(kv_len)
+    hq = g * rep
+    o4 = o.reshape(sq, b, hq, d).contiguous()
+    do4 = do.reshape(sq, b, hq, d).contiguous()
+    if out is None:
+        dq = torch.empty(sq, b, g, rep, d, dtype=q.dtype, device=q.device)
+        dk = torch.empty_like(k, memory_format=torch.contiguous_format)
+        dv = torch.empty_like(v, memory_format=torch.contiguous_format)
+    else:
+        dq, dk, dv = out
+    if skv < k.shape[0]:
+        dk[skv:].zero_()
+        dv[skv:].zero_()
+    _, _, _, _, _, dqs = _geom5(dq, kg)
+    L = _lib()
+    work = torch.empty(L.kb_flash_attn_bwd_scratch_floats(sq, skv, b, g, rep, d), dtype=torch.float32, device=q.device)
+    st = KC.status_word(q.device)
+    rc = L.kb_flash_attn_bwd(q.data_ptr(), *qs, k.data_ptr(), k.stride(0), k.stride(1), k.stride(2),
+                             v.data_ptr(), v.stride(0), v.stride(1), v.stride(2), o4.data_ptr(), do4.data_ptr(),
+                             lse.data_ptr(), dq.data_ptr(), *dqs, dk.data_ptr(), dk.stride(0), dk.stride(1),
+                             dk.stride(2), dv.data_ptr(), dv.stride(0), dv.stride(1), dv.stride(2), work.data_ptr(),
+                             sq, skv, b, g, rep, d, float(scale), 1 if causal else 0, int(q_offset), st.data_ptr(),
+                             KC._stream())
+    KC._check(rc, "flash_attn_bwd")
+    KC._count(6)
+    if out is not None:
+        return out
+    return dq.reshape(q.shape), dk, dv

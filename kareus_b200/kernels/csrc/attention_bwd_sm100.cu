@@ -1,0 +1,405 @@
+// Causal GQA flash-attention backward for sm_100a (head dim 128, bf16, fp32 accumulation).
+//
+// One CTA owns 128 keys of one (batch, query head) and walks the query tiles that can see them:
+//   warp 0      TMA producer: K and V once, then Q and dO per query tile
+//   warp 1      MMA issuer (tcgen05, accumulators in TMEM):
+//                 S  = Q·Kᵀ          dP = dO·Vᵀ                       (per query tile)
+//                 dV += Pᵀ·dO        dK += dSᵀ·Q        dQ = dS·K      (per query tile)
+//   warps 2..5  one thread per query row: P = exp2(S·c − lse), dS = P∘(dP − δ)·scale, both as bf16
+//               into swizzled shared memory; later dQ from TMEM → fp32 vector reductions in global.
+// P and dS are stored once ([q][key], keys contiguous) and serve as K-major operands (dQ) and, read
+// through MN-major descriptors, as the transposed operands of dV and dK — no transposes anywhere.
+// TMEM: S|dQ (shared) + dP + dV + dK = 512 columns.  dK/dV stay in TMEM across the whole walk and
+// are added to fp32 accumulators at the end (query heads of one KV group run in different CTAs).
+// A second kernel converts the fp32 accumulators into the packed bf16 gradient of the QKV GEMM.
+//
+// Replaces the FlashAttention-2 backward the reference calls through its wheel
+// (kareus/flash_attn/flash_attn_interface.py:147-199).
+#include "sm100.cuh"
+#include "host_utils.h"
+
+namespace kb {
+
+constexpr int FB_T = 128;                      // tile edge (queries, keys) and head dim
+constexpr int FB_TILE = FB_T * FB_T * 2;       // 32 KB bf16 tile as two 64-wide swizzled chunks
+constexpr int FB_CHUNK = 16384;
+constexpr int FB_THREADS = 192;
+
+struct BwdParams {
+  const float* lse;      // [b, hq, sq]  natural log
+  const float* delta;    // [b, hq, sq]  rowsum(dO ∘ O)
+  float* dq_acc;         // [sq, b, hq, d]
+  float* dk_acc;         // [skv, b, g, d]
+  float* dv_acc;         // [skv, b, g, d]
+  int sq, skv, b, hq, rep, q_offset, causal;
+  float scale, scale_log2;
+  int* status;
+};
+
+struct FbSmem {
+  static constexpr int K_OFF = 0, V_OFF = FB_TILE, Q_OFF = 2 * FB_TILE, DO_OFF = 3 * FB_TILE, P_OFF = 4 * FB_TILE,
+                       DS_OFF = 5 * FB_TILE, BAR_OFF = 6 * FB_TILE, TOTAL = BAR_OFF + 256 + 1024;
+};
+
+__device__ __forceinline__ float bwd_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+__global__ void __launch_bounds__(FB_THREADS, 1)
+flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                      const BwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FbSmem::BAR_OFF);
+  uint64_t* kv_full = bars + 0;
+  uint64_t* qdo_full = bars + 1;
+  uint64_t* qdo_empty = bars + 2;   // MMAs that read Q/dO/P/dS of this iteration have retired
+  uint64_t* s_full = bars + 3;      // S and dP are in TMEM
+  uint64_t* pds_full = bars + 4;    // P and dS are in shared memory (4 warp arrivals)
+  uint64_t* dq_full = bars + 5;     // dQ (and this iteration's dV/dK updates) retired
+  uint64_t* dq_empty = bars + 6;    // dQ has been read out of TMEM (4 warp arrivals)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kt = blockIdx.x;                 // key tile; tile 0 is seen by the most queries → first
+  const int head = blockIdx.y, batch = blockIdx.z;
+  const int g = head / p.rep, r = head % p.rep;
+  const int k0 = kt * FB_T;
+  const int n_q = (p.sq + FB_T - 1) / FB_T;
+  int m_start = 0;
+  if (p.causal) {
+    const int d0 = k0 - p.q_offset;
+    m_start = d0 > 0 ? d0 / FB_T : 0;
+  }
+  const int n_it = n_q > m_start ? n_q - m_start : 0;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    mbar_init(qdo_full, 1);
+    mbar_init(qdo_empty, 1);
+    mbar_init(s_full, 1);
+    mbar_init(pds_full, 4);
+    mbar_init(dq_full, 1);
+    mbar_init(dq_empty, 4);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t t_s = tmem_base, t_dp = tmem_base + 128, t_dv = tmem_base + 256, t_dk = tmem_base + 384;
+
+  if (warp == 0) {
+    if (lane == 0 && n_it > 0) {
+      prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmDO);
+      mbar_expect_tx(kv_full, 2 * FB_TILE);
+      tma_load_4d(smem + FbSmem::K_OFF, &tmK, kv_full, 0, g, batch, k0);
+      tma_load_4d(smem + FbSmem::K_OFF + FB_CHUNK, &tmK, kv_full, 64, g, batch, k0);
+      tma_load_4d(smem + FbSmem::V_OFF, &tmV, kv_full, 0, g, batch, k0);
+      tma_load_4d(smem + FbSmem::V_OFF + FB_CHUNK, &tmV, kv_full, 64, g, batch, k0);
+      for (int it = 0; it < n_it; ++it) {
+        if (!mbar_wait(qdo_empty, (it & 1u) ^ 1u, abort_flag, p.status, ST_TIMEOUT_EMPTY)) break;
+        const int q0 = (m_start + it) * FB_T;
+        mbar_expect_tx(qdo_full, 2 * FB_TILE);
+        tma_load_5d(smem + FbSmem::Q_OFF, &tmQ, qdo_full, 0, r, g, batch, q0);
+        tma_load_5d(smem + FbSmem::Q_OFF + FB_CHUNK, &tmQ, qdo_full, 64, r, g, batch, q0);
+        tma_load_4d(smem + FbSmem::DO_OFF, &tmDO, qdo_full, 0, head, batch, q0);
+        tma_load_4d(smem + FbSmem::DO_OFF + FB_CHUNK, &tmDO, qdo_full, 64, head, batch, q0);
+      }
+      if (*abort_flag) {
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) {}
+      }
+    }
+  } else if (warp == 1) {
+    constexpr uint32_t id_kk = make_idesc_bf16(FB_T, FB_T, false, false);   // A K-major, B K-major
+    constexpr uint32_t id_mm = make_idesc_bf16(FB_T, FB_T, true, true);     // A MN-major, B MN-major
+    constexpr uint32_t id_km = make_idesc_bf16(FB_T, FB_T, false, true);    // A K-major, B MN-major
+    const uint32_t a_k = smem_u32(smem + FbSmem::K_OFF), a_v = smem_u32(smem + FbSmem::V_OFF);
+    const uint32_t a_q = smem_u32(smem + FbSmem::Q_OFF), a_do = smem_u32(smem + FbSmem::DO_OFF);
+    const uint32_t a_p = smem_u32(smem + FbSmem::P_OFF), a_ds = smem_u32(smem + FbSmem::DS_OFF);
+    auto kmaj = [](uint32_t base, int k) { return make_smem_desc(base + (k >> 2) * FB_CHUNK + (k & 3) * 32, 16, 1024); };
+    auto mnmaj = [](uint32_t base, int k) { return make_smem_desc(base + k * 2048, FB_CHUNK, 1024); };
+    bool ok = n_it > 0;
+    if (ok) ok = mbar_wait(kv_full, 0, abort_flag, p.status, ST_TIMEOUT_FULL);
+    for (int it = 0; it < n_it && ok; ++it) {
+      const uint32_t ph = it & 1u;
+      if (!mbar_wait(qdo_full, ph, abort_flag, p.status, ST_TIMEOUT_FULL)) { ok = false; break; }
+      if (!mbar_wait(dq_empty, ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+      tc_fence_after();
+      if (lane == 0) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) umma_ss(t_s, kmaj(a_q, k), kmaj(a_k, k), id_kk, k > 0);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) umma_ss(t_dp, kmaj(a_do, k), kmaj(a_v, k), id_kk, k > 0);
+        umma_commit(s_full);
+      }
+      __syncwarp();
+      if (!mbar_wait(pds_full, ph, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      if (lane == 0) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) umma_ss(t_dv, mnmaj(a_p, k), mnmaj(a_do, k), id_mm, (it > 0 || k > 0));
+#pragma unroll
+        for (int k = 0; k < 8; ++k) umma_ss(t_dk, mnmaj(a_ds, k), mnmaj(a_q, k), id_mm, (it > 0 || k > 0));
+#pragma unroll
+        for (int k = 0; k < 8; ++k) umma_ss(t_s, kmaj(a_ds, k), mnmaj(a_k, k), id_km, k > 0);
+        umma_commit(qdo_empty);
+        umma_commit(dq_full);
+      }
+      __syncwarp();
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    const float lg2e = 1.4426950408889634f;
+    bool ok = n_it > 0;
+    for (int it = 0; it < n_it && ok; ++it) {
+      const uint32_t ph = it & 1u;
+      const int q0 = (m_start + it) * FB_T;
+      const int qrow = q0 + row;
+      const int qpos = p.q_offset + qrow;
+      const bool valid = qrow < p.sq;
+      const size_t stat = (static_cast<size_t>(batch) * p.hq + head) * p.sq + (valid ? qrow : 0);
+      const float lse2 = valid ? p.lse[stat] * lg2e : 0.f;
+      const float dlt = valid ? p.delta[stat] : 0.f;
+      if (!mbar_wait(s_full, ph, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      const bool tile_mask = (p.causal && k0 + FB_T - 1 > p.q_offset + q0) || (k0 + FB_T > p.skv) || (q0 + FB_T > p.sq);
+      uint8_t* p_row = smem + FbSmem::P_OFF + row * 128;
+      uint8_t* ds_row = smem + FbSmem::DS_OFF + row * 128;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t sv[32], dv[32];
+        tmem_ld_32x32(t_s + lane_addr + c * 32, sv);
+        tmem_ld_32x32(t_dp + lane_addr + c * 32, dv);
+        tmem_ld_wait();
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          uint32_t wp[4], wd[4];
+#pragma unroll
+          for (int h2 = 0; h2 < 4; ++h2) {
+            const int i = 8 * u + 2 * h2;
+            float e0 = bwd_exp2(__uint_as_float(sv[i]) * p.scale_log2 - lse2);
+            float e1 = bwd_exp2(__uint_as_float(sv[i + 1]) * p.scale_log2 - lse2);
+            if (tile_mask) {
+              const int key = k0 + c * 32 + i;
+              if (!valid || (p.causal && key > qpos) || key >= p.skv) e0 = 0.f;
+              if (!valid || (p.causal && key + 1 > qpos) || key + 1 >= p.skv) e1 = 0.f;
+            }
+            const float d0 = e0 * (__uint_as_float(dv[i]) - dlt) * p.scale;
+            const float d1 = e1 * (__uint_as_float(dv[i + 1]) - dlt) * p.scale;
+            wp[h2] = pack_bf16x2(e0, e1);
+            wd[h2] = pack_bf16x2(d0, d1);
+          }
+          const int unit = (c & 1) * 4 + u;
+          const int o = (c >> 1) * FB_CHUNK + ((unit ^ (row & 7)) << 4);
+          *reinterpret_cast<uint4*>(p_row + o) = make_uint4(wp[0], wp[1], wp[2], wp[3]);
+          *reinterpret_cast<uint4*>(ds_row + o) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
+        }
+      }
+      tc_fence_before();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pds_full);
+      // dQ tile → fp32 vector reductions into the global accumulator
+      if (!mbar_wait(dq_full, ph, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      float* dq_row = p.dq_acc + ((static_cast<size_t>(valid ? qrow : 0) * p.b + batch) * p.hq + head) * FB_T;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(t_s + lane_addr + c * 32, v);
+        tmem_ld_wait();
+        if (valid) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            red_add_v4(dq_row + c * 32 + 4 * j, __uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                       __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(dq_empty);
+    }
+    // dV, dK of this key tile → fp32 accumulators (rows = keys)
+    if (n_it > 0) {
+      // the last dq_full wait above already covered every MMA of the walk
+      tc_fence_after();
+      const int key = k0 + row;
+      const bool kvalid = ok && key < p.skv;
+      const size_t base = ((static_cast<size_t>(kvalid ? key : 0) * p.b + batch) * (p.hq / p.rep) + g) * FB_T;
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        float* dst = (which == 0 ? p.dv_acc : p.dk_acc) + base;
+        const uint32_t src = (which == 0 ? t_dv : t_dk) + lane_addr;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(src + c * 32, v);
+          tmem_ld_wait();
+          if (kvalid) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              red_add_v4(dst + c * 32 + 4 * j, __uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                         __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// delta[b, h, s] = Σ_d dO[s,b,h,d] · O[s,b,h,d]   (both [s,b,h,d] contiguous), one warp per row
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ dO, const __nv_bfloat16* __restrict__ O,
+                                  float* __restrict__ delta, int S, int B, int H) {
+  const long rows = static_cast<long>(S) * B * H;
+  const int lane = threadIdx.x & 31;
+  for (long w = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; w < rows;
+       w += (static_cast<long>(gridDim.x) * blockDim.x) >> 5) {
+    const uint2 a = reinterpret_cast<const uint2*>(dO + w * FB_T)[lane];
+    const uint2 b = reinterpret_cast<const uint2*>(O + w * FB_T)[lane];
+    const float2 a0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a.x));
+    const float2 a1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a.y));
+    const float2 b0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&b.x));
+    const float2 b1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&b.y));
+    float s = a0.x * b0.x + a0.y * b0.y + a1.x * b1.x + a1.y * b1.y;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) {
+      const int h = static_cast<int>(w % H);
+      const long sb = w / H;
+      const int bb = static_cast<int>(sb % B);
+      const long ss = sb / B;
+      delta[(static_cast<long>(bb) * H + h) * S + ss] = s;
+    }
+  }
+}
+
+// fp32 accumulator [rows(s,b), heads, d] → bf16 strided view (strides in elements per s, b, head)
+__global__ void attn_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ out, long n_vec, int B,
+                                    int G, int R, long st_s, long st_b, long st_g, long st_r) {
+  // one thread per 4 elements of d
+  for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const int dv = static_cast<int>(i % (FB_T / 4));
+    long rest = i / (FB_T / 4);
+    const int rr = static_cast<int>(rest % R); rest /= R;
+    const int gg = static_cast<int>(rest % G); rest /= G;
+    const int bb = static_cast<int>(rest % B);
+    const long ss = rest / B;
+    const float4 v = reinterpret_cast<const float4*>(acc)[i];
+    __nv_bfloat16* o = out + ss * st_s + bb * st_b + gg * st_g + rr * st_r + dv * 4;
+    uint2 w;
+    *reinterpret_cast<__nv_bfloat162*>(&w.x) = __floats2bfloat162_rn(v.x, v.y);
+    *reinterpret_cast<__nv_bfloat162*>(&w.y) = __floats2bfloat162_rn(v.z, v.w);
+    *reinterpret_cast<uint2*>(o) = w;
+  }
+}
+
+static int make_qkv_map(CUtensorMap* m, const void* ptr, int d, int inner_heads, int g, int b, int s, long st_r,
+                        long st_g, long st_b, long st_s, int rank5) {
+  if (rank5) {
+    uint64_t dims[5] = {(uint64_t)d, (uint64_t)inner_heads, (uint64_t)g, (uint64_t)b, (uint64_t)s};
+    uint64_t str[4] = {(uint64_t)st_r * 2, (uint64_t)st_g * 2, (uint64_t)st_b * 2, (uint64_t)st_s * 2};
+    uint32_t box[5] = {64, 1, 1, 1, FB_T};
+    for (int i = 0; i < 4; ++i) if (str[i] == 0 || (str[i] & 15)) str[i] = (uint64_t)d * 2;
+    return make_tmap(m, ptr, 2, 5, dims, str, box, 3);
+  }
+  uint64_t dims[4] = {(uint64_t)d, (uint64_t)g, (uint64_t)b, (uint64_t)s};
+  uint64_t str[3] = {(uint64_t)st_g * 2, (uint64_t)st_b * 2, (uint64_t)st_s * 2};
+  uint32_t box[4] = {64, 1, 1, FB_T};
+  for (int i = 0; i < 3; ++i) if (str[i] == 0 || (str[i] & 15)) str[i] = (uint64_t)d * 2;
+  return make_tmap(m, ptr, 2, 4, dims, str, box, 3);
+}
+
+}  // namespace kb
+
+using namespace kb;
+
+// Scratch: `work` must hold (sq*b*hq*d + 2*skv*b*g*d + b*hq*sq) floats; it is zeroed here.
+extern "C" long kb_flash_attn_bwd_scratch_floats(int sq, int skv, int b, int g, int rep, int d) {
+  return (long)sq * b * g * rep * d + 2L * skv * b * g * d + (long)b * g * rep * sq;
+}
+
+// q: view [sq,b,g,rep,d]; k,v: views [skv,b,g,d]; o, dO: [sq,b,hq,d] contiguous; lse [b,hq,sq].
+// dq/dk/dv: destination views with the same geometry as q/k/v (strides in elements).
+extern "C" int kb_flash_attn_bwd(const void* q, long qs_s, long qs_b, long qs_g, long qs_r, const void* k, long ks_s,
+                                 long ks_b, long ks_g, const void* v, long vs_s, long vs_b, long vs_g, const void* o,
+                                 const void* dO, const float* lse, void* dq, long dqs_s, long dqs_b, long dqs_g,
+                                 long dqs_r, void* dk, long dks_s, long dks_b, long dks_g, void* dv, long dvs_s,
+                                 long dvs_b, long dvs_g, float* work, int sq, int skv, int b, int g, int rep, int d,
+                                 float scale, int causal, int q_offset, int* status, cudaStream_t stream) {
+  if (d != FB_T || sq <= 0 || skv <= 0) return ST_BAD_ARG;
+  const int hq = g * rep;
+  const long n_dq = (long)sq * b * hq * d, n_dkv = (long)skv * b * g * d;
+  float* dq_acc = work;
+  float* dk_acc = dq_acc + n_dq;
+  float* dv_acc = dk_acc + n_dkv;
+  float* delta = dv_acc + n_dkv;
+  cudaError_t e = cudaMemsetAsync(work, 0, sizeof(float) * (n_dq + 2 * n_dkv), stream);
+  if (e != cudaSuccess) return 1000 + (int)e;
+  {
+    const long rows = (long)sq * b * hq;
+    long blocks = (rows * 32 + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    attn_delta_kernel<<<(int)blocks, 256, 0, stream>>>((const __nv_bfloat16*)dO, (const __nv_bfloat16*)o, delta, sq, b, hq);
+  }
+  CUtensorMap tmQ, tmK, tmV, tmDO;
+  int rc = make_qkv_map(&tmQ, q, d, rep, g, b, sq, qs_r, qs_g, qs_b, qs_s, 1);
+  if (rc) return rc;
+  rc = make_qkv_map(&tmK, k, d, 1, g, b, skv, 0, ks_g, ks_b, ks_s, 0);
+  if (rc) return rc;
+  rc = make_qkv_map(&tmV, v, d, 1, g, b, skv, 0, vs_g, vs_b, vs_s, 0);
+  if (rc) return rc;
+  rc = make_qkv_map(&tmDO, dO, d, 1, hq, b, sq, 0, d, (long)hq * d, (long)b * hq * d, 0);
+  if (rc) return rc;
+  BwdParams p;
+  p.lse = lse; p.delta = delta; p.dq_acc = dq_acc; p.dk_acc = dk_acc; p.dv_acc = dv_acc;
+  p.sq = sq; p.skv = skv; p.b = b; p.hq = hq; p.rep = rep; p.q_offset = q_offset; p.causal = causal;
+  p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
+  static bool configured = false;
+  if (!configured) {
+    e = cudaFuncSetAttribute(flash_attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FbSmem::TOTAL);
+    if (e != cudaSuccess) return 1000 + (int)e;
+    configured = true;
+  }
+  int n_kv = (skv + FB_T - 1) / FB_T;
+  if (causal) {
+    const int last = q_offset + sq;               // keys >= last are seen by no query
+    const int lim = (last + FB_T - 1) / FB_T;
+    if (lim < n_kv) n_kv = lim > 0 ? lim : 0;
+  }
+  if (n_kv > 0) {
+    dim3 grid(n_kv, hq, b);
+    flash_attn_bwd_kernel<<<grid, FB_THREADS, FbSmem::TOTAL, stream>>>(tmQ, tmK, tmV, tmDO, p);
+  }
+  auto conv = [&](const float* acc, void* out, long n, int G, int R, long s_s, long s_b, long s_g, long s_r) {
+    long nvec = n / 4;
+    long blocks = (nvec + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    attn_convert_kernel<<<(int)blocks, 256, 0, stream>>>(acc, (__nv_bfloat16*)out, nvec, b, G, R, s_s, s_b, s_g, s_r);
+  };
+  conv(dq_acc, dq, n_dq, g, rep, dqs_s, dqs_b, dqs_g, dqs_r);
+  conv(dk_acc, dk, n_dkv, g, 1, dks_s, dks_b, dks_g, 0);
+  conv(dv_acc, dv, n_dkv, g, 1, dvs_s, dvs_b, dvs_g, 0);
+  e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 2000 + (int)e;
+}

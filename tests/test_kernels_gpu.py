@@ -200,3 +200,49 @@ def test_flash_attention_forward_offsets():
         want, lse_w = ref.attention_fwd(q.float(), k.float(), v.float(), d ** -0.5, True, cid * c, (cid + 1) * c)
         assert _rel(out, want) < 1e-2
         torch.testing.assert_close(lse, lse_w, rtol=1e-3, atol=1e-3)
+
+
+@pytest.mark.parametrize("s,b,g,rep", [(256, 1, 1, 1), (512, 2, 2, 3), (1000, 1, 1, 3)])
+def test_flash_attention_backward(s, b, g, rep):
+    KC = _K()
+    from kareus_b200.kernels import attention_cuda, ref
+    if not (attention_cuda.have_native() and hasattr(KC.lib(), "kb_flash_attn_bwd")):
+        pytest.skip("native attention backward not built")
+    d = 128
+    packed = torch.randn(s, b, g, (rep + 2) * d, device="cuda").bfloat16()
+    q = packed[..., : rep * d].unflatten(-1, (rep, d))
+    k = packed[..., rep * d:(rep + 1) * d]
+    v = packed[..., (rep + 1) * d:]
+    out, lse = attention_cuda.forward(q, k, v, d ** -0.5, True, 0, None)
+    do = torch.randn_like(out)
+    gbase = torch.full((s, b, g, (rep + 2) * d), float("nan"), device="cuda", dtype=torch.bfloat16)
+    dq = gbase[..., : rep * d].unflatten(-1, (rep, d))
+    dk = gbase[..., rep * d:(rep + 1) * d]
+    dv = gbase[..., (rep + 1) * d:]
+    attention_cuda.backward(do, q, k, v, out, lse, d ** -0.5, True, 0, None, (dq, dk, dv))
+    KC.check_status()
+    o_ref, lse_ref = ref.attention_fwd(q.float(), k.float(), v.float(), d ** -0.5, True)
+    wq, wk, wv = ref.attention_bwd(do.float(), q.float(), k.float(), v.float(), o_ref, lse_ref, d ** -0.5, True)
+    assert not torch.isnan(gbase.float()).any()
+    assert _rel(dq, wq) < 2e-2 and _rel(dk, wk) < 2e-2 and _rel(dv, wv) < 2e-2
+
+
+def test_flash_attention_backward_offsets():
+    KC = _K()
+    from kareus_b200.kernels import attention_cuda, ref
+    if not (attention_cuda.have_native() and hasattr(KC.lib(), "kb_flash_attn_bwd")):
+        pytest.skip("native attention backward not built")
+    d, c = 128, 192
+    q = torch.randn(c, 2, 2, 2, d, device="cuda").bfloat16()
+    k = torch.randn(4 * c, 2, 2, d, device="cuda").bfloat16()
+    v = torch.randn(4 * c, 2, 2, d, device="cuda").bfloat16()
+    for cid in (0, 2):
+        out, lse = attention_cuda.forward(q, k, v, d ** -0.5, True, cid * c, (cid + 1) * c)
+        do = torch.randn_like(out)
+        dq, dk, dv = attention_cuda.backward(do, q, k, v, out, lse, d ** -0.5, True, cid * c, (cid + 1) * c)
+        KC.check_status()
+        o_ref, lse_ref = ref.attention_fwd(q.float(), k.float(), v.float(), d ** -0.5, True, cid * c, (cid + 1) * c)
+        wq, wk, wv = ref.attention_bwd(do.float(), q.float(), k.float(), v.float(), o_ref, lse_ref, d ** -0.5, True,
+                                       cid * c, (cid + 1) * c)
+        assert _rel(dq, wq) < 2e-2 and _rel(dk, wk) < 2e-2 and _rel(dv, wv) < 2e-2
+        assert dk[(cid + 1) * c:].abs().max().item() == 0

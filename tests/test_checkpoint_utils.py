@@ -1,0 +1,81 @@
+"""Checkpoint layout (keys, prepended layer axis, TP axes, SwiGLU split), resharding load, utils."""
+import json
+
+import torch
+
+from kareus_b200.config import ParallelConfig, get_model_config
+from kareus_b200.models import checkpoint as ck
+from kareus_b200.models.llama import GPTModel
+from kareus_b200.utils.debug import nvtx_range, save_tensors
+from kareus_b200.utils.timers import Timers
+
+
+class _FakeComm:
+    """CommFactory stand-in that reports a TP size without process groups."""
+    heap = None
+
+    def __init__(self, tp, rank):
+        self.tp, self.rank = tp, rank
+
+    def _args(self, axis):
+        return (None, self.tp, self.rank) if axis == "tp" else (None, 1, 0)
+
+    def make(self, cls, axis, name):
+        g, w, r = self._args(axis)
+        return cls(g, w, r, name=name)
+
+
+def test_sharded_state_dict_contract():
+    cfg = get_model_config("tiny")
+    m = GPTModel(cfg, ParallelConfig(tp=2, tp_comm="sp"), comm=_FakeComm(2, 1), dtype="fp32")
+    sd = ck.sharded_state_dict(m, tp_rank=1, tp=2)
+    by = {}
+    for s in sd:
+        by.setdefault(s.key, []).append(s)
+    q = by["decoder.layers.self_attention.linear_qkv.weight"]
+    assert len(q) == cfg.num_layers and q[1].prepend_axis_num == 1
+    assert q[1].global_shape[0] == cfg.num_layers and q[1].global_offset[0] == 1
+    assert q[0].global_offset[1] == q[0].local_shape[1] and q[0].axis_fragmentations == (cfg.num_layers, 2, 1)
+    pj = by["decoder.layers.self_attention.linear_proj.weight"][0]
+    assert pj.axis_fragmentations == (cfg.num_layers, 1, 2) and pj.global_offset[2] == pj.local_shape[2]
+    fc1 = by["decoder.layers.mlp.linear_fc1.weight"]
+    assert len(fc1) == 2 * cfg.num_layers and fc1[0].axis_fragmentations == (cfg.num_layers, 4, 1)
+    f_local = cfg.ffn_hidden_size // 2
+    assert fc1[0].global_offset[1] == f_local and fc1[1].global_offset[1] == cfg.ffn_hidden_size + f_local
+    assert by["decoder.final_layernorm.weight"][0].replica_id == 1
+    assert "embedding.word_embeddings.weight" in by and "output_layer.weight" in by
+
+
+def test_save_tp2_load_tp1_and_back(tmp_path):
+    cfg = get_model_config("tiny")
+    shards = [GPTModel(cfg, ParallelConfig(tp=2), comm=_FakeComm(2, r), dtype="fp32", seed=3) for r in range(2)]
+    for r, m in enumerate(shards):
+        ck.save(m, tmp_path / "ckpt", rank=r, tp_rank=r, tp=2, common={"step": 7})
+    assert json.loads((tmp_path / "ckpt" / "metadata.json").read_text())["sharded_backend"] == "torch_dist"
+    full = GPTModel(cfg, ParallelConfig(tp=1), dtype="fp32", seed=99)
+    common = ck.load(full, tmp_path / "ckpt", tp_rank=0, tp=1)
+    assert common["step"] == 7
+    l0 = full.decoder.layers[0]
+    want_qkv = torch.cat([s.decoder.layers[0].qkv.weight for s in shards], 0)
+    torch.testing.assert_close(l0.qkv.weight.data, want_qkv)
+    gates = [s.decoder.layers[0].fc1.weight.chunk(2, 0)[0] for s in shards]
+    ups = [s.decoder.layers[0].fc1.weight.chunk(2, 0)[1] for s in shards]
+    torch.testing.assert_close(l0.fc1.weight.data, torch.cat(gates + ups, 0))
+    torch.testing.assert_close(l0.proj.weight.data, torch.cat([s.decoder.layers[0].proj.weight for s in shards], 1))
+    # and back: write TP1, load into a TP2 shard
+    ck.save(full, tmp_path / "ckpt1", rank=0)
+    again = GPTModel(cfg, ParallelConfig(tp=2), comm=_FakeComm(2, 1), dtype="fp32", seed=5)
+    ck.load(again, tmp_path / "ckpt1", tp_rank=1, tp=2)
+    torch.testing.assert_close(again.decoder.layers[1].fc2.weight.data, shards[1].decoder.layers[1].fc2.weight.data)
+    torch.testing.assert_close(again.embedding.weight.data, shards[1].embedding.weight.data)
+
+
+def test_debug_and_timers(tmp_path):
+    with nvtx_range("x", enabled=True):
+        pass
+    p = save_tensors({"a": torch.ones(2)}, tmp_path, tp_rank=1, pp_rank=0)
+    assert p.name == "tensors_tp1_pp0.pt" and torch.load(p)["a"].sum() == 2
+    t = Timers(sync=False)
+    t.on_instruction_begin("forward"); t.on_instruction_end("forward")
+    out = t.export(tmp_path, 3, 1)
+    assert out.name == "instructions-3-1.csv" and "forward-compute" in out.read_text()

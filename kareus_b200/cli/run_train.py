@@ -1,0 +1,119 @@
+"""Phase 3: training run under a plan, with the reference's method names and output layout.
+
+    torchrun --nproc-per-node 8 -m kareus_b200.cli.run_train --method kareus --model llama3.2_3b \
+        --tp 8 --pp 1 --mbs 8 --seq 4096 --gbs 64 --steps 30 \
+        --freqs plans/freqs_pipeline_02495.py --scheds plans/scheds_pipeline_02495.py
+
+Methods: ``megatron`` (one nanobatch, no plan), ``nanobatch`` (two nanobatches, fixed schedule),
+``perseus`` / ``nanobatch_perseus`` (frequency plan only), ``kareus`` (frequency + overlap plan).
+Each rank writes ``<out>/<model>/<cp.._tp.._mbs.._seq..>/<method>/zeus_monitor_global_rank-G_local_rank-L.txt``
+with the windows ``training_step`` and ``training_step_fwd_bwd_step_call``.
+"""
+from __future__ import annotations
+
+import argparse
+import os
+from pathlib import Path
+
+import torch
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--method", default="kareus",
+                    choices=["megatron", "nanobatch", "perseus", "nanobatch_perseus", "kareus"])
+    ap.add_argument("--model", default="llama3.2_3b")
+    ap.add_argument("--tp", type=int, default=1)
+    ap.add_argument("--cp", type=int, default=1)
+    ap.add_argument("--pp", type=int, default=1)
+    ap.add_argument("--mbs", type=int, default=8)
+    ap.add_argument("--gbs", type=int, default=64)
+    ap.add_argument("--seq", type=int, default=4096)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--tp-comm", default="sp_fused")
+    ap.add_argument("--comm-backend", default="kernel")
+    ap.add_argument("--freqs", default=None, help="freqs_pipeline_*.py (served in process, or by --pfo-url)")
+    ap.add_argument("--scheds", default=None, help="scheds_pipeline_*.py")
+    ap.add_argument("--pfo-url", default=None, help="http://MASTER_ADDR:7787 of a running plan server")
+    ap.add_argument("--clock-mode", default="advisory", choices=["off", "advisory", "locked"])
+    ap.add_argument("--out", default="nemo_experiments")
+    ap.add_argument("--enable-power-monitor", action="store_true")
+    ap.add_argument("--enable-timers", action="store_true")
+    ap.add_argument("--recompute-layers", type=int, default=4)
+    a = ap.parse_args(argv)
+
+    import torch.distributed as dist
+    from ..config import ParallelConfig, TrainConfig, get_model_config
+    from ..energy import EnergyMonitor, FrequencyController, PipelineFrequencyOptimizer, PointSolution, PowerMonitor
+    from ..parallel.mesh import Mesh, init_distributed
+    from ..plan import PipelineCommScheduler, parse_schedule_file
+    from ..train.trainer import Trainer, synthetic_batch
+    from ..utils.timers import Timers
+
+    rank, world, local = init_distributed()
+    cuda = torch.cuda.is_available()
+    device = torch.device("cuda", local) if cuda else torch.device("cpu")
+    if cuda:
+        torch.cuda.set_device(device)
+    dp = world // (a.tp * a.cp * a.pp)
+    nano = 1 if a.method in ("megatron", "perseus") else 2
+    tp_comm = a.tp_comm if a.tp > 1 else "allreduce"
+    par = ParallelConfig(tp=a.tp, cp=a.cp, pp=a.pp, dp=dp, num_nanobatches=nano, tp_comm=tp_comm,
+                         comm_backend=a.comm_backend if cuda else "nccl", recompute=True)
+    mesh = Mesh(tp=a.tp, cp=a.cp, dp=dp, pp=a.pp)
+    cfg = get_model_config(a.model)
+    tc = TrainConfig(micro_batch_size=a.mbs, global_batch_size=a.gbs, seq_len=a.seq,
+                     dtype="bf16" if cuda else "fp32")
+    tag = f"cp{a.cp}_tp{a.tp}_mbs{a.mbs}_seq{a.seq}"
+    out = Path(a.out) / a.model / tag / a.method
+    out.mkdir(parents=True, exist_ok=True)
+    monitor = EnergyMonitor([local] if cuda else [0],
+                            log_file=str(out / f"zeus_monitor_global_rank-{rank}_local_rank-{local}.txt")) \
+        if cuda else None
+    M = tc.num_microbatches(dp)
+    ctl = FrequencyController(local, a.clock_mode)
+    freq_client = None
+    if a.method in ("perseus", "nanobatch_perseus", "kareus") and (a.freqs or a.pfo_url):
+        tpr, tpd = mesh.folded_tp_rank()
+        freq_client = PipelineFrequencyOptimizer(rank, mesh.dp_rank, mesh.pp_rank, tpr, local, dp, a.pp, tpd, world, ctl,
+                                                 server_url=a.pfo_url,
+                                                 solution=PointSolution.from_file(a.freqs) if a.freqs else None)
+    sched = None
+    if a.method == "kareus" and a.scheds:
+        parsed = [None]
+        if rank == 0:
+            parsed[0] = parse_schedule_file(a.scheds, True, a.cp > 1)
+        if world > 1:
+            dist.broadcast_object_list(parsed, src=0)      # rank 0 parses, everyone receives
+        sched = PipelineCommScheduler.from_parsed(parsed[0], mesh.pp_rank, M, True, a.cp > 1)
+    heap = None
+    if cuda and a.tp > 1 and (par.comm_backend == "kernel" or par.tp_comm == "sp_fused"):
+        from ..parallel.symm_heap import SymmetricHeap
+        heap = SymmetricHeap.create(mesh.group("tp"), device)
+    trainer = Trainer(cfg, par, tc, mesh=mesh, device=device, monitor=monitor, freq_client=freq_client,
+                      comm_scheduler=sched, heap=heap, recompute_layers=a.recompute_layers)
+    timers = Timers() if a.enable_timers else None
+    if timers is not None:
+        trainer._hooks.append(timers)
+    power = PowerMonitor(local).start() if (a.enable_power_monitor and cuda) else None
+    try:
+        for step in range(a.steps):
+            batch = synthetic_batch(cfg, tc, M, seed=step, cp=a.cp, cp_rank=mesh.cp_rank)
+            loss = trainer.train_step(batch, loss_denominator=float(a.gbs * a.seq))
+            if rank == 0:
+                print(f"step {step} loss {loss:.4f}", flush=True)
+    finally:
+        ctl.close()
+        if power is not None:
+            power.stop()
+            power.dump(out / f"power_monitor_global_rank-{rank}_local_rank-{local}.txt")
+        if timers is not None:
+            timers.export(out, rank, local)
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -672,3 +672,34 @@ extern "C" int kb_sumsq(const void* x, long n, int is_f32, float* out, cudaStrea
   else sumsq_bf16_kernel<<<grid_for(n, 256, 148 * 8), 256, 0, st>>>((const __nv_bfloat16*)x, n, out);
   KB_CHECK_LAUNCH();
 }
+
+// ----------------------------------------------------------------------------- allocation-free RMSNorm backward
+// Declared in kareus_b200_noalloc.h.  Same kernels as kb_rmsnorm_bwd; the per-CTA partial sums of
+// the weight gradient live in a fixed device array instead of caller-provided scratch.
+namespace kb {
+constexpr int NOALLOC_MAX_H = 8192;
+constexpr int NOALLOC_MAX_CTAS = 148;
+static __device__ __align__(256) float g_rmsnorm_bwd_partial[NOALLOC_MAX_CTAS * NOALLOC_MAX_H];
+static float* g_rmsnorm_bwd_partial_addr[64] = {nullptr};
+}  // namespace kb
+
+extern "C" int kb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const float* rstd, const void* w, void* dx,
+                                      float* dw, int rows, int H, cudaStream_t st) {
+  if (rows <= 0 || H < 512 || H > NOALLOC_MAX_H || (H % 8) != 0) return 7;   // outside the supported range
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 7;
+  if (g_rmsnorm_bwd_partial_addr[dev] == nullptr) {
+    // once per device, with that device current: the symbol's name is only a host-side handle,
+    // the kernel needs the device address behind it
+    float* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_rmsnorm_bwd_partial);
+    if (e != cudaSuccess || ptr == nullptr) return 1000 + static_cast<int>(e);
+    g_rmsnorm_bwd_partial_addr[dev] = ptr;
+  }
+  float* partial = g_rmsnorm_bwd_partial_addr[dev];
+  const int grid = rows < NOALLOC_MAX_CTAS ? rows : NOALLOC_MAX_CTAS;
+  rmsnorm_bwd_kernel<<<grid, NORM_THREADS, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, rstd,
+                                                    (const __nv_bfloat16*)w, (__nv_bfloat16*)dx, partial, rows, H);
+  rmsnorm_dw_reduce_kernel<<<(H + 255) / 256, 256, 0, st>>>(partial, dw, grid, H);
+  KB_CHECK_LAUNCH();
+}

@@ -119,6 +119,12 @@ reducescatter_kernel(PeerCtx c, uint64_t off, long shard_elems, __nv_bfloat16* _
   peer_barrier(c, blockIdx.x, epoch * 4 + 2, &ok);
 }
 
+// Stream-ordered barrier among ranks: one CTA signals every peer and waits for all of them.
+__global__ void barrier_kernel(PeerCtx c, uint64_t epoch) {
+  __shared__ int ok;
+  peer_barrier(c, 0, epoch * 4 + 3, &ok);
+}
+
 // A wait that nothing satisfies: used by the tests of the bounded-wait path.  `slot` is a flag
 // nobody writes; the kernel polls it for at most `limit_ns`, records ST_TIMEOUT_PEER and returns.
 __global__ void wait_flag_kernel(const uint64_t* slot, uint64_t want, uint64_t limit_ns, int* status) {
@@ -169,6 +175,12 @@ extern "C" int kb_reducescatter(void* const* bases, int rank, int world, uint64_
   if (world < 1 || world > MAX_PEERS || (off & 15) || ((shard_elems * 2) & 15)) return ST_BAD_ARG;
   reducescatter_kernel<<<clamp_grid(sm_num), clamp_block(block), 0, st>>>(
       make_ctx(bases, rank, world, flag_off, status), off, shard_elems, reinterpret_cast<__nv_bfloat16*>(out), epoch);
+  KB_RET_LAUNCH();
+}
+extern "C" int kb_peer_barrier(void* const* bases, int rank, int world, uint64_t flag_off, uint64_t epoch, int* status,
+                               cudaStream_t st) {
+  if (world < 1 || world > MAX_PEERS) return ST_BAD_ARG;
+  barrier_kernel<<<1, 32, 0, st>>>(make_ctx(bases, rank, world, flag_off, status), epoch);
   KB_RET_LAUNCH();
 }
 extern "C" int kb_wait_flag(const void* slot, uint64_t want, uint64_t limit_ns, int* status, cudaStream_t st) {

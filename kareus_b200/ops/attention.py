@@ -162,7 +162,11 @@ class AttentionOp(GraphOperator):
             self.ag_kv = comm.make(AllGatherKV, "cp", f"{name}.ag_kv")
             self.ag_kv_bwd = comm.make(AllGatherKV, "cp", f"{name}.ag_kv_bwd")
             self.rs_kv = comm.make(ReduceScatterKV, "cp", f"{name}.rs_kv")
-        self.ring = None  # set by parallel.ring_attention when cp_comm == "ring"
+        self.ring = None
+        if self.cp > 1 and cp_comm == "ring":
+            from ..parallel.ring_attention import RingAttention
+            self.ring = RingAttention(comm._args("cp")[0], self.cp, self.cp_rank, heap=getattr(comm, "heap_cp", None),
+                                      name=f"{name}.ring")
 
     # graph --------------------------------------------------------------------
     def forward_specs(self):
@@ -189,7 +193,7 @@ class AttentionOp(GraphOperator):
     def forward(self, ctx, q, k, v):
         s, b = q.shape[0], q.shape[1]
         if self.cp > 1 and self.cp_comm == "ring":
-            out, lse = self.ring.forward(q, k, v, self.scale)
+            out, lse = self.ring.forward(q, k, v, self.scale, nb=ctx.nb_index)
             if ctx.requires_grad:
                 ctx.save_for_backward(q, k, v, out, lse)
             return (out.reshape(s, b, -1),)
@@ -224,7 +228,7 @@ class AttentionOp(GraphOperator):
         do = dout.reshape(s, b, q_heads(q), self.d)
         base, dq, dk, dv = alloc_packed_grads(q, k)
         if self.cp > 1:
-            self.ring.backward(do, q, k, v, out, lse, self.scale, out=(dq, dk, dv))
+            self.ring.backward(do, q, k, v, out, lse, self.scale, out_grads=(dq, dk, dv), nb=ctx.nb_index)
         else:
             K.attention_bwd(do, q, k, v, out, lse, self.scale, causal=True, out=(dq, dk, dv))
         base3 = base.view(s, b, -1)

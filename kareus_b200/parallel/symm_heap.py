@@ -99,6 +99,8 @@ class SymmetricHeap:
         L.kb_allgather.argtypes = [P, I, I, U64, U64, LNG, U64, I, I, P, P]
         L.kb_reducescatter.argtypes = [P, I, I, U64, U64, LNG, P, U64, I, I, P, P]
         L.kb_wait_flag.argtypes = [P, U64, U64, P, P]
+        L.kb_peer_barrier.argtypes = [P, I, I, U64, U64, P, P]
+        L.kb_peer_barrier.restype = c_int
         for n in ("kb_heap_alloc", "kb_ipc_get_handle", "kb_ipc_open", "kb_ipc_close", "kb_heap_free", "kb_allreduce",
                   "kb_allgather", "kb_reducescatter", "kb_wait_flag"):
             getattr(L, n).restype = c_int
@@ -127,6 +129,26 @@ class SymmetricHeap:
             ch.buffers[name] = (off, nbytes)
             cur = (off, nbytes)
         return cur[0], self.local[cur[0]:cur[0] + nbytes]
+
+    def peer_view(self, rank: int, off: int, shape, dtype) -> torch.Tensor:
+        """The same buffer in rank ``rank``'s heap, addressed through the peer mapping.  Kernels of this
+        package may read it (plain or TMA loads without multicast); never hand it to a library kernel."""
+        if rank == self.rank:
+            return self.view(off, shape, dtype)
+        n = 1
+        for s_ in shape:
+            n *= s_
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        raw = torch.as_tensor(_Raw(self.bases[rank] + off, nbytes), device=self.device)
+        return raw.view(dtype).view(shape)
+
+    def barrier(self, ch: Channel) -> None:
+        """Stream-ordered barrier among the ranks (a one-CTA kernel on the current stream)."""
+        ch.epoch += 1
+        st = KC.status_word(self.device)
+        KC._check(self.lib.kb_peer_barrier(self._bases_arr, self.rank, self.world, ch.flag_off, ch.epoch,
+                                           st.data_ptr(), KC._stream()), "peer barrier")
+        KC._count()
 
     def view(self, off: int, shape, dtype) -> torch.Tensor:
         n = 1

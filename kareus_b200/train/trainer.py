@@ -45,7 +45,7 @@ def stage_layer_range(cfg: ModelConfig, pp: int, pp_rank: int) -> range:
 class Trainer:
     def __init__(self, model_cfg: ModelConfig, par: ParallelConfig, train_cfg: TrainConfig,
                  mesh: Optional[Mesh] = None, device=None, dtype: Optional[str] = None,
-                 monitor=None, freq_client=None, comm_scheduler=None, heap=None,
+                 monitor=None, freq_client=None, comm_scheduler=None, heap=None, heap_cp=None,
                  recompute_layers: Optional[int] = None, sync: str = "partition_end"):
         self.model_cfg, self.par, self.cfg = model_cfg, par, train_cfg
         self.mesh = mesh or Mesh(par.tp, par.cp, par.dp, par.pp)
@@ -54,6 +54,7 @@ class Trainer:
         self.monitor, self.freq_client, self.comm_scheduler = monitor, freq_client, comm_scheduler
         mesh = self.mesh
         comm = CommFactory(mesh, par.comm_backend, heap=heap)
+        comm.heap_cp = heap_cp        # symmetric heap of the context-parallel group (ring attention)
         self.model = GPTModel(model_cfg, par, mesh=mesh, comm=comm, dtype=self.dtype, device=self.device,
                               seed=train_cfg.seed, pre_process=mesh.is_first_stage,
                               post_process=mesh.is_last_stage,

@@ -119,6 +119,31 @@ def test_model_modes(heap, rank, world, dev):
             assert abs(a - b) < 0.05, (k, v, base)
 
 
+def test_ring_attention(heap, rank, world, dev):
+    """CP over the GPUs: K/V tiles of other ranks are read by the attention kernels from peer memory."""
+    from kareus_b200.config import ParallelConfig, TrainConfig, get_model_config
+    from kareus_b200.parallel.mesh import Mesh
+    from kareus_b200.train.trainer import Trainer, synthetic_batch
+    from kareus_b200.kernels import cuda as KC
+    cfg = get_model_config("tiny128")
+    tc = TrainConfig(micro_batch_size=2, global_batch_size=4, seq_len=1024, warmup_steps=0, lr=1e-3)
+    mesh = Mesh(cp=world)
+    losses = {}
+    for cp_comm in ("all_gather", "ring"):
+        par = ParallelConfig(cp=world, num_nanobatches=2, recompute=True, cp_comm=cp_comm)
+        tr = Trainer(cfg, par, tc, mesh=mesh, device=dev, heap_cp=heap if cp_comm == "ring" else None)
+        batch = synthetic_batch(cfg, tc, tr.num_microbatches, seed=3, cp=world, cp_rank=mesh.cp_rank)
+        losses[cp_comm] = [tr.train_step(batch, loss_denominator=float(4 * 1024)) for _ in range(3)]
+        torch.cuda.synchronize()
+        KC.check_status()
+        del tr
+    if rank == 0:
+        print("cp losses:", losses, flush=True)
+    for a, b in zip(losses["ring"], losses["all_gather"]):
+        assert abs(a - b) < 0.05, losses
+    assert losses["ring"][-1] < losses["ring"][0]
+
+
 def main():
     from kareus_b200.parallel.mesh import init_distributed
     from kareus_b200.parallel.symm_heap import SymmetricHeap
@@ -131,6 +156,8 @@ def main():
         test_heap_collectives(heap, rank, world, dev)
     if which in ("all", "fused"):
         test_fused_gemm_collectives(heap, rank, world, dev)
+    if which in ("all", "ring"):
+        test_ring_attention(heap, rank, world, dev)
     if which in ("all", "wait"):
         test_bounded_wait(heap, dev)
     if which in ("all", "model"):

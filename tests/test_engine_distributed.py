@@ -6,7 +6,7 @@ import torch.distributed as dist
 from dist_utils import run_distributed
 
 
-def _worker(rank, world, tp, cp, tp_comm, n, recompute, with_plan):
+def _worker(rank, world, tp, cp, tp_comm, n, recompute, with_plan, cp_comm="all_gather"):
     from kareus_b200.config import ParallelConfig, get_model_config
     from kareus_b200.models.llama import GPTModel
     from kareus_b200.models.oracle import OracleLlama, load_from_shards, shard_of_oracle_grad
@@ -15,7 +15,7 @@ def _worker(rank, world, tp, cp, tp_comm, n, recompute, with_plan):
     from kareus_b200.plan import PipelineCommScheduler, uniform_schedule, CommConfig
 
     cfg = get_model_config("tiny")
-    par = ParallelConfig(tp=tp, cp=cp, num_nanobatches=n, tp_comm=tp_comm, recompute=recompute)
+    par = ParallelConfig(tp=tp, cp=cp, num_nanobatches=n, tp_comm=tp_comm, recompute=recompute, cp_comm=cp_comm)
     mesh = Mesh(tp=tp, cp=cp)
     model = GPTModel(cfg, par, mesh=mesh, dtype="fp64", seed=0)
     if with_plan:
@@ -121,3 +121,8 @@ def test_cp2_all_gather():
 
 def test_tp2_cp2_sp():
     run_distributed(_worker, 4, 2, 2, "sp", 2, True, False)
+
+
+def test_cp2_ring_attention():
+    """Pull-based ring attention (chunk schedule + log-sum-exp merge + dKV reduce-scatter) on gloo."""
+    run_distributed(_worker, 2, 1, 2, "allreduce", 2, True, False, "ring")

@@ -19,7 +19,7 @@ def _run(which, n):
     assert "multigpu worker ok" in r.stdout
 
 
-@pytest.mark.parametrize("which", ["collectives", "fused", "wait", "model"])
+@pytest.mark.parametrize("which", ["collectives", "fused", "ring", "wait", "model"])
 def test_two_gpus(which):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")

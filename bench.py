@@ -104,6 +104,8 @@ def main() -> int:
     ap.add_argument("--tp-comm", default=os.environ.get("KAREUS_TP_COMM", "allreduce"))
     ap.add_argument("--comm-backend", default=os.environ.get("KAREUS_COMM_BACKEND", "nccl"))
     ap.add_argument("--recompute-layers", type=int, default=int(os.environ.get("KAREUS_RECOMPUTE_LAYERS", "4")))
+    ap.add_argument("--comm-sm", type=int, default=int(os.environ.get("KAREUS_COMM_SM", "16")),
+                    help="CTAs given to a collective (plan knob sm_num) when no plan file is loaded")
     ap.add_argument("--skip-e2e", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -135,6 +137,7 @@ def main() -> int:
         from kareus_b200.parallel.symm_heap import SymmetricHeap
         heap = SymmetricHeap.create(mesh.group("tp"), device)
     trainer = Trainer(cfg, par, tc, mesh=mesh, device=device, heap=heap, recompute_layers=args.recompute_layers)
+    trainer.model.decoder.engine.default_shape = (args.comm_sm, 1024)
     M = trainer.num_microbatches
     host_batches = [synthetic_batch(cfg, tc, M, seed=1000 + i) for i in range(2)]
     tokens_per_step = args.gbs * args.seq
@@ -211,7 +214,7 @@ def main() -> int:
             "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights",
             "config": {"model": args.model, "global_batch": args.gbs, "micro_batch": args.mbs, "seq_len": args.seq,
                        "parallelism": f"tp{world}", "nanobatches": args.nano, "tp_comm": par.tp_comm,
-                       "comm_backend": par.comm_backend, "recompute": f"full, {args.recompute_layers} layers per chunk",
+                       "comm_backend": par.comm_backend, "comm_sm": args.comm_sm, "recompute": f"full, {args.recompute_layers} layers per chunk",
                        "optimizer": "AdamW fp32 master, in the timed region",
                        "l2": "inputs larger than L2 (6.4 GB of weights and multi-GB activations per step)"},
             "energy_j_per_step": float(en.item()) / args.steps,

@@ -13,6 +13,7 @@ the linear operator's own context: these nodes share its graph uid.
 from __future__ import annotations
 
 import ctypes
+import re
 from ctypes import c_int, c_uint32, c_uint64, c_void_p
 
 import torch
@@ -44,6 +45,8 @@ class _FusedBase:
     def __init__(self, linear, heap, default_sm: int):
         self.linear, self.heap, self.default_sm = linear, heap, default_sm
         self.name = linear.name + "." + type(self).__name__
+        # one set of heap buffers per call site, shared by all layers (see CollectiveBase.tag)
+        self.tag = re.sub(r"layers\.\d+\.", "", linear.name)
         self._graph_uid = operator_uid(linear)
         self._local = {}
 
@@ -66,7 +69,7 @@ class FusedAGGemm(_FusedBase):
         m, n = ms * world, lin.out_features
         if ms % 128 or x2.dtype != torch.bfloat16:
             raise KC.KernelError(f"fused all-gather GEMM needs bf16 and a multiple of 128 rows per rank, got {ms}")
-        ch = heap.channel(f"{lin.name}/ag_gemm/{nb}")
+        ch = heap.channel(f"{self.tag}/ag_gemm/{nb}")
         off, _ = heap.buffer(ch, "xg", m * k * 2)
         xg = heap.view(off, (m, k), torch.bfloat16)
         xg[rank * ms:(rank + 1) * ms].copy_(x2)
@@ -101,7 +104,7 @@ class FusedGemmRS(_FusedBase):
             raise KC.KernelError(f"fused GEMM reduce-scatter needs bf16 and rows divisible by {world * 128}, got {m}")
         L = _lib()
         tiles_n = L.kb_fused_tiles_n(n)
-        ch = heap.channel(f"{lin.name}/gemm_rs/{nb}")
+        ch = heap.channel(f"{self.tag}/gemm_rs/{nb}")
         stage_off, _ = heap.buffer(ch, "stage", m * n * 2)
         cnt_off, _ = heap.buffer(ch, "cnt", world * (ms // 128) * tiles_n * 4)
         go = self._local_flags(("go", nb), 1)

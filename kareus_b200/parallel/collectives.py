@@ -13,6 +13,7 @@ its symmetric buffers by ``nb``, so two nanobatches never alias each other's sta
 """
 from __future__ import annotations
 
+import re
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
@@ -30,6 +31,9 @@ class CollectiveBase:
         self.backend = backend
         self.heap = heap
         self.name = name or type(self).__name__
+        # heap buffers are shared by the same call site of every layer (layers run one after another
+        # on the ordered side stream), so the tag drops the layer index
+        self.tag = re.sub(r"layers\.\d+\.", "", self.name)
         self.calls = 0
 
     def _use_kernel(self, t, sm_num) -> bool:
@@ -46,7 +50,7 @@ class AllReduce(CollectiveBase):
         if self.world == 1:
             return (x,)
         if self._use_kernel(x, sm_num):
-            return (self.heap.all_reduce(x, nb=nb, sm_num=sm_num, block_size=block_size, tag=self.name),)
+            return (self.heap.all_reduce(x, nb=nb, sm_num=sm_num, block_size=block_size, tag=self.tag),)
         if not x.is_contiguous():
             x = x.contiguous()
         dist.all_reduce(x, group=self.group)
@@ -62,7 +66,7 @@ class AllGather(CollectiveBase):
         if self.world == 1:
             return (x,)
         if self._use_kernel(x, sm_num):
-            return (self.heap.all_gather(x, nb=nb, sm_num=sm_num, block_size=block_size, tag=self.name),)
+            return (self.heap.all_gather(x, nb=nb, sm_num=sm_num, block_size=block_size, tag=self.tag),)
         x = x.contiguous()
         out = torch.empty((x.shape[0] * self.world,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
         dist.all_gather_into_tensor(out, x, group=self.group)
@@ -80,7 +84,7 @@ class ReduceScatter(CollectiveBase):
         if x.shape[0] % self.world:
             raise ValueError(f"{self.name}: dim 0 ({x.shape[0]}) not divisible by group size {self.world}")
         if self._use_kernel(x, sm_num):
-            return (self.heap.reduce_scatter(x, nb=nb, sm_num=sm_num, block_size=block_size, tag=self.name),)
+            return (self.heap.reduce_scatter(x, nb=nb, sm_num=sm_num, block_size=block_size, tag=self.tag),)
         x = x.contiguous()
         out = torch.empty((x.shape[0] // self.world,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
         if x.is_cuda:
@@ -136,7 +140,7 @@ class AllGatherKV(CollectiveBase):
             t = t.contiguous()
             if self._use_kernel(t, sm_num):
                 g = self.heap.all_gather(t, nb=nb, sm_num=sm_num, block_size=block_size,
-                                         tag=self.name + ("_k" if t is k else "_v"))
+                                         tag=self.tag + ("_k" if t is k else "_v"))
             else:
                 g = torch.empty((t.shape[0] * self.world,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
                 dist.all_gather_into_tensor(g, t, group=self.group)
@@ -159,7 +163,7 @@ class ReduceScatterKV(CollectiveBase):
             t = to_rank_order(t, self.world).contiguous()
             if self._use_kernel(t, sm_num):
                 o = self.heap.reduce_scatter(t, nb=nb, sm_num=sm_num, block_size=block_size,
-                                             tag=self.name + ("_k" if t is dk else "_v"))
+                                             tag=self.tag + ("_k" if t is dk else "_v"))
             else:
                 o = torch.empty((t.shape[0] // self.world,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
                 if t.is_cuda:

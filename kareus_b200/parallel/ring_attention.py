@@ -17,6 +17,7 @@ schedule and merge run on the PyTorch statements, which is how the math is teste
 """
 from __future__ import annotations
 
+import re
 from typing import List, Optional, Tuple
 
 import torch
@@ -34,9 +35,10 @@ def chunk_owner(j: int, cp: int) -> Tuple[int, int]:
 
 class RingAttention:
     def __init__(self, group, cp: int, cp_rank: int, heap=None, name: str = "ring"):
-        self.group, self.cp, self.rank, self.heap, self.name = group, cp, cp_rank, heap, name
+        self.group, self.cp, self.rank, self.heap = group, cp, cp_rank, heap
+        self.name = re.sub(r"layers\.\d+\.", "", name)      # heap buffers shared by all layers
         self.rs = ReduceScatterKV(group, cp, cp_rank, backend="kernel" if heap is not None else "nccl", heap=heap,
-                                  name=name + ".rs_dkv")
+                                  name=self.name + ".rs_dkv")
 
     # ------------------------------------------------------------------ K/V publication
     def _publish(self, k, v, nb: int, tag: str) -> List[Tuple[torch.Tensor, torch.Tensor]]:

@@ -188,7 +188,7 @@ class SymmetricHeap:
         KC._check(self.lib.kb_allgather(self._bases_arr, self.rank, self.world, ch.flag_off, off, shard, ch.epoch, sm,
                                         blk, st.data_ptr(), KC._stream()), "allgather")
         KC._count()
-        return out
+        return out.clone()        # callers may keep the result (saved for backward); the buffer is reused
 
     def reduce_scatter(self, x: torch.Tensor, nb: int = 0, sm_num=None, block_size=None, tag: str = "rs") -> torch.Tensor:
         ch = self.channel(f"{tag}/{nb}")

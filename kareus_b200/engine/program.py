@@ -155,13 +155,16 @@ def _shared_comm_stream(device) -> "torch.cuda.Stream":
 
 class PartitionProgram:
     def __init__(self, graph: TensorGraph, num_nanobatches: int, backward: bool,
-                 sync: str = "partition_end"):
+                 sync: str = "partition_end", reverse_nb: bool = False):
         if sync not in ("partition_end", "lazy"):
             raise ValueError(sync)
         self.graph = graph
         self.n = int(num_nanobatches)
         self.backward = backward
         self.sync = sync
+        # sequence-split nanobatches: a later nanobatch's attention backward produces dK/dV for the
+        # earlier ones, so the backward program visits nanobatches last-to-first
+        self.nb_order = list(reversed(range(self.n))) if reverse_nb else list(range(self.n))
         self.trail_key = "bwd_trail" if backward else "fwd_trail"
         self.segments = split_segments(graph.nodes, self.trail_key)
         self.steps = self._form_steps()
@@ -174,7 +177,7 @@ class PartitionProgram:
         steps: List[Step] = []
         prev: Optional[Tuple[int, int]] = None
         for seg in self.segments:
-            for nb in range(self.n):
+            for nb in self.nb_order:
                 st = Step(index=len(steps), key=seg.key, nb=nb, segment=seg.index,
                           compute=seg.compute, slots=build_overlap_slots(seg.compute))
                 if prev is not None:

@@ -94,15 +94,17 @@ class TransformerLayer(nn.Module):
 class TransformerBlock(nn.Module):
     def __init__(self, cfg: ModelConfig, par: ParallelConfig, comm: CommFactory, layer_range: range,
                  dtype, device, seed: int = 0, recompute_layers: Optional[int] = None,
-                 sync: str = "partition_end"):
+                 sync: str = "partition_end", seq_split: bool = False):
         super().__init__()
-        if par.tp_comm != "allreduce" and cfg.hidden_dropout > 0 and par.tp > 1:
-            pass  # dropout under SP draws per-rank masks from the per-operator seed: allowed
         self.cfg, self.par = cfg, par
         self.layers = nn.ModuleList(
             TransformerLayer(cfg, par, comm, i, dtype, device, seed=seed * 1000 + i) for i in layer_range)
+        if seq_split:
+            for l in self.layers:
+                l.core_attn.seq_nano = par.num_nanobatches
         self.engine = BlockEngine([l.operators() for l in self.layers], par.num_nanobatches,
-                                  recompute=par.recompute, recompute_layers=recompute_layers, sync=sync)
+                                  recompute=par.recompute, recompute_layers=recompute_layers, sync=sync,
+                                  seq_split=seq_split)
 
     def set_scheduler(self, scheduler) -> None:
         self.engine.scheduler = scheduler
@@ -271,7 +273,7 @@ class GPTModel(nn.Module):
                  comm: Optional[CommFactory] = None, dtype="bf16", device=None, seed: int = 42,
                  pre_process: bool = True, post_process: bool = True,
                  layer_range: Optional[range] = None, recompute_layers: Optional[int] = None,
-                 sync: str = "partition_end"):
+                 sync: str = "partition_end", micro_batch_size: Optional[int] = None):
         super().__init__()
         self.cfg = cfg
         self.par = par or ParallelConfig()
@@ -282,8 +284,13 @@ class GPTModel(nn.Module):
         self.pre_process, self.post_process = pre_process, post_process
         layer_range = layer_range if layer_range is not None else range(cfg.num_layers)
         self.embedding = VocabParallelEmbedding(cfg, self.par, self.comm, dt, device, seed + 1) if pre_process else None
+        # nanobatches split the batch when it is large enough, otherwise the sequence (MBS = 1)
+        d = self.par.nano_split_dim
+        if d == "auto":
+            d = "seq" if (micro_batch_size is not None and micro_batch_size % self.par.num_nanobatches) else "batch"
+        self.seq_split = d == "seq" and self.par.num_nanobatches > 1
         self.decoder = TransformerBlock(cfg, self.par, self.comm, layer_range, dt, device, seed=seed,
-                                        recompute_layers=recompute_layers, sync=sync)
+                                        recompute_layers=recompute_layers, sync=sync, seq_split=self.seq_split)
         if post_process:
             self.final_norm = RMSNormOp(cfg.hidden_size, cfg.norm_eps, "final_layernorm", dtype=dt,
                                         device=device, sequence_parallel=self.par.sequence_parallel)
@@ -295,15 +302,6 @@ class GPTModel(nn.Module):
     @property
     def n(self) -> int:
         return self.par.num_nanobatches
-
-    def split_dim(self, b: int) -> str:
-        d = self.par.nano_split_dim
-        if d == "auto":
-            d = "batch" if b >= self.n and b % self.n == 0 else "seq"
-        if d == "seq":
-            raise NotImplementedError("sequence-dimension nanobatching is not available yet; use "
-                                      "micro_batch_size >= num_nanobatches")
-        return d
 
     def rotary(self, s_local: int, device) -> torch.Tensor:
         """Angle table for this rank's sequence positions (dual-chunk slice under CP)."""
@@ -323,8 +321,15 @@ class GPTModel(nn.Module):
         return t
 
     def split_nanobatches(self, t_bs: torch.Tensor) -> List[torch.Tensor]:
-        """``[b, s]`` → N tensors ``[s, b/N]`` (sequence-major token order)."""
-        self.split_dim(t_bs.shape[0])
+        """``[b, s]`` → N tensors ``[s, b/N]`` (batch split) or ``[s/N, b]`` (sequence split), each in
+        sequence-major token order."""
+        if self.seq_split:
+            if t_bs.shape[1] % self.n:
+                raise ValueError("sequence length must be divisible by the number of nanobatches")
+            return [c.t().contiguous() for c in t_bs.chunk(self.n, dim=1)]
+        if t_bs.shape[0] % self.n:
+            raise ValueError(f"micro batch {t_bs.shape[0]} is not divisible by {self.n} nanobatches; "
+                             "build the model with nano_split_dim='seq'")
         return [c.t().contiguous() for c in t_bs.chunk(self.n, dim=0)]
 
     # ------------------------------------------------------------------ forward
@@ -333,6 +338,9 @@ class GPTModel(nn.Module):
 
     def run_block(self, hidden: Sequence[torch.Tensor]) -> List[torch.Tensor]:
         s_local = hidden[0].shape[0] * (self.par.tp if self.par.sequence_parallel else 1)
+        if self.seq_split:
+            full = self.rotary(s_local * self.n, hidden[0].device)
+            return self.decoder(hidden, [full[i * s_local:(i + 1) * s_local] for i in range(self.n)])
         return self.decoder(hidden, self.rotary(s_local, hidden[0].device))
 
     def head_loss(self, hidden: Sequence[torch.Tensor], labels: torch.Tensor, loss_mask: torch.Tensor,

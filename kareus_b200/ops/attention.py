@@ -162,6 +162,11 @@ class AttentionOp(GraphOperator):
             self.ag_kv = comm.make(AllGatherKV, "cp", f"{name}.ag_kv")
             self.ag_kv_bwd = comm.make(AllGatherKV, "cp", f"{name}.ag_kv_bwd")
             self.rs_kv = comm.make(ReduceScatterKV, "cp", f"{name}.rs_kv")
+        # sequence-split nanobatches: nanobatch i holds rows [i·s/N, (i+1)·s/N) of every sequence and
+        # attends to the keys of nanobatches 0..i, which they leave in this per-layer bank
+        self.seq_nano = 0
+        self._kv_bank = {}
+        self._dkv_bank = {}
         self.ring = None
         if self.cp > 1 and cp_comm == "ring":
             from ..parallel.ring_attention import RingAttention
@@ -192,6 +197,8 @@ class AttentionOp(GraphOperator):
     # compute --------------------------------------------------------------------
     def forward(self, ctx, q, k, v):
         s, b = q.shape[0], q.shape[1]
+        if self.seq_nano > 1:
+            return self._forward_seq_split(ctx, q, k, v)
         if self.cp > 1 and self.cp_comm == "ring":
             out, lse = self.ring.forward(q, k, v, self.scale, nb=ctx.nb_index)
             if ctx.requires_grad:
@@ -220,7 +227,41 @@ class AttentionOp(GraphOperator):
             ctx.save_for_backward(q, k_loc, v_loc, out, lses[0], lses[1])
         return (out.reshape(s, b, -1),)
 
+    def _forward_seq_split(self, ctx, q, k, v):
+        if self.cp > 1:
+            raise NotImplementedError("sequence-split nanobatches with context parallelism")
+        i, s, b = ctx.nb_index, q.shape[0], q.shape[1]
+        self._kv_bank[i] = (k, v)
+        if i > 0:
+            k_all = torch.cat([self._kv_bank[j][0] for j in range(i + 1)], dim=0)
+            v_all = torch.cat([self._kv_bank[j][1] for j in range(i + 1)], dim=0)
+        else:
+            k_all, v_all = k, v
+        if i == self.seq_nano - 1:
+            self._kv_bank.clear()
+        out, lse = K.attention_fwd(q, k_all, v_all, self.scale, causal=True, q_offset=i * s)
+        if ctx.requires_grad:
+            ctx.save_for_backward(q, k_all, v_all, out, lse)
+        return (out.reshape(s, b, -1),)
+
+    def _backward_seq_split(self, ctx, dout):
+        q, k_all, v_all, out, lse = ctx.saved_tensors
+        i, s, b = ctx.nb_index, q.shape[0], q.shape[1]
+        do = dout.reshape(s, b, q_heads(q), self.d)
+        dq, dk_all, dv_all = K.attention_bwd(do, q, k_all, v_all, out, lse, self.scale, causal=True, q_offset=i * s)
+        dk, dv = dk_all[i * s:(i + 1) * s], dv_all[i * s:(i + 1) * s]
+        late = self._dkv_bank.pop(i, None)            # contributions of the nanobatches after this one
+        if late is not None:
+            dk, dv = dk + late[0], dv + late[1]
+        for j in range(i):
+            part = (dk_all[j * s:(j + 1) * s], dv_all[j * s:(j + 1) * s])
+            old = self._dkv_bank.get(j)
+            self._dkv_bank[j] = part if old is None else (old[0] + part[0], old[1] + part[1])
+        return dq, dk, dv
+
     def backward(self, ctx, dout):
+        if self.seq_nano > 1:
+            return self._backward_seq_split(ctx, dout)
         if self.cp > 1 and self.cp_comm != "ring":
             return self._backward_cp(ctx, dout)
         q, k, v, out, lse = ctx.saved_tensors

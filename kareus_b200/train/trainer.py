@@ -59,7 +59,8 @@ class Trainer:
                               seed=train_cfg.seed, pre_process=mesh.is_first_stage,
                               post_process=mesh.is_last_stage,
                               layer_range=stage_layer_range(model_cfg, mesh.pp, mesh.pp_rank),
-                              recompute_layers=recompute_layers, sync=sync)
+                              recompute_layers=recompute_layers, sync=sync,
+                              micro_batch_size=train_cfg.micro_batch_size)
         if comm_scheduler is not None:
             self.model.decoder.set_scheduler(comm_scheduler)
         mp_group = mesh.group("tp_pp") if mesh.size("tp_pp") > 1 else None
@@ -75,6 +76,8 @@ class Trainer:
     def _msg_shapes(self, mbs: int, s_local: int):
         n = self.par.num_nanobatches
         s = s_local // self.par.tp if self.par.sequence_parallel else s_local
+        if self.model.seq_split:
+            return [(s // n, mbs, self.model_cfg.hidden_size)] * n
         return [(s, mbs // n, self.model_cfg.hidden_size)] * n
 
     def instruction_order(self) -> List[str]:

@@ -74,3 +74,23 @@ def test_qk_layernorm_and_dropout_replay():
         m(tokens, labels, mask).backward()
         grads.append(m.decoder.layers[0].fc1.weight.main_grad.clone())
     torch.testing.assert_close(grads[0], grads[1], rtol=1e-9, atol=1e-12)
+
+
+@pytest.mark.parametrize("n,recompute", [(2, True), (4, False)])
+def test_sequence_split_nanobatches(n, recompute):
+    """MBS 1: nanobatches split the sequence; later nanobatches attend to earlier ones' keys and
+    send dK/dV back (backward visits nanobatches last to first)."""
+    cfg = get_model_config("tiny")
+    par = ParallelConfig(num_nanobatches=n, recompute=recompute, nano_split_dim="seq")
+    model = GPTModel(cfg, par, dtype="fp64")
+    assert model.seq_split
+    oracle = OracleLlama(cfg)
+    load_from_shards(oracle, [model])
+    tokens, labels, mask = _batch(cfg, 1, 64)
+    loss = model(tokens, labels, mask)
+    loss.backward()
+    model.finalize_grads()
+    ref_loss = oracle(tokens, labels, mask)
+    ref_loss.backward()
+    torch.testing.assert_close(loss.detach(), ref_loss.detach(), rtol=1e-9, atol=1e-10)
+    _check(model, oracle)

@@ -49,10 +49,18 @@ class _LinearBase(nn.Module, GraphOperator):
         self._comm_factory = comm
 
     # compute -------------------------------------------------------------------
+    def _fwd_staging(self, shape, dtype, nb, device):
+        """Where the forward result should be written so the following collective needs no copy."""
+        return None
+
+    def _bwd_staging(self, shape, dtype, nb, device):
+        return None
+
     def forward(self, ctx, x):
         shp = x.shape
         x2 = x.reshape(-1, shp[-1])
-        y = K.gemm(x2, self.weight, trans_b=True)
+        out = self._fwd_staging((x2.shape[0], self.out_features), x2.dtype, ctx.nb_index, x2.device)
+        y = K.gemm(x2, self.weight, trans_b=True, out=out)
         if ctx.requires_grad:
             ctx.save_for_backward(x2)
         return (y.reshape(shp[:-1] + (self.out_features,)),)
@@ -61,7 +69,8 @@ class _LinearBase(nn.Module, GraphOperator):
         (x2,) = ctx.saved_tensors
         shp = dy.shape
         dy2 = dy.reshape(-1, shp[-1])
-        dx = K.gemm(dy2, self.weight, trans_b=False)                       # [M,N]·[N,K]
+        out = self._bwd_staging((dy2.shape[0], self.in_features), dy2.dtype, ctx.nb_index, dy2.device)
+        dx = K.gemm(dy2, self.weight, trans_b=False, out=out)              # [M,N]·[N,K]
         K.gemm(dy2, x2, trans_a=True, trans_b=False, accumulate=ensure_main_grad(self.weight))
         return (dx.reshape(shp[:-1] + (self.in_features,)),)
 
@@ -78,6 +87,12 @@ class ColumnParallelLinear(_LinearBase):
         self.fwd_allgather = f.make(AllGather, "tp", f"{self.name}.fwd_ag")
         self.bwd_reducescatter = f.make(ReduceScatter, "tp", f"{self.name}.bwd_rs")
         self.fused_ag_gemm = None   # set by kareus_b200.ops.fused when tp_comm == "sp_fused"
+
+    def _bwd_staging(self, shape, dtype, nb, device):
+        if self.tp == 1:
+            return None
+        op = self.bwd_allreduce if self.tp_comm == "allreduce" else self.bwd_reducescatter
+        return op.staging(shape, dtype, nb, device)
 
     def forward_specs(self) -> List[object]:
         compute = ComputeSpec(self, ("main",), ("main",))
@@ -111,6 +126,12 @@ class RowParallelLinear(_LinearBase):
         self.fwd_reducescatter = f.make(ReduceScatter, "tp", f"{self.name}.fwd_rs")
         self.bwd_allgather = f.make(AllGather, "tp", f"{self.name}.bwd_ag")
         self.fused_gemm_rs = None
+
+    def _fwd_staging(self, shape, dtype, nb, device):
+        if self.tp == 1:
+            return None
+        op = self.fwd_allreduce if self.tp_comm == "allreduce" else self.fwd_reducescatter
+        return op.staging(shape, dtype, nb, device)
 
     def forward_specs(self) -> List[object]:
         compute = ComputeSpec(self, ("main",), ("main",))

@@ -36,6 +36,16 @@ class CollectiveBase:
         self.tag = re.sub(r"layers\.\d+\.", "", self.name)
         self.calls = 0
 
+    def staging(self, shape, dtype, nb: int, device) -> Optional[torch.Tensor]:
+        """Heap buffer this collective reads its input from (kernel backend only), so the producing
+        GEMM can write there directly; ``None`` when the library path is used."""
+        if self.backend == "kernel" and self.heap is not None and self.world > 1 and device.type == "cuda" \
+                and dtype == torch.bfloat16 and self.staging_kind is not None:
+            return self.heap.staging(self.staging_kind, self.tag, nb, shape, dtype)
+        return None
+
+    staging_kind: Optional[str] = None
+
     def _use_kernel(self, t, sm_num) -> bool:
         return (self.backend == "kernel" and self.heap is not None and sm_num is not None
                 and isinstance(t, torch.Tensor) and t.is_cuda and self.world > 1)
@@ -43,6 +53,8 @@ class CollectiveBase:
 
 class AllReduce(CollectiveBase):
     """In-place sum over the group."""
+
+    staging_kind = "ar"
 
     def run(self, tensors, sm_num=None, block_size=None, backward=False, nb=0, ctx=None):
         (x,) = tensors
@@ -66,7 +78,9 @@ class AllGather(CollectiveBase):
         if self.world == 1:
             return (x,)
         if self._use_kernel(x, sm_num):
-            return (self.heap.all_gather(x, nb=nb, sm_num=sm_num, block_size=block_size, tag=self.tag),)
+            # the forward gather feeds a linear layer that keeps its input for wgrad
+            return (self.heap.all_gather(x, nb=nb, sm_num=sm_num, block_size=block_size, tag=self.tag,
+                                         keep=not backward),)
         x = x.contiguous()
         out = torch.empty((x.shape[0] * self.world,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
         dist.all_gather_into_tensor(out, x, group=self.group)
@@ -75,6 +89,8 @@ class AllGather(CollectiveBase):
 
 class ReduceScatter(CollectiveBase):
     """Sum over the group, each rank keeps its dim-0 shard."""
+
+    staging_kind = "rs"
 
     def run(self, tensors, sm_num=None, block_size=None, backward=False, nb=0, ctx=None):
         (x,) = tensors

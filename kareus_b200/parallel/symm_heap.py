@@ -176,7 +176,18 @@ class SymmetricHeap:
         KC._count()
         return buf
 
-    def all_gather(self, x: torch.Tensor, nb: int = 0, sm_num=None, block_size=None, tag: str = "ag") -> torch.Tensor:
+    def staging(self, kind: str, tag: str, nb: int, shape, dtype) -> torch.Tensor:
+        """The heap buffer a collective would copy its input into; a producer that writes its result
+        there (``gemm(..., out=...)``) saves the copy.  ``kind``: ``"ar"`` or ``"rs"``."""
+        ch = self.channel(f"{tag}/{nb}")
+        n = 1
+        for s_ in shape:
+            n *= s_
+        off, _ = self.buffer(ch, "x", n * torch.empty((), dtype=dtype).element_size())
+        return self.view(off, shape, dtype)
+
+    def all_gather(self, x: torch.Tensor, nb: int = 0, sm_num=None, block_size=None, tag: str = "ag",
+                   keep: bool = False) -> torch.Tensor:
         ch = self.channel(f"{tag}/{nb}")
         shard = x.numel() * x.element_size()
         off, _ = self.buffer(ch, "x", shard * self.world)
@@ -188,7 +199,8 @@ class SymmetricHeap:
         KC._check(self.lib.kb_allgather(self._bases_arr, self.rank, self.world, ch.flag_off, off, shard, ch.epoch, sm,
                                         blk, st.data_ptr(), KC._stream()), "allgather")
         KC._count()
-        return out.clone()        # callers may keep the result (saved for backward); the buffer is reused
+        # the buffer is reused by the next call of this site: callers that keep the result ask for a copy
+        return out.clone() if keep else out
 
     def reduce_scatter(self, x: torch.Tensor, nb: int = 0, sm_num=None, block_size=None, tag: str = "rs") -> torch.Tensor:
         ch = self.channel(f"{tag}/{nb}")

@@ -173,7 +173,8 @@ __device__ void rs_reduce_items(const FusedParams& p, int N, int tiles_n, int BN
 }
 
 // ----------------------------------------------------------------------------- kernel
-template <int BN>
+// B_MN: the weight operand is stored [K rows][N contiguous] (dgrad: dY·W with W as [N_red, K_out]).
+template <int BN, bool B_MN>
 __global__ void __launch_bounds__(FG_THREADS, 1)
 fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const FusedParams p, int M, int N, int K) {
@@ -279,7 +280,13 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           uint8_t* a_dst = smem + s * S::STAGE_BYTES;
           mbar_expect_tx(&full[s], S::STAGE_BYTES);
           tma_load_2d(a_dst, &tmA, &full[s], kb_ * FG_BK, m0);
-          tma_load_2d(a_dst + S::A_BYTES, &tmB, &full[s], kb_ * FG_BK, n0);
+          if constexpr (!B_MN) {
+            tma_load_2d(a_dst + S::A_BYTES, &tmB, &full[s], kb_ * FG_BK, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(a_dst + S::A_BYTES + j * 8192, &tmB, &full[s], n0 + 64 * j, kb_ * FG_BK);
+          }
         }
       }
       if (!ok) {
@@ -288,7 +295,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       }
     }
   } else if (warp == 1) {
-    constexpr uint32_t idesc = make_idesc_bf16(FG_BM, BN, false, false);
+    constexpr uint32_t idesc = make_idesc_bf16(FG_BM, BN, false, B_MN);
     uint32_t it = 0, tile_i = 0;
     bool ok = true;
     for (int t = cta; t < num_tiles && ok; t += p.n_gemm, ++tile_i) {
@@ -306,7 +313,8 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           const uint32_t b_addr = a_addr + S::A_BYTES;
 #pragma unroll
           for (int k = 0; k < FG_BK / 16; ++k)
-            umma_ss(d_tmem, make_smem_desc(a_addr + k * 32, 16, 1024), make_smem_desc(b_addr + k * 32, 16, 1024),
+            umma_ss(d_tmem, make_smem_desc(a_addr + k * 32, 16, 1024),
+                    B_MN ? make_smem_desc(b_addr + k * 2048, 8192, 1024) : make_smem_desc(b_addr + k * 32, 16, 1024),
                     idesc, (kb_ > 0 || k > 0) ? 1u : 0u);
           umma_commit(&empty[s]);
           if (kb_ == nk - 1) umma_commit(&tfull[buf]);
@@ -393,15 +401,16 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   }
 }
 
-template <int BN>
+template <int BN, bool B_MN>
 static int launch_fused(const void* A, const void* W, const FusedParams& p, int M, int N, int K, int lda, int ldw,
                         cudaStream_t stream) {
   CUtensorMap tmA, tmB;
   int rc = make_tmap_2d_bf16(&tmA, A, K, M, lda, FG_BK, FG_BM);
   if (rc) return rc;
-  rc = make_tmap_2d_bf16(&tmB, W, K, N, ldw, FG_BK, BN);
+  if (!B_MN) rc = make_tmap_2d_bf16(&tmB, W, K, N, ldw, FG_BK, BN);
+  else       rc = make_tmap_2d_bf16(&tmB, W, N, K, ldw, 64, FG_BK);
   if (rc) return rc;
-  auto kern = fused_gemm_kernel<BN>;
+  auto kern = fused_gemm_kernel<BN, B_MN>;
   constexpr int smem = FgSmem<BN>::TOTAL > (FG_SLOTS * FG_CHUNK + 2048) ? FgSmem<BN>::TOTAL : (FG_SLOTS * FG_CHUNK + 2048);
   static bool configured = false;
   if (!configured) {
@@ -426,12 +435,12 @@ static PeerCtx fused_ctx(void* const* bases, int rank, int world, uint64_t flag_
 
 using namespace kb;
 
-// Y[M,N] = gathered(X)[M,K] · W[N,K]ᵀ where this rank's shard already sits at rows
+// Y[M,N] = gathered(X)[M,K] · op(W) with W stored [N,K] (b_mn = 0) or [K,N] (b_mn = 1), where this rank's shard already sits at rows
 // [rank*Ms, (rank+1)*Ms) of the gathered buffer at heap offset xg_off (same offset on all ranks).
 // ready: local uint32[M/128] flags (persist across calls, epoch-valued).  n_comm copy-driver CTAs.
 extern "C" int kb_ag_gemm_bf16(void* const* bases, int rank, int world, uint64_t flag_off, uint64_t xg_off,
-                               const void* W, void* Y, int M, int N, int K, int ldw, uint32_t* ready, uint32_t epoch,
-                               int n_comm, int num_sms, int* status, cudaStream_t stream) {
+                               const void* W, void* Y, int M, int N, int K, int ldw, int b_mn, uint32_t* ready,
+                               uint32_t epoch, int n_comm, int num_sms, int* status, cudaStream_t stream) {
   if (world < 2 || world > MAX_PEERS || M % (world * FG_BM) || (K & 7) || (xg_off & 1023)) return ST_BAD_ARG;
   if (num_sms <= 0) num_sms = device_sm_count();
   if (n_comm < 1) n_comm = 1;
@@ -452,16 +461,18 @@ extern "C" int kb_ag_gemm_bf16(void* const* bases, int rank, int world, uint64_t
   const int bn = narrow ? 128 : 256;
   const int tiles = (M / FG_BM) * ((N + bn - 1) / bn);
   p.n_gemm = num_sms - n_comm < tiles ? num_sms - n_comm : tiles;
-  if (narrow) return launch_fused<128>(A, W, p, M, N, K, K, ldw, stream);
-  return launch_fused<256>(A, W, p, M, N, K, K, ldw, stream);
+  if (narrow) return b_mn ? launch_fused<128, true>(A, W, p, M, N, K, K, ldw, stream)
+                          : launch_fused<128, false>(A, W, p, M, N, K, K, ldw, stream);
+  return b_mn ? launch_fused<256, true>(A, W, p, M, N, K, K, ldw, stream)
+              : launch_fused<256, false>(A, W, p, M, N, K, K, ldw, stream);
 }
 
-// out[M/world, N] = rows owned by this rank of sum over ranks of (A[M,K] · W[N,K]ᵀ).
+// out[M/world, N] = rows owned by this rank of sum over ranks of (A[M,K] · op(W)); W as above.
 // stage_off: staging [world][M/world][N] bf16; cnt_off: uint32 counters [world][M/world/128][tiles_n];
 // go: local uint32 flag.  n_comm reducer CTAs run next to the GEMM CTAs.
 extern "C" int kb_gemm_rs_bf16(void* const* bases, int rank, int world, uint64_t flag_off, uint64_t stage_off,
-                               uint64_t cnt_off, const void* A, int lda, const void* W, int ldw, void* out, int M, int N,
-                               int K, uint32_t* go, uint32_t epoch, int n_comm, int num_sms, int* status,
+                               uint64_t cnt_off, const void* A, int lda, const void* W, int ldw, int b_mn, void* out,
+                               int M, int N, int K, uint32_t* go, uint32_t epoch, int n_comm, int num_sms, int* status,
                                cudaStream_t stream) {
   if (world < 2 || world > MAX_PEERS || M % (world * FG_BM) || (K & 7) || (N & 7) || (lda & 7)) return ST_BAD_ARG;
   if (num_sms <= 0) num_sms = device_sm_count();
@@ -483,8 +494,10 @@ extern "C" int kb_gemm_rs_bf16(void* const* bases, int rank, int world, uint64_t
   if (n_comm > num_sms / 2) n_comm = num_sms / 2;
   p.n_last = n_comm;
   p.n_gemm = num_sms - n_comm < tiles ? num_sms - n_comm : tiles;   // reducers get SMs of their own
-  if (narrow) return launch_fused<128>(A, W, p, M, N, K, lda, ldw, stream);
-  return launch_fused<256>(A, W, p, M, N, K, lda, ldw, stream);
+  if (narrow) return b_mn ? launch_fused<128, true>(A, W, p, M, N, K, lda, ldw, stream)
+                          : launch_fused<128, false>(A, W, p, M, N, K, lda, ldw, stream);
+  return b_mn ? launch_fused<256, true>(A, W, p, M, N, K, lda, ldw, stream)
+              : launch_fused<256, false>(A, W, p, M, N, K, lda, ldw, stream);
 }
 
 // Number of column tiles the fused kernels use for a given N (sizes the counter array).

@@ -1,25 +1,27 @@
 """Graph nodes that run a GEMM fused with its sequence-parallel collective.
 
-``FusedAGGemm`` (all-gather → column-parallel GEMM) and ``FusedGemmRS`` (row-parallel GEMM →
-reduce-scatter) wrap the kernels of ``csrc/fused_gemm_comm.cu``.  To the partition engine they are
-collective nodes: they run on the side stream, take the plan entry's ``sm_num`` (copy-driver /
-reducer CTAs) and overlap with the other nanobatch's compute, but they also produce the GEMM
-result, so the graph has no separate compute node for that linear layer in forward.  Backward
-uses the linear operator's ordinary dgrad/wgrad with the (unfused) mirrored collective.
+Forward: ``FusedAGGemm`` (all-gather → column-parallel GEMM) and ``FusedGemmRS`` (row-parallel GEMM
+→ reduce-scatter).  Backward mirrors: ``FusedDgradRS`` (column-parallel dgrad → reduce-scatter, plus
+the local wgrad) and ``FusedAGDgrad`` (all-gather of dY → row-parallel dgrad, plus the wgrad on the
+gathered dY).  All four wrap the kernels of ``csrc/fused_gemm_comm.cu``.
 
-State the forward leaves for backward (the gathered input, or the row-parallel input) goes into
-the linear operator's own context: these nodes share its graph uid.
+To the partition engine they are collective nodes: they run on the side stream, take the plan
+entry's ``sm_num`` (copy-driver / reducer CTAs) and overlap with the other nanobatch's compute, but
+they also produce the GEMM results, so the graph has no separate compute node for the linear layer.
+State kept between forward and backward (the gathered input, or the row-parallel input) lives in the
+linear operator's own context: these nodes share its graph uid.
 """
 from __future__ import annotations
 
-import ctypes
 import re
 from ctypes import c_int, c_uint32, c_uint64, c_void_p
 
 import torch
 
+from .. import kernels as K
 from ..engine.graph import operator_uid
 from ..kernels import cuda as KC
+from .basic import ensure_main_grad
 
 _DECLARED = False
 
@@ -29,8 +31,8 @@ def _lib():
     L = KC.lib()
     if not _DECLARED:
         P, I, U32, U64 = c_void_p, c_int, c_uint32, c_uint64
-        L.kb_ag_gemm_bf16.argtypes = [P, I, I, U64, U64, P, P, I, I, I, I, P, U32, I, I, P, P]
-        L.kb_gemm_rs_bf16.argtypes = [P, I, I, U64, U64, U64, P, I, P, I, P, I, I, I, P, U32, I, I, P, P]
+        L.kb_ag_gemm_bf16.argtypes = [P, I, I, U64, U64, P, P, I, I, I, I, I, P, U32, I, I, P, P]
+        L.kb_gemm_rs_bf16.argtypes = [P, I, I, U64, U64, U64, P, I, P, I, I, P, I, I, I, P, U32, I, I, P, P]
         L.kb_fused_tiles_n.argtypes = [I]
         for n in ("kb_ag_gemm_bf16", "kb_gemm_rs_bf16", "kb_fused_tiles_n"):
             getattr(L, n).restype = c_int
@@ -45,8 +47,9 @@ class _FusedBase:
     def __init__(self, linear, heap, default_sm: int):
         self.linear, self.heap, self.default_sm = linear, heap, default_sm
         self.name = linear.name + "." + type(self).__name__
-        # one set of heap buffers per call site, shared by all layers (see CollectiveBase.tag)
-        self.tag = re.sub(r"layers\.\d+\.", "", linear.name)
+        # one set of heap buffers per call site, shared by all layers (layers run one after another on
+        # the ordered side stream)
+        self.tag = re.sub(r"layers\.\d+\.", "", linear.name) + "/" + type(self).__name__
         self._graph_uid = operator_uid(linear)
         self._local = {}
 
@@ -57,74 +60,118 @@ class _FusedBase:
             self._local[key] = t
         return t
 
-
-class FusedAGGemm(_FusedBase):
-    def run(self, tensors, sm_num=None, block_size=None, backward=False, nb=0, ctx=None):
-        (x,) = tensors
-        heap, lin = self.heap, self.linear
+    # ---- kernels ------------------------------------------------------------------------------
+    def _ag_gemm(self, x2, w, n_out, b_mn: bool, sm_num, nb: int):
+        """Gather ``x2`` ([Ms, K] shard) over the group and multiply: returns ``(y [M, n_out], xg [M, K])``
+        where ``xg`` is the gathered input inside the heap (valid until this site's next call)."""
+        heap = self.heap
         world, rank = heap.world, heap.rank
-        lead = x.shape[:-1]
-        x2 = x.reshape(-1, x.shape[-1])
         ms, k = x2.shape
-        m, n = ms * world, lin.out_features
+        m = ms * world
         if ms % 128 or x2.dtype != torch.bfloat16:
             raise KC.KernelError(f"fused all-gather GEMM needs bf16 and a multiple of 128 rows per rank, got {ms}")
-        ch = heap.channel(f"{self.tag}/ag_gemm/{nb}")
+        ch = heap.channel(f"{self.tag}/{nb}")
         off, _ = heap.buffer(ch, "xg", m * k * 2)
         xg = heap.view(off, (m, k), torch.bfloat16)
         xg[rank * ms:(rank + 1) * ms].copy_(x2)
         ready = self._local_flags(("ready", nb), m // 128)
         ch.epoch += 1
-        y = torch.empty(m, n, dtype=torch.bfloat16, device=x.device)
-        st = KC.status_word(x.device)
-        w = lin.weight
-        rc = _lib().kb_ag_gemm_bf16(heap._bases_arr, rank, world, ch.flag_off, off, w.data_ptr(), y.data_ptr(), m, n, k,
-                                    w.stride(0), ready.data_ptr(), ch.epoch, int(sm_num or self.default_sm), 0,
-                                    st.data_ptr(), KC._stream())
-        KC._check(rc, f"ag_gemm {lin.name}")
+        y = torch.empty(m, n_out, dtype=torch.bfloat16, device=x2.device)
+        st = KC.status_word(x2.device)
+        rc = _lib().kb_ag_gemm_bf16(heap._bases_arr, rank, world, ch.flag_off, off, w.data_ptr(), y.data_ptr(), m,
+                                    n_out, k, w.stride(0), 1 if b_mn else 0, ready.data_ptr(), ch.epoch,
+                                    int(sm_num or self.default_sm), 0, st.data_ptr(), KC._stream())
+        KC._check(rc, f"ag_gemm {self.name}")
         KC._count()
-        if ctx is not None and ctx.requires_grad:
-            ctx.save_for_backward(xg.clone())         # gathered input for the wgrad GEMM
-        return (y.reshape((lead[0] * world,) + tuple(lead[1:]) + (n,)),)
+        return y, xg
 
-
-class FusedGemmRS(_FusedBase):
-    def run(self, tensors, sm_num=None, block_size=None, backward=False, nb=0, ctx=None):
-        (a,) = tensors
-        heap, lin = self.heap, self.linear
+    def _gemm_rs(self, a2, w, n_out, b_mn: bool, sm_num, nb: int):
+        """``reduce_scatter_rows(a2 · op(w))`` → ``[M/world, n_out]``."""
+        heap = self.heap
         world, rank = heap.world, heap.rank
-        lead = a.shape[:-1]
-        a2 = a.reshape(-1, a.shape[-1])
         if not KC._rowmajor_ok(a2):
             a2 = a2.contiguous()
         m, k = a2.shape
-        n = lin.out_features
         ms = m // world
         if m % (world * 128) or a2.dtype != torch.bfloat16:
             raise KC.KernelError(f"fused GEMM reduce-scatter needs bf16 and rows divisible by {world * 128}, got {m}")
         L = _lib()
-        tiles_n = L.kb_fused_tiles_n(n)
-        ch = heap.channel(f"{self.tag}/gemm_rs/{nb}")
-        stage_off, _ = heap.buffer(ch, "stage", m * n * 2)
+        tiles_n = L.kb_fused_tiles_n(n_out)
+        ch = heap.channel(f"{self.tag}/{nb}")
+        stage_off, _ = heap.buffer(ch, "stage", m * n_out * 2)
         cnt_off, _ = heap.buffer(ch, "cnt", world * (ms // 128) * tiles_n * 4)
         go = self._local_flags(("go", nb), 1)
         ch.epoch += 1
-        out = torch.empty(ms, n, dtype=torch.bfloat16, device=a.device)
-        st = KC.status_word(a.device)
-        w = lin.weight
+        out = torch.empty(ms, n_out, dtype=torch.bfloat16, device=a2.device)
+        st = KC.status_word(a2.device)
         rc = L.kb_gemm_rs_bf16(heap._bases_arr, rank, world, ch.flag_off, stage_off, cnt_off, a2.data_ptr(),
-                               a2.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), m, n, k, go.data_ptr(), ch.epoch,
-                               int(sm_num or self.default_sm), 0, st.data_ptr(), KC._stream())
-        KC._check(rc, f"gemm_rs {lin.name}")
+                               a2.stride(0), w.data_ptr(), w.stride(0), 1 if b_mn else 0, out.data_ptr(), m, n_out, k,
+                               go.data_ptr(), ch.epoch, int(sm_num or self.default_sm), 0, st.data_ptr(),
+                               KC._stream())
+        KC._check(rc, f"gemm_rs {self.name}")
         KC._count()
+        return out, a2
+
+
+class FusedAGGemm(_FusedBase):
+    """forward of a column-parallel layer: ``Y = AllGather(x)·Wᵀ``."""
+
+    def run(self, tensors, sm_num=None, block_size=None, backward=False, nb=0, ctx=None):
+        (x,) = tensors
+        lin = self.linear
+        lead = x.shape[:-1]
+        y, xg = self._ag_gemm(x.reshape(-1, x.shape[-1]), lin.weight, lin.out_features, False, sm_num, nb)
+        if ctx is not None and ctx.requires_grad:
+            ctx.save_for_backward(xg.clone())         # gathered input for the wgrad GEMM
+        return (y.reshape((lead[0] * self.heap.world,) + tuple(lead[1:]) + (lin.out_features,)),)
+
+
+class FusedGemmRS(_FusedBase):
+    """forward of a row-parallel layer: ``Y_shard = ReduceScatter(a·Wᵀ)``."""
+
+    def run(self, tensors, sm_num=None, block_size=None, backward=False, nb=0, ctx=None):
+        (a,) = tensors
+        lin = self.linear
+        lead = a.shape[:-1]
+        out, a2 = self._gemm_rs(a.reshape(-1, a.shape[-1]), lin.weight, lin.out_features, False, sm_num, nb)
         if ctx is not None and ctx.requires_grad:
             ctx.save_for_backward(a2)
-        return (out.reshape((lead[0] // world,) + tuple(lead[1:]) + (n,)),)
+        return (out.reshape((lead[0] // self.heap.world,) + tuple(lead[1:]) + (lin.out_features,)),)
+
+
+class FusedDgradRS(_FusedBase):
+    """backward of a column-parallel layer: ``dX_shard = ReduceScatter(dY·W)`` and ``dW += dYᵀ·X``."""
+
+    def run(self, tensors, sm_num=None, block_size=None, backward=True, nb=0, ctx=None):
+        (dy,) = tensors
+        lin = self.linear
+        (x_full,) = ctx.saved_tensors
+        lead = dy.shape[:-1]
+        dx, dy2 = self._gemm_rs(dy.reshape(-1, dy.shape[-1]), lin.weight, lin.in_features, True, sm_num, nb)
+        K.gemm(dy2, x_full, trans_a=True, trans_b=False, accumulate=ensure_main_grad(lin.weight))
+        ctx.clear()
+        return (dx.reshape((lead[0] // self.heap.world,) + tuple(lead[1:]) + (lin.in_features,)),)
+
+
+class FusedAGDgrad(_FusedBase):
+    """backward of a row-parallel layer: ``dX = AllGather(dY)·W`` and ``dW += AllGather(dY)ᵀ·A``."""
+
+    def run(self, tensors, sm_num=None, block_size=None, backward=True, nb=0, ctx=None):
+        (dy,) = tensors
+        lin = self.linear
+        (a2,) = ctx.saved_tensors
+        lead = dy.shape[:-1]
+        dx, dyg = self._ag_gemm(dy.reshape(-1, dy.shape[-1]), lin.weight, lin.in_features, True, sm_num, nb)
+        K.gemm(dyg, a2, trans_a=True, trans_b=False, accumulate=ensure_main_grad(lin.weight))
+        ctx.clear()
+        return (dx.reshape((lead[0] * self.heap.world,) + tuple(lead[1:]) + (lin.in_features,)),)
 
 
 def attach_fused(layer, heap, default_sm: int = 16) -> None:
-    """Give the four linear layers of a transformer layer their fused forward nodes."""
-    layer.qkv.fused_ag_gemm = FusedAGGemm(layer.qkv, heap, default_sm)
-    layer.fc1.fused_ag_gemm = FusedAGGemm(layer.fc1, heap, default_sm)
-    layer.proj.fused_gemm_rs = FusedGemmRS(layer.proj, heap, default_sm)
-    layer.fc2.fused_gemm_rs = FusedGemmRS(layer.fc2, heap, default_sm)
+    """Give the four linear layers of a transformer layer their fused forward and backward nodes."""
+    for lin in (layer.qkv, layer.fc1):
+        lin.fused_ag_gemm = FusedAGGemm(lin, heap, default_sm)
+        lin.fused_dgrad_rs = FusedDgradRS(lin, heap, default_sm)
+    for lin in (layer.proj, layer.fc2):
+        lin.fused_gemm_rs = FusedGemmRS(lin, heap, default_sm)
+        lin.fused_ag_dgrad = FusedAGDgrad(lin, heap, default_sm)

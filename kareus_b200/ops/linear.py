@@ -87,6 +87,7 @@ class ColumnParallelLinear(_LinearBase):
         self.fwd_allgather = f.make(AllGather, "tp", f"{self.name}.fwd_ag")
         self.bwd_reducescatter = f.make(ReduceScatter, "tp", f"{self.name}.bwd_rs")
         self.fused_ag_gemm = None   # set by kareus_b200.ops.fused when tp_comm == "sp_fused"
+        self.fused_dgrad_rs = None
 
     def _bwd_staging(self, shape, dtype, nb, device):
         if self.tp == 1:
@@ -110,6 +111,9 @@ class ColumnParallelLinear(_LinearBase):
         if self.tp_comm == "allreduce":
             return [compute, CommSpec(self.bwd_allreduce, CommKind.ALL_REDUCE, ("grad_main",), ("grad_main",),
                                       f"bwd_{self.key}", backward=True)]
+        if self.tp_comm == "sp_fused" and self.fused_dgrad_rs is not None:
+            return [CommSpec(self.fused_dgrad_rs, CommKind.FUSED, ("grad_main",), ("grad_main",),
+                             f"bwd_{self.key}", backward=True)]
         return [compute, CommSpec(self.bwd_reducescatter, CommKind.REDUCE_SCATTER, ("grad_main",),
                                   ("grad_main",), f"bwd_{self.key}", backward=True)]
 
@@ -126,6 +130,7 @@ class RowParallelLinear(_LinearBase):
         self.fwd_reducescatter = f.make(ReduceScatter, "tp", f"{self.name}.fwd_rs")
         self.bwd_allgather = f.make(AllGather, "tp", f"{self.name}.bwd_ag")
         self.fused_gemm_rs = None
+        self.fused_ag_dgrad = None
 
     def _fwd_staging(self, shape, dtype, nb, device):
         if self.tp == 1:
@@ -149,5 +154,8 @@ class RowParallelLinear(_LinearBase):
         compute = ComputeSpec(self, ("grad_main",), ("grad_main",), backward=True)
         if self.tp == 1 or self.tp_comm == "allreduce":
             return [compute]
+        if self.tp_comm == "sp_fused" and self.fused_ag_dgrad is not None:
+            return [CommSpec(self.fused_ag_dgrad, CommKind.FUSED, ("grad_main",), ("grad_main",),
+                             f"bwd_{self.key}_ag", backward=True)]
         return [CommSpec(self.bwd_allgather, CommKind.ALL_GATHER, ("grad_main",), ("grad_main",),
                          f"bwd_{self.key}_ag", backward=True), compute]

@@ -45,11 +45,11 @@ def test_fused_gemm_collectives(heap, rank, world, dev):
     from types import SimpleNamespace
     from kareus_b200.engine.context import OpContext
     from kareus_b200.kernels import cuda as KC
-    from kareus_b200.ops.fused import FusedAGGemm, FusedGemmRS
+    from kareus_b200.ops.fused import FusedAGDgrad, FusedAGGemm, FusedDgradRS, FusedGemmRS
     g = torch.Generator(device=dev).manual_seed(5 + rank)
     for (ms, k, n, sm) in [(256, 512, 384, 4), (1024, 3072, 640, 12), (512, 1024, 3072, 8)]:
         w = (torch.randn(n, k, device=dev, generator=g) * 0.05).bfloat16()
-        lin = SimpleNamespace(name=f"lin{ms}_{n}", out_features=n, weight=w)
+        lin = SimpleNamespace(name=f"lin{ms}_{n}", out_features=n, in_features=k, weight=w)
         x = torch.randn(ms, 1, k, device=dev, generator=g).bfloat16()
         xs = torch.empty(ms * world, 1, k, device=dev, dtype=torch.bfloat16)
         dist.all_gather_into_tensor(xs, x)
@@ -73,6 +73,29 @@ def test_fused_gemm_collectives(heap, rank, world, dev):
             torch.cuda.synchronize()
             KC.check_status()
             assert rel(o.reshape(-1, n), want_rs) < 2e-2, ("gemm_rs", ms, k, n, rep, rel(o.reshape(-1, n), want_rs))
+        # backward mirrors (weight read as an MN-major operand): dgrad → reduce-scatter, all-gather → dgrad
+        w.main_grad = torch.zeros(n, k, device=dev)
+        dy = torch.randn(ms * world, 1, n, device=dev, generator=g).bfloat16()
+        ctx = OpContext()
+        ctx.save_for_backward(xs.reshape(-1, k))
+        (dx,) = FusedDgradRS(lin, heap, 8).run((dy,), sm_num=sm, nb=0, ctx=ctx)
+        torch.cuda.synchronize()
+        KC.check_status()
+        full = dy.float().reshape(-1, n) @ w.float()
+        dist.all_reduce(full)
+        assert rel(dx.reshape(-1, k), full[rank * ms:(rank + 1) * ms]) < 2e-2, ("dgrad_rs", ms, k, n)
+        assert rel(w.main_grad, dy.float().reshape(-1, n).t() @ xs.float().reshape(-1, k)) < 2e-2
+        w.main_grad.zero_()
+        dys = torch.randn(ms, 1, n, device=dev, generator=g).bfloat16()
+        dyg = torch.empty(ms * world, 1, n, device=dev, dtype=torch.bfloat16)
+        dist.all_gather_into_tensor(dyg, dys)
+        ctx = OpContext()
+        ctx.save_for_backward(a.reshape(-1, k))
+        (dxa,) = FusedAGDgrad(lin, heap, 8).run((dys,), sm_num=sm, nb=1, ctx=ctx)
+        torch.cuda.synchronize()
+        KC.check_status()
+        assert rel(dxa.reshape(-1, k), dyg.float().reshape(-1, n) @ w.float()) < 2e-2, ("ag_dgrad", ms, k, n)
+        assert rel(w.main_grad, dyg.float().reshape(-1, n).t() @ a.float().reshape(-1, k)) < 2e-2
 
 
 def test_bounded_wait(heap, dev):
@@ -147,7 +170,7 @@ def test_ring_attention(heap, rank, world, dev):
 def main():
     from kareus_b200.parallel.mesh import init_distributed
     from kareus_b200.parallel.symm_heap import SymmetricHeap
-    rank, world, local = init_distributed()
+    rank, world, local = init_distributed(timeout_s=120)     # a rank that died must not hang the others for long
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
     which = sys.argv[1] if len(sys.argv) > 1 else "all"

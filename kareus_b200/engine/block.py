@@ -28,17 +28,19 @@ BWD_INPUTS = {"grad_main": "ext_grad_main"}
 
 
 class _Chunk:
-    def __init__(self, operators: Sequence[GraphOperator], n: int, sync: str, seq_split: bool = False):
+    def __init__(self, operators: Sequence[GraphOperator], n: int, sync: str, seq_split: bool = False,
+                 cp_keys: bool = False):
         self.operators = list(operators)
         self.fwd_graph, self.bwd_graph = build_graphs(self.operators, FWD_INPUTS, BWD_INPUTS)
-        self.fwd = PartitionProgram(self.fwd_graph, n, backward=False, sync=sync)
-        self.bwd = PartitionProgram(self.bwd_graph, n, backward=True, sync=sync, reverse_nb=seq_split)
+        self.fwd = PartitionProgram(self.fwd_graph, n, backward=False, sync=sync, cp_keys=cp_keys)
+        self.bwd = PartitionProgram(self.bwd_graph, n, backward=True, sync=sync, reverse_nb=seq_split,
+                                    cp_keys=cp_keys)
 
 
 class BlockEngine:
     def __init__(self, layer_operators: Sequence[Sequence[GraphOperator]], num_nanobatches: int = 2,
                  recompute: bool = True, recompute_layers: Optional[int] = None,
-                 sync: str = "partition_end", scheduler=None, seq_split: bool = False):
+                 sync: str = "partition_end", scheduler=None, seq_split: bool = False, cp_keys: bool = False):
         self.layers = [list(ops) for ops in layer_operators]
         self.n = int(num_nanobatches)
         self.recompute = bool(recompute)
@@ -49,14 +51,14 @@ class BlockEngine:
         self.recompute_layers = L if recompute_layers is None else max(1, min(int(recompute_layers), L))
         all_ops = [op for ops in self.layers for op in ops]
         self.seq_split = seq_split
-        self.full = _Chunk(all_ops, self.n, sync, seq_split)
+        self.full = _Chunk(all_ops, self.n, sync, seq_split, cp_keys)
         self.chunks: List[_Chunk] = []
         self._boundary_ids: List[str] = []
         if self.recompute and self.recompute_layers < L:
             bounds = list(range(0, L, self.recompute_layers))
             for s in bounds:
                 ops = [op for l in self.layers[s:s + self.recompute_layers] for op in l]
-                self.chunks.append(_Chunk(ops, self.n, sync, seq_split))
+                self.chunks.append(_Chunk(ops, self.n, sync, seq_split, cp_keys))
             # tensor ids of the full forward graph that enter each chunk
             first_nodes = {id(c.operators[0]): i for i, c in enumerate(self.chunks)}
             ids: Dict[int, str] = {}

@@ -67,6 +67,8 @@ class Node:
     kind: Optional[CommKind] = None
     key: str = ""          # plan key of the compute segment this collective terminates
     backward: bool = False
+    segment: str = ""      # context-parallel plan vocabulary: segment name (qkv, ao, a, o, mlp) ...
+    short: str = ""        # ... and collective type (ar, ag, rs)
 
     @property
     def name(self) -> str:
@@ -93,6 +95,8 @@ class CommSpec:
     out_channels: Tuple[str, ...]
     key: str
     backward: bool = False
+    segment: str = ""
+    short: str = ""
 
 
 class GraphOperator:
@@ -185,7 +189,8 @@ class TensorGraphBuilder:
         is_comm = isinstance(spec, CommSpec)
         node = Node(index=len(self._nodes), op_id=operator_uid(spec.operator), operator=spec.operator, inputs=ins,
                     outputs=tuple(outs), is_comm=is_comm, kind=getattr(spec, "kind", None),
-                    key=getattr(spec, "key", ""), backward=spec.backward)
+                    key=getattr(spec, "key", ""), backward=spec.backward,
+                    segment=getattr(spec, "segment", ""), short=getattr(spec, "short", ""))
         self._nodes.append(node)
         return node
 

@@ -155,7 +155,7 @@ def _shared_comm_stream(device) -> "torch.cuda.Stream":
 
 class PartitionProgram:
     def __init__(self, graph: TensorGraph, num_nanobatches: int, backward: bool,
-                 sync: str = "partition_end", reverse_nb: bool = False):
+                 sync: str = "partition_end", reverse_nb: bool = False, cp_keys: bool = False):
         if sync not in ("partition_end", "lazy"):
             raise ValueError(sync)
         self.graph = graph
@@ -166,6 +166,9 @@ class PartitionProgram:
         # earlier ones, so the backward program visits nanobatches last-to-first
         self.nb_order = list(reversed(range(self.n))) if reverse_nb else list(range(self.n))
         self.trail_key = "bwd_trail" if backward else "fwd_trail"
+        # context-parallel plan files name a step after its compute segment AND the collective it
+        # carries (fwd_qkv_ar, fwd_qkv_ag, fwd_ao_ag, ...: reference transformer_block.py:193-203)
+        self.cp_keys = cp_keys
         self.segments = split_segments(graph.nodes, self.trail_key)
         self.steps = self._form_steps()
         self._last_use = self._compute_last_use()
@@ -185,6 +188,8 @@ class PartitionProgram:
                     pc = self.segments[ps].comm
                     if pc is not None:
                         st.comm, st.comm_nb, st.comm_segment = pc, pnb, ps
+                if self.cp_keys:
+                    st.key = self._cp_key(seg, st.comm)
                 steps.append(st)
                 prev = (seg.index, nb)
         if prev is not None and self.segments[prev[0]].comm is not None:
@@ -192,6 +197,16 @@ class PartitionProgram:
             steps.append(Step(index=len(steps), key=self.trail_key, nb=pnb, segment=ps + 1,
                               compute=[], comm=self.segments[ps].comm, comm_nb=pnb, comm_segment=ps))
         return steps
+
+    def _cp_key(self, seg: Segment, carried: Optional[Node]) -> str:
+        if seg.comm is None or not seg.comm.segment:
+            return seg.key
+        d = "bwd" if self.backward else "fwd"
+        name = seg.comm.segment
+        if name == "mlp":
+            return f"{d}_mlp"
+        short = carried.short if carried is not None and carried.short else seg.comm.short
+        return f"{d}_{name}_{short}"
 
     def expected_keys(self) -> List[str]:
         return [s.key for s in self.steps]

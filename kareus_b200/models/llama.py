@@ -104,7 +104,9 @@ class TransformerBlock(nn.Module):
                 l.core_attn.seq_nano = par.num_nanobatches
         self.engine = BlockEngine([l.operators() for l in self.layers], par.num_nanobatches,
                                   recompute=par.recompute, recompute_layers=recompute_layers, sync=sync,
-                                  seq_split=seq_split)
+                                  seq_split=seq_split,
+                                  cp_keys=(par.cp > 1 and par.tp > 1 and par.tp_comm == "allreduce"
+                                           and par.cp_comm == "all_gather"))
 
     def set_scheduler(self, scheduler) -> None:
         self.engine.scheduler = scheduler

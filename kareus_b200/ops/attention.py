@@ -178,7 +178,8 @@ class AttentionOp(GraphOperator):
         compute = ComputeSpec(self, self.in_channels, self.out_channels)
         if self.cp == 1 or self.cp_comm == "ring":
             return [compute]
-        return [CommSpec(self.ag_kv, CommKind.ALL_GATHER_KV, ("key", "value"), ("key", "value"), "fwd_qkv_ag"),
+        return [CommSpec(self.ag_kv, CommKind.ALL_GATHER_KV, ("key", "value"), ("key", "value"), "fwd_qkv_ag",
+                         segment="qkv", short="ag"),
                 compute]
 
     def backward_specs(self):
@@ -189,10 +190,10 @@ class AttentionOp(GraphOperator):
         # graph input (it re-reads the local shards kept by the forward), so it is modelled as a
         # pass-through on grad_main that stashes the gathered tensors for the compute node.
         return [CommSpec(_RegatherKV(self), CommKind.ALL_GATHER_KV, ("grad_main",), ("grad_main",),
-                         "bwd_a_ag", backward=True),
+                         "bwd_a_ag", backward=True, segment="o", short="ag"),
                 compute,
                 CommSpec(self.rs_kv, CommKind.REDUCE_SCATTER_KV, ("grad_key", "grad_value"),
-                         ("grad_key", "grad_value"), "bwd_a_rs", backward=True)]
+                         ("grad_key", "grad_value"), "bwd_a_rs", backward=True, segment="a", short="rs")]
 
     # compute --------------------------------------------------------------------
     def forward(self, ctx, q, k, v):

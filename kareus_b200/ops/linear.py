@@ -110,7 +110,8 @@ class ColumnParallelLinear(_LinearBase):
             return [compute]
         if self.tp_comm == "allreduce":
             return [compute, CommSpec(self.bwd_allreduce, CommKind.ALL_REDUCE, ("grad_main",), ("grad_main",),
-                                      f"bwd_{self.key}", backward=True)]
+                                      f"bwd_{self.key}", backward=True,
+                                      segment="qkv" if self.key == "attn" else "mlp", short="ar")]
         if self.tp_comm == "sp_fused" and self.fused_dgrad_rs is not None:
             return [CommSpec(self.fused_dgrad_rs, CommKind.FUSED, ("grad_main",), ("grad_main",),
                              f"bwd_{self.key}", backward=True)]
@@ -144,7 +145,7 @@ class RowParallelLinear(_LinearBase):
             return [compute]
         if self.tp_comm == "allreduce":
             return [compute, CommSpec(self.fwd_allreduce, CommKind.ALL_REDUCE, ("main",), ("main",),
-                                      f"fwd_{self.key}")]
+                                      f"fwd_{self.key}", segment="ao" if self.key == "attn" else "mlp", short="ar")]
         if self.tp_comm == "sp_fused" and self.fused_gemm_rs is not None:
             return [CommSpec(self.fused_gemm_rs, CommKind.FUSED, ("main",), ("main",), f"fwd_{self.key}")]
         return [compute, CommSpec(self.fwd_reducescatter, CommKind.REDUCE_SCATTER, ("main",), ("main",),

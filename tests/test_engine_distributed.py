@@ -126,3 +126,24 @@ def test_tp2_cp2_sp():
 def test_cp2_ring_attention():
     """Pull-based ring attention (chunk schedule + log-sum-exp merge + dKV reduce-scatter) on gloo."""
     run_distributed(_worker, 2, 1, 2, "allreduce", 2, True, False, "ring")
+
+
+def _cp_keys_worker(rank, world):
+    from kareus_b200.config import ParallelConfig, get_model_config
+    from kareus_b200.models.llama import GPTModel
+    from kareus_b200.parallel.mesh import Mesh
+    from kareus_b200.plan import FWD_KEYS_CP, BWD_KEYS_CP
+    par = ParallelConfig(tp=2, cp=2, num_nanobatches=2, tp_comm="allreduce")
+    m = GPTModel(get_model_config("tiny"), par, mesh=Mesh(tp=2, cp=2), dtype="fp32")
+    eng = m.decoder.engine
+    fk = [k for k in eng.full.fwd.expected_keys()]
+    bk = [k for k in eng.full.bwd.expected_keys()]
+    # the 5 forward and 7 backward keys of the reference's context-parallel plan files all occur
+    assert set(FWD_KEYS_CP) <= set(fk), fk
+    assert set(BWD_KEYS_CP) <= set(bk), bk
+    # one layer: qkv_ar/qkv_ag, ao_ag/ao_ar, mlp/mlp (skipping the very first step, which carries nothing)
+    assert fk[1:6] == ["fwd_qkv_ag", "fwd_ao_ag", "fwd_ao_ar", "fwd_mlp", "fwd_mlp"], fk[:8]
+
+
+def test_cp_plan_keys_match_reference_vocabulary():
+    run_distributed(_cp_keys_worker, 4)

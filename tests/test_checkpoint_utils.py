@@ -79,3 +79,41 @@ def test_debug_and_timers(tmp_path):
     t.on_instruction_begin("forward"); t.on_instruction_end("forward")
     out = t.export(tmp_path, 3, 1)
     assert out.name == "instructions-3-1.csv" and "forward-compute" in out.read_text()
+
+
+def test_yaml_run_config(tmp_path):
+    from kareus_b200.config_yaml import load_run_config
+    (tmp_path / "c.yaml").write_text("""
+name: megatron_llama3.2_3b
+trainer: {devices: 8, num_nodes: 2, precision: bf16, max_steps: 30, gradient_clip_val: 1.0}
+model:
+  micro_batch_size: 8
+  global_batch_size: 64
+  tensor_model_parallel_size: 8
+  pipeline_model_parallel_size: 2
+  context_parallel_size: 1
+  cp_comm_type: all_gather
+  num_layers_in_first_pipeline_stage: 15
+  encoder_seq_length: 4096
+  num_layers: 28
+  hidden_size: 3072
+  ffn_hidden_size: 8192
+  num_attention_heads: 24
+  kv_channels: 128
+  num_query_groups: 8
+  hidden_dropout: 0.1
+  layernorm_epsilon: 1e-5
+  enable_zeus_monitor: true
+  enable_kareus_scheduler: false
+  kareus_scheduler_kwargs: {solution_path: null}
+  activations_checkpoint_granularity: full
+  sequence_parallel: false
+  optim: {lr: 2e-4, weight_decay: 0.01, betas: [0.9, 0.98], sched: {warmup_steps: 500, min_lr: 2e-5}}
+""")
+    model, par, train, sw = load_run_config(tmp_path / "c.yaml", ["model.enable_kareus_scheduler=True",
+                                                                 "model.kareus_scheduler_kwargs.solution_path=/p/s.py",
+                                                                 "model.micro_batch_size=4"])
+    assert (model.num_layers, model.hd, model.num_layers_in_first_pipeline_stage) == (28, 128, 15)
+    assert (par.tp, par.pp, par.dp, par.recompute, par.tp_comm) == (8, 2, 1, True, "allreduce")
+    assert train.micro_batch_size == 4 and train.num_microbatches(1) == 16 and train.betas == (0.9, 0.98)
+    assert sw.enable_zeus_monitor and sw.enable_kareus_scheduler and sw.solution_path == "/p/s.py"

@@ -94,3 +94,22 @@ def test_sequence_split_nanobatches(n, recompute):
     ref_loss.backward()
     torch.testing.assert_close(loss.detach(), ref_loss.detach(), rtol=1e-9, atol=1e-10)
     _check(model, oracle)
+
+
+def test_gelu_and_geglu_ops_match_autograd():
+    from kareus_b200.engine.context import OpContext
+    from kareus_b200.ops.activations import GegluOp, GeluOp
+    for op, width in ((GeluOp(), 16), (GegluOp(), 32)):
+        x = torch.randn(3, 5, width, dtype=torch.float64, requires_grad=True)
+        ctx = OpContext()
+        (y,) = op.forward(ctx, x.detach())
+        if op.gated:
+            a, b = x[..., :16], x[..., 16:]
+            want = torch.nn.functional.gelu(a, approximate="tanh") * b
+        else:
+            want = torch.nn.functional.gelu(x, approximate="tanh")
+        torch.testing.assert_close(y, want.detach(), rtol=1e-9, atol=1e-10)
+        g = torch.randn_like(want)
+        want.backward(g)
+        (dx,) = op.backward(ctx, g)
+        torch.testing.assert_close(dx, x.grad, rtol=1e-8, atol=1e-9)

@@ -246,3 +246,19 @@ def test_flash_attention_backward_offsets():
                                        cid * c, (cid + 1) * c)
         assert _rel(dq, wq) < 2e-2 and _rel(dk, wk) < 2e-2 and _rel(dv, wv) < 2e-2
         assert dk[(cid + 1) * c:].abs().max().item() == 0
+
+
+def test_gelu_geglu_kernels():
+    from kareus_b200.engine.context import OpContext
+    from kareus_b200.ops.activations import GegluOp, GeluOp, gelu_grad_ref, gelu_ref
+    for op, width in ((GeluOp(), 1024), (GegluOp(), 2048)):
+        x = torch.randn(200, width, device="cuda").bfloat16()
+        ctx = OpContext()
+        (y,) = op.forward(ctx, x)
+        ctx2 = OpContext()
+        (yr,) = op.forward(ctx2, x.float())
+        assert _rel(y, yr) < 5e-3
+        g = torch.randn_like(y)
+        (dx,) = op.backward(ctx, g)
+        (dxr,) = op.backward(ctx2, g.float())
+        assert _rel(dx, dxr) < 5e-3

@@ -219,6 +219,33 @@ class SymmetricHeap:
         KC._count()
         return out
 
+    def auto_tune(self, kind: str, shape, dtype=torch.bfloat16, sm_candidates=(4, 8, 12, 16, 24, 32),
+                  block_candidates=(512, 1024), iters: int = 5):
+        """Time a collective over a small grid of launch shapes and return ``(best (sm, block), table)``.
+        Times are CUDA-event times, max over ranks (the reference's algorithm objects carry the same
+        kind of ``auto_tune()`` candidate sweep: ``mscclpp_benchmark/mscclpp_op.py``)."""
+        fn = {"all_reduce": self.all_reduce, "all_gather": self.all_gather, "reduce_scatter": self.reduce_scatter}[kind]
+        x = torch.ones(shape, dtype=dtype, device=self.device)
+        table = {}
+        for sm in sm_candidates:
+            for blk in block_candidates:
+                fn(x, nb=0, sm_num=sm, block_size=blk, tag=f"__tune_{kind}")
+                torch.cuda.synchronize(self.device)
+                if self.world > 1:
+                    dist.barrier(group=self.group)
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                for _ in range(iters):
+                    fn(x, nb=0, sm_num=sm, block_size=blk, tag=f"__tune_{kind}")
+                b.record()
+                torch.cuda.synchronize(self.device)
+                t = torch.tensor([a.elapsed_time(b) / iters], device=self.device)
+                if self.world > 1:
+                    dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+                table[(sm, blk)] = float(t.item())
+        best = min(table, key=table.get)
+        return best, table
+
     def wait_flag_probe(self, limit_ns: int = 200_000_000) -> None:
         """Launch a kernel that waits (bounded) on a flag nobody sets; the status word then holds the
         peer-timeout code.  Used to test the bounded-wait path without any peer."""

@@ -73,6 +73,16 @@ def main(case: str, reps: int = 3) -> None:
         p = w.bfloat16()
         for i in range(reps):
             KC.adamw_step(p, g, m, v, w, 1e-3, 0.9, 0.98, 1e-8, 0.01, i + 1)
+    elif case == "step":
+        # one training step of a 2-layer model with the 3B layer shape (1 microbatch of 8 x 4096)
+        from ..config import ParallelConfig, TrainConfig, get_model_config
+        from ..train.trainer import Trainer, synthetic_batch
+        cfg = get_model_config("llama3.2_3b").replace(num_layers=2, vocab_size=32768)
+        tc = TrainConfig(micro_batch_size=8, global_batch_size=8, seq_len=4096, warmup_steps=0)
+        tr = Trainer(cfg, ParallelConfig(num_nanobatches=2, recompute=True), tc, device=dev, recompute_layers=2)
+        batch = synthetic_batch(cfg, tc, 1, seed=0)
+        for _ in range(reps):
+            tr.train_step(batch)
     else:
         raise SystemExit(f"unknown case {case!r}")
     torch.cuda.synchronize()

@@ -32,3 +32,18 @@ def test_compare_cli(tmp_path, capsys):
     assert cli_compare.main(["--base", str(tmp_path / "megatron"), "--runs", str(tmp_path / "kareus")]) == 0
     lines = [json.loads(l) for l in capsys.readouterr().out.strip().splitlines()]
     assert lines[1]["time_reduction_pct"] == pytest.approx(20.0)
+
+
+def test_perseus_profile_and_frequency_only_plan(tmp_path, capsys):
+    from kareus_b200.cli import run_perseus_profile
+    from kareus_b200.compose import run_optimization
+    out = tmp_path / "perseus.csv"
+    rc = run_perseus_profile.main(["--model", "tiny", "--mbs", "2", "--gbs", "4", "--seq", "32", "--steps", "2",
+                                   "--skip", "0", "--freqs", "1500", "1200", "900", "--out", str(out)])
+    assert rc == 0
+    rows = out.read_text().strip().splitlines()
+    assert rows[0] == "stage,instruction,frequency,time,energy" and len(rows) == 1 + 2 * 3
+    summary = run_optimization(out, tmp_path / "plans", num_stages=1, num_mbs=2, gpu_type="B200", unit_time=1e-4,
+                               use_native=False, max_iterations=5)
+    assert (tmp_path / "plans" / "freqs_pipeline_00000.py").exists() or summary == []
+    assert not list((tmp_path / "plans").glob("scheds_pipeline_*.py"))

@@ -300,10 +300,11 @@ extern "C" int kb_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
     return ST_BAD_ARG;
   if (num_sms <= 0) num_sms = device_sm_count();
   {
-    // large problems: 256x256 tile per SM (a third less L2 traffic per FLOP), see gemm256_sm100.cu
+    // large problems with a long K loop: 256x256 tile per SM (a third less L2 traffic per FLOP; its
+    // epilogue is not overlapped, which only pays off when the main loop is long), see gemm256_sm100.cu
     static const bool allow256 = [] { const char* e = getenv("KB_GEMM256"); return !(e && e[0] == '0'); }();
     const long tiles256 = (long)((M + 255) / 256) * ((N + 255) / 256);
-    if (allow256 && M >= 512 && N >= 512 && K >= 512 && (N % 256 == 0 || N >= 4096) && tiles256 >= num_sms)
+    if (allow256 && M >= 512 && N >= 512 && K >= 2048 && (N % 256 == 0 || N >= 4096) && tiles256 >= num_sms)
       return gemm256_dispatch(A, B, C, M, N, K, a_mn, lda, b_mn, ldb, ldc, out_f32, accumulate, num_sms, status,
                               stream);
   }

@@ -13,6 +13,7 @@ linear operator's own context: these nodes share its graph uid.
 """
 from __future__ import annotations
 
+import os
 import re
 from ctypes import c_int, c_uint32, c_uint64, c_void_p
 
@@ -38,6 +39,12 @@ def _lib():
             getattr(L, n).restype = c_int
         _DECLARED = True
     return L
+
+
+def _fused_sms() -> int:
+    """SMs a fused kernel may occupy (copy drivers + GEMM CTAs); 0 = all.  When the kernel is link
+    bound, fewer GEMM CTAs lose nothing and leave SMs to the other nanobatch's compute."""
+    return int(os.environ.get("KAREUS_FUSED_SMS", "0"))
 
 
 class _FusedBase:
@@ -80,7 +87,7 @@ class _FusedBase:
         st = KC.status_word(x2.device)
         rc = _lib().kb_ag_gemm_bf16(heap._bases_arr, rank, world, ch.flag_off, off, w.data_ptr(), y.data_ptr(), m,
                                     n_out, k, w.stride(0), 1 if b_mn else 0, ready.data_ptr(), ch.epoch,
-                                    int(sm_num or self.default_sm), 0, st.data_ptr(), KC._stream())
+                                    int(sm_num or self.default_sm), _fused_sms(), st.data_ptr(), KC._stream())
         KC._check(rc, f"ag_gemm {self.name}")
         KC._count()
         return y, xg
@@ -106,7 +113,7 @@ class _FusedBase:
         st = KC.status_word(a2.device)
         rc = L.kb_gemm_rs_bf16(heap._bases_arr, rank, world, ch.flag_off, stage_off, cnt_off, a2.data_ptr(),
                                a2.stride(0), w.data_ptr(), w.stride(0), 1 if b_mn else 0, out.data_ptr(), m, n_out, k,
-                               go.data_ptr(), ch.epoch, int(sm_num or self.default_sm), 0, st.data_ptr(),
+                               go.data_ptr(), ch.epoch, int(sm_num or self.default_sm), _fused_sms(), st.data_ptr(),
                                KC._stream())
         KC._check(rc, f"gemm_rs {self.name}")
         KC._count()

@@ -36,6 +36,8 @@ def main(argv=None) -> int:
     ap.add_argument("--measure-s", type=float, default=5.0)
     ap.add_argument("--cooldown-s", type=float, default=5.0)
     ap.add_argument("--nano", type=int, nargs="*", default=[2])
+    ap.add_argument("--freqs", type=int, nargs="*", default=None,
+                    help="restrict the clock grid (default: the GPU type's full grid)")
     a = ap.parse_args(argv)
 
     import torch.distributed as dist
@@ -64,7 +66,7 @@ def main(argv=None) -> int:
     base = run_dir(a.out, a.model_name, cp, tp, a.batch_size, a.seq_len)
     monitor = EnergyMonitor([local] if cuda else [0])
     ctl = FrequencyController(local, a.clock_mode)
-    freqs = get_freq_grid(a.gpu_type)
+    freqs = list(a.freqs) if a.freqs else get_freq_grid(a.gpu_type)
 
     if a.nonpartition:
         from ..models.llama import GPTModel

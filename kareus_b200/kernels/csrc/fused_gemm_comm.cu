@@ -59,7 +59,7 @@ struct FgSmem {
   static constexpr int B_BYTES = BN * FG_BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int TILE_BYTES = STAGE_BYTES * FG_STAGES;
-  static constexpr int TOTAL = TILE_BYTES + 256 + 1024;
+  static constexpr int TOTAL = TILE_BYTES + 256 + 4 * 4096 + 1024;   // + per-warp epilogue staging
 };
 
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
@@ -334,9 +334,8 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       const int m0 = tm * FG_BM, n0 = tn * BN;
       if (!mbar_wait(&tfull[buf], bph, abort_flag, status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
-      const int row = m0 + q * 32 + lane;
       const uint32_t taddr = tmem_base + buf * BN + (static_cast<uint32_t>(q * 32) << 16);
-      __nv_bfloat16* crow;
+      __nv_bfloat16* cbase;        // row 0 of this warp's 32 rows in the destination
       if (p.mode == MODE_RS) {
         if (!go_seen) {
           if (!wait_u32_ge(p.go, p.epoch, false, status, ST_TIMEOUT_PEER, abort_flag)) { ok = false; break; }
@@ -345,31 +344,44 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         const int owner = tm / tiles_per_rank;
         __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(c.base[owner] + p.stage_off) +
                                static_cast<long>(c.rank) * p.rows_per_rank * N;
-        crow = stage + static_cast<long>(row - owner * p.rows_per_rank) * N;
+        cbase = stage + static_cast<long>(m0 + q * 32 - owner * p.rows_per_rank) * N;
       } else {
-        crow = p.out + static_cast<long>(row) * N;
+        cbase = p.out + static_cast<long>(m0 + q * 32) * N;
       }
+      // Accumulator → bf16 → this warp's 4 KB of shared memory (32 rows x 128 B, 16-byte units
+      // XOR-swizzled by row) → global/peer memory as full 128-byte row segments.  Writing straight
+      // from registers would give every lane its own row, i.e. 16-byte scattered writes, which
+      // NVLink carries at a fraction of its bandwidth.
+      uint8_t* stg = smem + S::TILE_BYTES + 256 + q * 4096;
 #pragma unroll 1
-      for (int cc = 0; cc < BN / 32; ++cc) {
-        uint32_t v[32];
-        tmem_ld_32x32(taddr + cc * 32, v);
-        tmem_ld_wait();
-        const int col = n0 + cc * 32;
-        if (row < M && col < N) {
-          if (col + 32 <= N && (N & 7) == 0) {
+      for (int cp = 0; cp < BN / 64; ++cp) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              uint4 o;
-              o.x = pack_bf16x2(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
-              o.y = pack_bf16x2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
-              o.z = pack_bf16x2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
-              o.w = pack_bf16x2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
-              reinterpret_cast<uint4*>(crow + col)[j] = o;
-            }
-          } else {
-            for (int j = 0; j < 32 && col + j < N; ++j) crow[col + j] = __float2bfloat16(__uint_as_float(v[j]));
+        for (int half = 0; half < 2; ++half) {
+          uint32_t v[32];
+          tmem_ld_32x32(taddr + (cp * 2 + half) * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
+            o.y = pack_bf16x2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
+            o.z = pack_bf16x2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
+            o.w = pack_bf16x2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
+            const int unit = half * 4 + j;
+            *reinterpret_cast<uint4*>(stg + lane * 128 + ((unit ^ (lane & 7)) << 4)) = o;
           }
         }
+        __syncwarp();
+        const int u = lane & 7;
+        const int col = n0 + cp * 64 + u * 8;
+#pragma unroll
+        for (int it4 = 0; it4 < 8; ++it4) {
+          const int r = it4 * 4 + (lane >> 3);
+          const uint4 o = *reinterpret_cast<const uint4*>(stg + r * 128 + ((u ^ (r & 7)) << 4));
+          if (m0 + q * 32 + r < M && col + 8 <= N)
+            *reinterpret_cast<uint4*>(cbase + static_cast<long>(r) * N + col) = o;
+        }
+        __syncwarp();
       }
       tc_fence_before();
       if (p.mode == MODE_RS) {

@@ -136,7 +136,8 @@ def main() -> int:
     if world > 1 and (par.comm_backend == "kernel" or par.tp_comm == "sp_fused"):
         from kareus_b200.parallel.symm_heap import SymmetricHeap
         heap = SymmetricHeap.create(mesh.group("tp"), device)
-    trainer = Trainer(cfg, par, tc, mesh=mesh, device=device, heap=heap, recompute_layers=args.recompute_layers)
+    trainer = Trainer(cfg, par, tc, mesh=mesh, device=device, heap=heap, recompute_layers=args.recompute_layers,
+                      sync=os.environ.get("KAREUS_SYNC", "partition_end"))
     trainer.model.decoder.engine.default_shape = (args.comm_sm, 1024)
     M = trainer.num_microbatches
     host_batches = [synthetic_batch(cfg, tc, M, seed=1000 + i) for i in range(2)]

@@ -100,6 +100,10 @@ class BlockEngine:
             c.store.put(chunk.bwd_graph.initial["grad_main"], g)
         chunk.bwd.run(ctxs, schedule=self.current_schedule(), streams=self._streams(grads[0]),
                       default_shape=self.default_shape)
+        if grads[0].is_cuda:
+            from .program import _per_nb_streams, _shared_comm_stream
+            if _per_nb_streams():       # weight-gradient GEMMs funnelled through the ordered side stream
+                torch.cuda.current_stream(grads[0].device).wait_stream(_shared_comm_stream(grads[0].device, 0))
         out_id = chunk.bwd_graph.final["grad_main"]
         return [c.store.get(out_id) for c in ctxs]
 

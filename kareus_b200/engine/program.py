@@ -128,6 +128,17 @@ class StreamSet:
             self._comm = _shared_comm_stream(self.device)
         return self._comm
 
+    def comm_for(self, nb: int):
+        """Side stream of a nanobatch.  By default all nanobatches share one ordered side stream (the
+        reference's single comm stream); with ``KAREUS_COMM_STREAMS=per_nanobatch`` each nanobatch
+        gets its own, so two fused GEMM+collective kernels (one link bound, one compute bound) can
+        run side by side."""
+        if not self.cuda:
+            return None
+        if _per_nb_streams():
+            return _shared_comm_stream(self.device, slot=1 + nb)
+        return self.comm
+
     def compute(self):
         return torch.cuda.current_stream(self.device) if self.cuda else None
 
@@ -139,18 +150,23 @@ class StreamSet:
         return ev
 
 
-_COMM_STREAMS: Dict[int, "torch.cuda.Stream"] = {}
+_COMM_STREAMS: Dict[tuple, "torch.cuda.Stream"] = {}
 
 
-def _shared_comm_stream(device) -> "torch.cuda.Stream":
+def _per_nb_streams() -> bool:
+    import os
+    return os.environ.get("KAREUS_COMM_STREAMS", "shared") == "per_nanobatch"
+
+
+def _shared_comm_stream(device, slot: int = 0) -> "torch.cuda.Stream":
     """One side stream per device shared by all collectives, which keeps them ordered among
     themselves (reference ``kareus/msccl/msccl_comm.py:577``)."""
     idx = torch.device(device).index
     if idx is None:
         idx = torch.cuda.current_device()
-    if idx not in _COMM_STREAMS:
-        _COMM_STREAMS[idx] = torch.cuda.Stream(device=idx, priority=-1)
-    return _COMM_STREAMS[idx]
+    if (idx, slot) not in _COMM_STREAMS:
+        _COMM_STREAMS[(idx, slot)] = torch.cuda.Stream(device=idx, priority=-1)
+    return _COMM_STREAMS[(idx, slot)]
 
 
 class PartitionProgram:
@@ -305,7 +321,7 @@ class PartitionProgram:
         nbctx = ctxs[nb]
         store = nbctx.store
         ins = [store.get(p.tensor_id) for p in node.inputs]
-        side = streams.comm
+        side = streams.comm_for(nb)
         if streams.cuda:
             ready = nbctx.ready_event.get(st.comm_segment)
             if ready is not None:

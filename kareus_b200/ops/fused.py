@@ -47,6 +47,24 @@ def _fused_sms() -> int:
     return int(os.environ.get("KAREUS_FUSED_SMS", "0"))
 
 
+def _wgrad(dy2, x, weight) -> None:
+    """``main_grad += dy2ᵀ·x``.  With one side stream per nanobatch two nanobatches' wgrads of the same
+    weight could overlap and lose updates, so they are funnelled through one ordered stream; the block
+    engine makes the compute stream wait for it at the end of backward."""
+    from ..engine.program import _per_nb_streams, _shared_comm_stream
+    acc = ensure_main_grad(weight)
+    if not (_per_nb_streams() and dy2.is_cuda):
+        K.gemm(dy2, x, trans_a=True, trans_b=False, accumulate=acc)
+        return
+    cur = torch.cuda.current_stream(dy2.device)
+    ws = _shared_comm_stream(dy2.device, slot=0)
+    ws.wait_stream(cur)
+    with torch.cuda.stream(ws):
+        K.gemm(dy2, x, trans_a=True, trans_b=False, accumulate=acc)
+    dy2.record_stream(ws)
+    x.record_stream(ws)
+
+
 class _FusedBase:
     needs_ctx = True
     group = "linear"
@@ -155,7 +173,7 @@ class FusedDgradRS(_FusedBase):
         (x_full,) = ctx.saved_tensors
         lead = dy.shape[:-1]
         dx, dy2 = self._gemm_rs(dy.reshape(-1, dy.shape[-1]), lin.weight, lin.in_features, True, sm_num, nb)
-        K.gemm(dy2, x_full, trans_a=True, trans_b=False, accumulate=ensure_main_grad(lin.weight))
+        _wgrad(dy2, x_full, lin.weight)
         ctx.clear()
         return (dx.reshape((lead[0] // self.heap.world,) + tuple(lead[1:]) + (lin.in_features,)),)
 
@@ -169,7 +187,8 @@ class FusedAGDgrad(_FusedBase):
         (a2,) = ctx.saved_tensors
         lead = dy.shape[:-1]
         dx, dyg = self._ag_gemm(dy.reshape(-1, dy.shape[-1]), lin.weight, lin.in_features, True, sm_num, nb)
-        K.gemm(dyg, a2, trans_a=True, trans_b=False, accumulate=ensure_main_grad(lin.weight))
+        _wgrad(dyg, a2, lin.weight)
+        dx.record_stream(torch.cuda.current_stream(dx.device))
         ctx.clear()
         return (dx.reshape((lead[0] * self.heap.world,) + tuple(lead[1:]) + (lin.in_features,)),)
 

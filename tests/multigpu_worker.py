@@ -123,7 +123,8 @@ def test_model_modes(heap, rank, world, dev):
                              ("sp_fused", "kernel")]:
         par = ParallelConfig(tp=world, num_nanobatches=2, tp_comm=tp_comm, comm_backend=backend, recompute=True)
         try:
-            tr = Trainer(cfg, par, tc, mesh=mesh, device=dev, heap=heap)
+            tr = Trainer(cfg, par, tc, mesh=mesh, device=dev, heap=heap,
+                         sync=os.environ.get("KAREUS_SYNC", "partition_end"))
         except NotImplementedError:
             continue
         tr.model.decoder.engine.default_shape = (8, 1024)

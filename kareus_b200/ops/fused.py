@@ -44,7 +44,14 @@ def _lib():
 def _fused_sms() -> int:
     """SMs a fused kernel may occupy (copy drivers + GEMM CTAs); 0 = all.  When the kernel is link
     bound, fewer GEMM CTAs lose nothing and leave SMs to the other nanobatch's compute."""
-    return int(os.environ.get("KAREUS_FUSED_SMS", "0"))
+    n = int(os.environ.get("KAREUS_FUSED_SMS", "0"))
+    from ..engine.program import _per_nb_streams
+    if n == 0 and _per_nb_streams():
+        # two fused kernels (one per nanobatch stream) must be able to be resident together on every
+        # rank: if each may fill the GPU, ranks can start them in different orders and wait for each
+        # other forever (the bounded waits then report a peer timeout)
+        n = KC.sm_count() // 2
+    return n
 
 
 def _wgrad(dy2, x, weight) -> None:

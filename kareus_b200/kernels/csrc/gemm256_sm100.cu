@@ -20,7 +20,7 @@ constexpr int G2_A_BYTES = G2_BM * G2_BK * 2;   // 32 KB
 constexpr int G2_B_BYTES = G2_BN * G2_BK * 2;   // 32 KB
 constexpr int G2_STAGE_BYTES = G2_A_BYTES + G2_B_BYTES;
 constexpr int G2_TILE_BYTES = G2_STAGE_BYTES * G2_STAGES;
-constexpr int G2_SMEM = G2_TILE_BYTES + 256 + 1024;
+constexpr int G2_SMEM = G2_TILE_BYTES + 256 + 4 * 4096 + 1024;   // + per-warp epilogue staging
 
 __device__ __forceinline__ void g2_tile_coords(int t, int tiles_m, int tiles_n, int group_m, int& tm, int& tn) {
   const int per_group = group_m * tiles_n;
@@ -152,6 +152,45 @@ gemm256_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       for (int h = 0; h < 2; ++h) {
         const int row = m0 + h * 128 + q * 32 + lane;
         const uint32_t taddr = tmem_base + h * G2_BN + (static_cast<uint32_t>(q * 32) << 16);
+        if constexpr (!OUT_F32) {
+          // bf16 rows go through 4 KB of shared memory per warp so that stores are full 128-byte row
+          // segments (see gemm_sm100.cu)
+          if ((ldc & 7) == 0 && (N & 7) == 0) {
+            uint8_t* stg = smem + G2_TILE_BYTES + 256 + q * 4096;
+            __nv_bfloat16* cbase = reinterpret_cast<__nv_bfloat16*>(Cout) + static_cast<size_t>(m0 + h * 128 + q * 32) * ldc;
+#pragma unroll 1
+            for (int cp = 0; cp < G2_BN / 64; ++cp) {
+#pragma unroll
+              for (int half = 0; half < 2; ++half) {
+                uint32_t v[32];
+                tmem_ld_32x32(taddr + (cp * 2 + half) * 32, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  uint4 o;
+                  o.x = pack_bf16x2(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
+                  o.y = pack_bf16x2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
+                  o.z = pack_bf16x2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
+                  o.w = pack_bf16x2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
+                  const int unit = half * 4 + j;
+                  *reinterpret_cast<uint4*>(stg + lane * 128 + ((unit ^ (lane & 7)) << 4)) = o;
+                }
+              }
+              __syncwarp();
+              const int u = lane & 7;
+              const int col = n0 + cp * 64 + u * 8;
+#pragma unroll
+              for (int it4 = 0; it4 < 8; ++it4) {
+                const int r = it4 * 4 + (lane >> 3);
+                const uint4 o = *reinterpret_cast<const uint4*>(stg + r * 128 + ((u ^ (r & 7)) << 4));
+                if (m0 + h * 128 + q * 32 + r < M && col + 8 <= N)
+                  *reinterpret_cast<uint4*>(cbase + static_cast<size_t>(r) * ldc + col) = o;
+              }
+              __syncwarp();
+            }
+            continue;
+          }
+        }
 #pragma unroll 1
         for (int c = 0; c < G2_BN / 32; ++c) {
           uint32_t v[32];

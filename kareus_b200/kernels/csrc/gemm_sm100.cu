@@ -32,7 +32,7 @@ struct GemmSmem {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int TILE_BYTES = STAGE_BYTES * GEMM_STAGES;
   static constexpr int BAR_BYTES = 256;
-  static constexpr int TOTAL = TILE_BYTES + BAR_BYTES + 1024;  // + alignment slack
+  static constexpr int TOTAL = TILE_BYTES + BAR_BYTES + 4 * 4096 + 1024;  // + epilogue staging + alignment slack
 };
 
 // Tile rasterisation: m-tiles are taken in groups of `group_m`; inside a group the m index runs
@@ -178,6 +178,49 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
       const uint32_t taddr = tmem_base + buf * BN + (static_cast<uint32_t>(q * 32) << 16);
+      if constexpr (!OUT_F32) {
+        // bf16 output with 16-byte aligned rows: go through this warp's 4 KB of shared memory (32 rows
+        // x 128 B, 16-byte units XOR-swizzled by row) so every store instruction writes four full
+        // 128-byte row segments instead of 32 scattered 16-byte pieces
+        if ((ldc & 7) == 0 && (N & 7) == 0) {
+          uint8_t* stg = smem + S::TILE_BYTES + S::BAR_BYTES + q * 4096;
+          __nv_bfloat16* cbase = reinterpret_cast<__nv_bfloat16*>(Cout) + static_cast<size_t>(m0 + q * 32) * ldc;
+#pragma unroll 1
+          for (int cp = 0; cp < BN / 64; ++cp) {
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+              uint32_t v[32];
+              tmem_ld_32x32(taddr + (cp * 2 + half) * 32, v);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint4 o;
+                o.x = pack_bf16x2(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
+                o.y = pack_bf16x2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
+                o.z = pack_bf16x2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
+                o.w = pack_bf16x2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
+                const int unit = half * 4 + j;
+                *reinterpret_cast<uint4*>(stg + lane * 128 + ((unit ^ (lane & 7)) << 4)) = o;
+              }
+            }
+            __syncwarp();
+            const int u = lane & 7;
+            const int col = n0 + cp * 64 + u * 8;
+#pragma unroll
+            for (int it4 = 0; it4 < 8; ++it4) {
+              const int r = it4 * 4 + (lane >> 3);
+              const uint4 o = *reinterpret_cast<const uint4*>(stg + r * 128 + ((u ^ (r & 7)) << 4));
+              if (m0 + q * 32 + r < M && col + 8 <= N)
+                *reinterpret_cast<uint4*>(cbase + static_cast<size_t>(r) * ldc + col) = o;
+            }
+            __syncwarp();
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tempty[buf]);
+          continue;
+        }
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t v[32];

@@ -168,6 +168,41 @@ def test_ring_attention(heap, rank, world, dev):
     assert losses["ring"][-1] < losses["ring"][0]
 
 
+def perf_fused(heap, rank, world, dev):
+    """CUDA-event timings (max over ranks) of the fused kernels on the 3B layer shapes for this TP size."""
+    from types import SimpleNamespace
+    from kareus_b200.engine.context import OpContext
+    from kareus_b200.ops.fused import FusedAGGemm, FusedGemmRS
+    M, H, F, HEADS, KV, D = 16384, 3072, 8192, 24, 8, 128
+    shapes = {"qkv": (H, (HEADS + 2 * KV) * D // world, "ag"), "fc1": (H, 2 * F // world, "ag"),
+              "proj": (HEADS * D // world, H, "rs"), "fc2": (F // world, H, "rs")}
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    for name, (k, n, kind) in shapes.items():
+        w = (torch.randn(n, k, device=dev) * 0.02).bfloat16()
+        lin = SimpleNamespace(name=f"perf_{name}", out_features=n, in_features=k, weight=w)
+        op = FusedAGGemm(lin, heap, 16) if kind == "ag" else FusedGemmRS(lin, heap, 16)
+        x = torch.randn(M // world if kind == "ag" else M, 1, k, device=dev).bfloat16()
+        ctx = OpContext(); ctx.requires_grad = False
+        times = []
+        for i in range(8):
+            flush.zero_()
+            dist.barrier(); torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); op.run((x,), sm_num=16, nb=0, ctx=ctx); b.record(); torch.cuda.synchronize()
+            t = torch.tensor([a.elapsed_time(b)], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            if i >= 3:
+                times.append(t.item())
+        times.sort()
+        ms = times[len(times) // 2]
+        flops = 2.0 * M * n * k
+        link_bytes = (world - 1) / world * M * (k if kind == "ag" else n) * 2
+        if rank == 0:
+            print(f"fused {kind}_{name} tp{world}: M={M} N={n} K={k}: {ms*1e3:.1f} us; gemm {flops/1e12/ (ms/1e3):.0f} TFLOP/s; "
+                  f"link {link_bytes/1e6:.0f} MB -> {link_bytes/1e9/(ms/1e3):.0f} GB/s per direction; "
+                  f"roofline max(gemm@1669TF {flops/1669e12*1e6:.0f} us, link@770GB/s {link_bytes/770e9*1e6:.0f} us)", flush=True)
+
+
 def main():
     from kareus_b200.parallel.mesh import init_distributed
     from kareus_b200.parallel.symm_heap import SymmetricHeap
@@ -182,6 +217,8 @@ def main():
         test_fused_gemm_collectives(heap, rank, world, dev)
     if which in ("all", "ring"):
         test_ring_attention(heap, rank, world, dev)
+    if which == "perf":
+        perf_fused(heap, rank, world, dev)
     if which in ("all", "wait"):
         test_bounded_wait(heap, dev)
     if which in ("all", "model"):

@@ -75,6 +75,7 @@ class SymmetricHeap:
         self._flag_top = 0
         self._data_top = FLAG_REGION
         self.channels: Dict[str, Channel] = {}
+        self._views: Dict[tuple, torch.Tensor] = {}
         self.closed = False
         if world > 1:
             dist.barrier(group=group)
@@ -151,6 +152,16 @@ class SymmetricHeap:
         KC._count()
 
     def view(self, off: int, shape, dtype) -> torch.Tensor:
+        key = (off, tuple(shape), dtype)
+        hit = self._views.get(key)
+        if hit is not None:
+            return hit
+        t = self._make_view(off, shape, dtype)
+        if len(self._views) < 4096:
+            self._views[key] = t
+        return t
+
+    def _make_view(self, off: int, shape, dtype) -> torch.Tensor:
         n = 1
         for s in shape:
             n *= s

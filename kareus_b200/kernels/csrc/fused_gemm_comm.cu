@@ -383,7 +383,11 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         }
         __syncwarp();
       }
+      // the accumulator has been drained: hand the TMEM buffer back before the (slow) system-scope
+      // fence, so the MMA warp is not held up by the publication of this tile
       tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[buf]);
       if (p.mode == MODE_RS) {
         // publish this warp's 32 rows of the tile to the owner
         __threadfence_system();
@@ -394,9 +398,8 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                           (static_cast<long>(c.rank) * tiles_per_rank + (tm - owner * tiles_per_rank)) * tiles_n + tn;
           red_release_sys_add_u32(cnt, 1u);
         }
+        __syncwarp();
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&tempty[buf]);
     }
   }
 
@@ -503,7 +506,9 @@ extern "C" int kb_gemm_rs_bf16(void* const* bases, int rank, int world, uint64_t
   const bool narrow = (N <= 128) || (N % 256 != 0 && N % 256 <= 128);
   const int bn = narrow ? 128 : 256;
   const int tiles = (M / FG_BM) * ((N + bn - 1) / bn);
-  if (n_comm > num_sms / 2) n_comm = num_sms / 2;
+  // the GEMM CTAs join the reduction when their tiles are done, so a few dedicated reducer CTAs (for
+  // the start barrier and the early tiles) are enough
+  if (n_comm > 4) n_comm = 4;
   p.n_last = n_comm;
   p.n_gemm = num_sms - n_comm < tiles ? num_sms - n_comm : tiles;   // reducers get SMs of their own
   if (narrow) return b_mn ? launch_fused<128, true>(A, W, p, M, N, K, lda, ldw, stream)

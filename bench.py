@@ -101,8 +101,10 @@ def main() -> int:
     ap.add_argument("--gbs", type=int, default=64)
     ap.add_argument("--seq", type=int, default=4096)
     ap.add_argument("--nano", type=int, default=int(os.environ.get("KAREUS_NANOBATCHES", "2")))
-    ap.add_argument("--tp-comm", default=os.environ.get("KAREUS_TP_COMM", "allreduce"))
-    ap.add_argument("--comm-backend", default=os.environ.get("KAREUS_COMM_BACKEND", "nccl"))
+    ap.add_argument("--tp-comm", default=os.environ.get("KAREUS_TP_COMM"),
+                    help="allreduce | sp | sp_fused (default: sp_fused, the fused GEMM+collective kernels)")
+    ap.add_argument("--comm-backend", default=os.environ.get("KAREUS_COMM_BACKEND"),
+                    help="nccl | kernel (default: kernel, peer-memory collectives of this package)")
     ap.add_argument("--recompute-layers", type=int, default=int(os.environ.get("KAREUS_RECOMPUTE_LAYERS", "4")))
     ap.add_argument("--comm-sm", type=int, default=int(os.environ.get("KAREUS_COMM_SM", "16")),
                     help="CTAs given to a collective (plan knob sm_num) when no plan file is loaded")
@@ -127,6 +129,20 @@ def main() -> int:
     device = torch.device("cuda", local)
     KC.lib()
 
+    # Defaults for N > 1: the product path (fused all-gather→GEMM / GEMM→reduce-scatter kernels over
+    # peer memory).  `--tp-comm allreduce --comm-backend nccl` is the reference-like NCCL baseline.
+    if args.tp_comm is None:
+        args.tp_comm = "sp_fused"
+    if args.comm_backend is None:
+        args.comm_backend = "kernel"
+    if world > 1 and args.tp_comm == "sp_fused":
+        os.environ.setdefault("KAREUS_SYNC", "lazy")
+        if world >= 4:
+            # two nanobatches' fused kernels side by side, each on half of the SMs
+            os.environ.setdefault("KAREUS_COMM_STREAMS", "per_nanobatch")
+            os.environ.setdefault("KAREUS_FUSED_SMS", "72")
+            if "KAREUS_COMM_SM" not in os.environ:
+                args.comm_sm = 12
     cfg = get_model_config(args.model)
     tc = TrainConfig(micro_batch_size=args.mbs, global_batch_size=args.gbs, seq_len=args.seq, dtype="bf16")
     par = ParallelConfig(tp=world, num_nanobatches=args.nano, tp_comm=args.tp_comm if world > 1 else "allreduce",
@@ -215,7 +231,10 @@ def main() -> int:
             "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights",
             "config": {"model": args.model, "global_batch": args.gbs, "micro_batch": args.mbs, "seq_len": args.seq,
                        "parallelism": f"tp{world}", "nanobatches": args.nano, "tp_comm": par.tp_comm,
-                       "comm_backend": par.comm_backend, "comm_sm": args.comm_sm, "recompute": f"full, {args.recompute_layers} layers per chunk",
+                       "comm_backend": par.comm_backend, "comm_sm": args.comm_sm,
+                       "sync": os.environ.get("KAREUS_SYNC", "partition_end"),
+                       "comm_streams": os.environ.get("KAREUS_COMM_STREAMS", "shared"),
+                       "fused_sms": os.environ.get("KAREUS_FUSED_SMS", "0"), "recompute": f"full, {args.recompute_layers} layers per chunk",
                        "optimizer": "AdamW fp32 master, in the timed region",
                        "l2": "inputs larger than L2 (6.4 GB of weights and multi-GB activations per step)"},
             "energy_j_per_step": float(en.item()) / args.steps,

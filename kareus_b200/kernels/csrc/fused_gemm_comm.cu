@@ -149,24 +149,45 @@ __device__ void rs_reduce_items(const FusedParams& p, int N, int tiles_n, int BN
     if (*ok_slot == 0) return;
     const int cols = min(BN, N - tn * BN);
     const int vec_per_row = cols >> 3;
-    for (int v = threadIdx.x; v < FG_BM * vec_per_row; v += blockDim.x) {
-      const int row = tm * FG_BM + v / vec_per_row;
-      const int col = tn * BN + (v % vec_per_row) * 8;
-      float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      for (int s = 0; s < c.world; ++s) {
-        const uint4 u = *reinterpret_cast<const uint4*>(stage + s * slot_elems + static_cast<long>(row) * N + col);
-        const __nv_bfloat162* x = reinterpret_cast<const __nv_bfloat162*>(&u);
+    const int nvec = FG_BM * vec_per_row;
+    // four independent vectors per thread and step: world x 4 loads are in flight before the first
+    // add, which is what lets 192 threads per SM pull HBM bandwidth
+    for (int v0 = threadIdx.x; v0 < nvec; v0 += 4 * blockDim.x) {
+      uint4 u[4][MAX_PEERS];
+      long offs[4];
+      bool on[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float2 t = __bfloat1622float2(x[i]);
-          f[2 * i] += t.x;
-          f[2 * i + 1] += t.y;
-        }
+      for (int j = 0; j < 4; ++j) {
+        const int v = v0 + j * blockDim.x;
+        on[j] = v < nvec;
+        const int row = tm * FG_BM + (on[j] ? v / vec_per_row : 0);
+        const int col = tn * BN + (on[j] ? (v % vec_per_row) * 8 : 0);
+        offs[j] = static_cast<long>(row) * N + col;
+#pragma unroll
+        for (int s2 = 0; s2 < MAX_PEERS; ++s2)
+          if (s2 < c.world && on[j]) u[j][s2] = *reinterpret_cast<const uint4*>(stage + s2 * slot_elems + offs[j]);
       }
-      uint4 o;
-      o.x = pack_bf16x2(f[0], f[1]); o.y = pack_bf16x2(f[2], f[3]);
-      o.z = pack_bf16x2(f[4], f[5]); o.w = pack_bf16x2(f[6], f[7]);
-      *reinterpret_cast<uint4*>(p.out + static_cast<long>(row) * N + col) = o;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (!on[j]) continue;
+        float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+        for (int s2 = 0; s2 < MAX_PEERS; ++s2) {
+          if (s2 < c.world) {
+            const __nv_bfloat162* x = reinterpret_cast<const __nv_bfloat162*>(&u[j][s2]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float2 t = __bfloat1622float2(x[i]);
+              f[2 * i] += t.x;
+              f[2 * i + 1] += t.y;
+            }
+          }
+        }
+        uint4 o;
+        o.x = pack_bf16x2(f[0], f[1]); o.y = pack_bf16x2(f[2], f[3]);
+        o.z = pack_bf16x2(f[4], f[5]); o.w = pack_bf16x2(f[6], f[7]);
+        *reinterpret_cast<uint4*>(p.out + offs[j]) = o;
+      }
     }
     __syncthreads();
   }

@@ -11,12 +11,15 @@
 //   visit row tiles in arrival order (own shard first, then rank+1, rank+2, …) and the TMA producer
 //   waits for a tile's flag only if the tile is remote.  No tile crosses NVLink more than once, no
 //   TMA multicast is used, and the gathered activations stay in the buffer for the wgrad GEMM.
-// * gemm_rs — the GEMM CTAs visit row tiles in owner order (rank+1 first, own rows last); the
-//   epilogue stores each bf16 tile straight into the owner's staging slot through its peer pointer
-//   and bumps a per-tile counter there; extra reducer CTAs on the owner wait for the counters of a
-//   tile from all ranks, sum the partial tiles in fp32 and write the sequence shard.
+// * gemm_rs — the GEMM CTAs visit row tiles in owner order (rank+1 first, own rows last).  For a
+//   peer's rows the epilogue stores the bf16 partial tile straight into the owner's staging slot
+//   through its peer pointer (full 128-byte row segments) and bumps a per-tile counter there.  For
+//   its own rows the epilogue waits for the other ranks' counters of that tile, adds their staged
+//   partials in fp32 and writes the finished sequence shard: no separate reduction pass exists.
+//   One extra CTA runs the start barrier (peers must have entered the call before their staging is
+//   written).
 //
-// `n_comm` (copy drivers / reducer CTAs) is the plan's "SMs given to the collective" knob.  Every
+// `n_comm` (copy-driver CTAs of ag_gemm) is the plan's "SMs given to the collective" knob.  Every
 // wait is bounded (status word + return).  Role of the reference's separate cuBLASLt GEMM followed
 // or preceded by an all-reduce kernel (kareus/megatron/core/extensions/ops/te_linear.py:303-445,
 // 3rdparty/mscclpp/python/mscclpp_benchmark/allreduce.cu:155-246).
@@ -241,9 +244,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       // tell this rank's epilogues that every peer has entered the call (their staging is free)
       const bool ok = peer_barrier(c, 0, static_cast<uint64_t>(p.epoch) * 4 + 1, ok_slot);
       if (threadIdx.x == 0 && ok) st_release_gpu_u32(p.go, p.epoch);
-      if (!ok) return;
     }
-    rs_reduce_items(p, N, tiles_n, BN, ok_slot);
     return;
   }
 
@@ -357,15 +358,30 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       tc_fence_after();
       const uint32_t taddr = tmem_base + buf * BN + (static_cast<uint32_t>(q * 32) << 16);
       __nv_bfloat16* cbase;        // row 0 of this warp's 32 rows in the destination
+      bool own = false;            // reduce-scatter: tile of this rank's own rows
       if (p.mode == MODE_RS) {
         if (!go_seen) {
           if (!wait_u32_ge(p.go, p.epoch, false, status, ST_TIMEOUT_PEER, abort_flag)) { ok = false; break; }
           go_seen = true;
         }
         const int owner = tm / tiles_per_rank;
-        __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(c.base[owner] + p.stage_off) +
-                               static_cast<long>(c.rank) * p.rows_per_rank * N;
-        cbase = stage + static_cast<long>(m0 + q * 32 - owner * p.rows_per_rank) * N;
+        own = owner == c.rank;
+        if (!own) {
+          __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(c.base[owner] + p.stage_off) +
+                                 static_cast<long>(c.rank) * p.rows_per_rank * N;
+          cbase = stage + static_cast<long>(m0 + q * 32 - owner * p.rows_per_rank) * N;
+        } else {
+          // this rank's own rows come last in its tile order; by then the peers' partial tiles have
+          // (normally) landed in the staging slots here, so the sum is finished in this epilogue
+          cbase = p.out + static_cast<long>(m0 + q * 32 - owner * p.rows_per_rank) * N;
+          bool got = true;
+          if (lane < c.world && lane != c.rank) {
+            const uint32_t* cnt = reinterpret_cast<const uint32_t*>(c.base[c.rank] + p.cnt_off) +
+                                  (static_cast<long>(lane) * tiles_per_rank + (tm - owner * tiles_per_rank)) * tiles_n + tn;
+            got = wait_u32_ge(cnt, p.epoch * 4u, true, status, ST_TIMEOUT_PEER, abort_flag);
+          }
+          if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
+        }
       } else {
         cbase = p.out + static_cast<long>(m0 + q * 32) * N;
       }
@@ -398,9 +414,44 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 #pragma unroll
         for (int it4 = 0; it4 < 8; ++it4) {
           const int r = it4 * 4 + (lane >> 3);
-          const uint4 o = *reinterpret_cast<const uint4*>(stg + r * 128 + ((u ^ (r & 7)) << 4));
-          if (m0 + q * 32 + r < M && col + 8 <= N)
+          uint4 o = *reinterpret_cast<const uint4*>(stg + r * 128 + ((u ^ (r & 7)) << 4));
+          if (m0 + q * 32 + r < M && col + 8 <= N) {
+            if (own) {
+              // add the peers' partial sums of the same 8 elements (coalesced 128-byte row segments)
+              const long off = static_cast<long>(m0 + q * 32 + r - c.rank * p.rows_per_rank) * N + col;
+              const __nv_bfloat16* st0 = reinterpret_cast<const __nv_bfloat16*>(c.base[c.rank] + p.stage_off);
+              const long slot_elems = static_cast<long>(p.rows_per_rank) * N;
+              uint4 pv[MAX_PEERS];
+#pragma unroll
+              for (int s2 = 0; s2 < MAX_PEERS; ++s2)
+                if (s2 < c.world && s2 != c.rank) pv[s2] = *reinterpret_cast<const uint4*>(st0 + s2 * slot_elems + off);
+              float f[8];
+              {
+                const __nv_bfloat162* x = reinterpret_cast<const __nv_bfloat162*>(&o);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const float2 t2 = __bfloat1622float2(x[i]);
+                  f[2 * i] = t2.x;
+                  f[2 * i + 1] = t2.y;
+                }
+              }
+#pragma unroll
+              for (int s2 = 0; s2 < MAX_PEERS; ++s2) {
+                if (s2 < c.world && s2 != c.rank) {
+                  const __nv_bfloat162* x = reinterpret_cast<const __nv_bfloat162*>(&pv[s2]);
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) {
+                    const float2 t2 = __bfloat1622float2(x[i]);
+                    f[2 * i] += t2.x;
+                    f[2 * i + 1] += t2.y;
+                  }
+                }
+              }
+              o.x = pack_bf16x2(f[0], f[1]); o.y = pack_bf16x2(f[2], f[3]);
+              o.z = pack_bf16x2(f[4], f[5]); o.w = pack_bf16x2(f[6], f[7]);
+            }
             *reinterpret_cast<uint4*>(cbase + static_cast<long>(r) * N + col) = o;
+          }
         }
         __syncwarp();
       }
@@ -409,9 +460,9 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[buf]);
-      if (p.mode == MODE_RS) {
-        // publish this warp's 32 rows of the tile to the owner
-        __threadfence_system();
+      if (p.mode == MODE_RS && !own) {
+        // publish this warp's 32 rows of the tile to the owner: the lanes' stores are ordered before
+        // lane 0 by the warp barrier, and lane 0's system-scope release is cumulative over them
         __syncwarp();
         if (lane == 0) {
           const int owner = tm / tiles_per_rank;
@@ -429,11 +480,6 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
-  }
-  if (p.mode == MODE_RS && *abort_flag == 0) {
-    if (threadIdx.x == 0) *ok_slot = 1;
-    __syncthreads();
-    rs_reduce_items(p, N, tiles_n, BN, ok_slot);
   }
 }
 
@@ -527,9 +573,7 @@ extern "C" int kb_gemm_rs_bf16(void* const* bases, int rank, int world, uint64_t
   const bool narrow = (N <= 128) || (N % 256 != 0 && N % 256 <= 128);
   const int bn = narrow ? 128 : 256;
   const int tiles = (M / FG_BM) * ((N + bn - 1) / bn);
-  // the GEMM CTAs join the reduction when their tiles are done, so a few dedicated reducer CTAs (for
-  // the start barrier and the early tiles) are enough
-  if (n_comm > 4) n_comm = 4;
+  n_comm = 1;     // one CTA for the start barrier; the sums are finished in the GEMM epilogues
   p.n_last = n_comm;
   p.n_gemm = num_sms - n_comm < tiles ? num_sms - n_comm : tiles;   // reducers get SMs of their own
   if (narrow) return b_mn ? launch_fused<128, true>(A, W, p, M, N, K, lda, ldw, stream)

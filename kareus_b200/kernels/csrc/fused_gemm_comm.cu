@@ -26,6 +26,7 @@
 #include "sm100.cuh"
 #include "peer.cuh"
 #include "host_utils.h"
+#include <stdlib.h>
 
 namespace kb {
 
@@ -54,6 +55,7 @@ struct FusedParams {
   uint64_t cnt_off;       // counters [world][Ms/128][tiles_n] (uint32) in every heap
   uint32_t* go;           // local flag: peers have entered this call
   __nv_bfloat16* out;     // [Ms, N]
+  int debug;              // timing experiments only (KB_RS_DEBUG): 1 = keep peer tiles local, 2 = skip peer reads
 };
 
 template <int BN>
@@ -367,7 +369,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         const int owner = tm / tiles_per_rank;
         own = owner == c.rank;
         if (!own) {
-          __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(c.base[owner] + p.stage_off) +
+          __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(c.base[p.debug == 1 ? c.rank : owner] + p.stage_off) +
                                  static_cast<long>(c.rank) * p.rows_per_rank * N;
           cbase = stage + static_cast<long>(m0 + q * 32 - owner * p.rows_per_rank) * N;
         } else {
@@ -392,6 +394,43 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       uint8_t* stg = smem + S::TILE_BYTES + 256 + q * 4096;
 #pragma unroll 1
       for (int cp = 0; cp < BN / 64; ++cp) {
+        // own rows of a reduce-scatter: gather the peers' partial sums of this 32x64 block first, eight
+        // independent 16-byte loads per lane and peer in flight, so their latency hides behind the
+        // accumulator drain below
+        float pacc[8][8];
+        if (own && p.debug != 2) {
+#pragma unroll
+          for (int a = 0; a < 8; ++a)
+#pragma unroll
+            for (int b2 = 0; b2 < 8; ++b2) pacc[a][b2] = 0.f;
+          const int u = lane & 7;
+          const int col = n0 + cp * 64 + u * 8;
+          const __nv_bfloat16* st0 = reinterpret_cast<const __nv_bfloat16*>(c.base[c.rank] + p.stage_off);
+          const long slot_elems = static_cast<long>(p.rows_per_rank) * N;
+          const long off0 = static_cast<long>(m0 + q * 32 + (lane >> 3) - c.rank * p.rows_per_rank) * N + col;
+          const bool colok = col + 8 <= N;
+#pragma unroll 1
+          for (int s2 = 0; s2 < c.world; ++s2) {
+            if (s2 == c.rank) continue;
+            uint4 pv[8];
+#pragma unroll
+            for (int it4 = 0; it4 < 8; ++it4) {
+              const bool rok = colok && (m0 + q * 32 + it4 * 4 + (lane >> 3) < M);
+              pv[it4] = rok ? *reinterpret_cast<const uint4*>(st0 + s2 * slot_elems + off0 + static_cast<long>(it4 * 4) * N)
+                            : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int it4 = 0; it4 < 8; ++it4) {
+              const __nv_bfloat162* x = reinterpret_cast<const __nv_bfloat162*>(&pv[it4]);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const float2 t2 = __bfloat1622float2(x[i]);
+                pacc[it4][2 * i] += t2.x;
+                pacc[it4][2 * i + 1] += t2.y;
+              }
+            }
+          }
+        }
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
           uint32_t v[32];
@@ -416,36 +455,14 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           const int r = it4 * 4 + (lane >> 3);
           uint4 o = *reinterpret_cast<const uint4*>(stg + r * 128 + ((u ^ (r & 7)) << 4));
           if (m0 + q * 32 + r < M && col + 8 <= N) {
-            if (own) {
-              // add the peers' partial sums of the same 8 elements (coalesced 128-byte row segments)
-              const long off = static_cast<long>(m0 + q * 32 + r - c.rank * p.rows_per_rank) * N + col;
-              const __nv_bfloat16* st0 = reinterpret_cast<const __nv_bfloat16*>(c.base[c.rank] + p.stage_off);
-              const long slot_elems = static_cast<long>(p.rows_per_rank) * N;
-              uint4 pv[MAX_PEERS];
-#pragma unroll
-              for (int s2 = 0; s2 < MAX_PEERS; ++s2)
-                if (s2 < c.world && s2 != c.rank) pv[s2] = *reinterpret_cast<const uint4*>(st0 + s2 * slot_elems + off);
+            if (own && p.debug != 2) {
+              const __nv_bfloat162* x = reinterpret_cast<const __nv_bfloat162*>(&o);
               float f[8];
-              {
-                const __nv_bfloat162* x = reinterpret_cast<const __nv_bfloat162*>(&o);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  const float2 t2 = __bfloat1622float2(x[i]);
-                  f[2 * i] = t2.x;
-                  f[2 * i + 1] = t2.y;
-                }
-              }
-#pragma unroll
-              for (int s2 = 0; s2 < MAX_PEERS; ++s2) {
-                if (s2 < c.world && s2 != c.rank) {
-                  const __nv_bfloat162* x = reinterpret_cast<const __nv_bfloat162*>(&pv[s2]);
-#pragma unroll
-                  for (int i = 0; i < 4; ++i) {
-                    const float2 t2 = __bfloat1622float2(x[i]);
-                    f[2 * i] += t2.x;
-                    f[2 * i + 1] += t2.y;
-                  }
-                }
+              for (int i = 0; i < 4; ++i) {
+                const float2 t2 = __bfloat1622float2(x[i]);
+                f[2 * i] = t2.x + pacc[it4][2 * i];
+                f[2 * i + 1] = t2.y + pacc[it4][2 * i + 1];
               }
               o.x = pack_bf16x2(f[0], f[1]); o.y = pack_bf16x2(f[2], f[3]);
               o.z = pack_bf16x2(f[4], f[5]); o.w = pack_bf16x2(f[6], f[7]);
@@ -570,6 +587,7 @@ extern "C" int kb_gemm_rs_bf16(void* const* bases, int rank, int world, uint64_t
   p.cnt_off = cnt_off;
   p.go = go;
   p.out = reinterpret_cast<__nv_bfloat16*>(out);
+  { const char* e = getenv("KB_RS_DEBUG"); p.debug = e ? atoi(e) : 0; }
   const bool narrow = (N <= 128) || (N % 256 != 0 && N % 256 <= 128);
   const int bn = narrow ? 128 : 256;
   const int tiles = (M / FG_BM) * ((N + bn - 1) / bn);

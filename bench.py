@@ -28,7 +28,7 @@ BASELINE_TOKENS_PER_S = 60200.0   # planner-predicted max-throughput plan of the
 def _reference_arm(args) -> int:
     print(json.dumps({
         "impl": "reference",
-        "unavailable": "kareus installs from /root/reference only with --no-deps (pure Python); its training "
+        "unavailable": "the reference's kareus package installs only with --no-deps (pure Python); its training "
                        "path imports megatron.core, transformer_engine, nemo, apex, mscclpp, cupy and zeus, none "
                        "of which is in the image or the offline wheelhouse",
     }))

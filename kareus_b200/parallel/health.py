@@ -4,7 +4,8 @@ Every rank publishes the last step it *finished* in the rendezvous store; before
 step a rank checks that all peers finished the previous one within ``timeout_s``.  A rank that died
 or stalled is therefore noticed on the host, before any kernel or collective that would wait for it
 is launched (device-side waits are bounded as a second line of defence and report a status code).
-The reference has no such mechanism (its device spins trap the GPU on expiry).
+The reference has no such mechanism: its device-side spins assert (trap the GPU) when their limit
+is hit (``3rdparty/mscclpp/include/mscclpp/poll_device.hpp:12-18``).
 """
 from __future__ import annotations
 

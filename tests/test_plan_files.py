@@ -1,5 +1,6 @@
 """Plan-file contracts: config strings, both layouts, emit∘parse identity, scheduler checks, and a
 round trip over every plan file shipped with the reference (when that checkout is present)."""
+import os
 from pathlib import Path
 
 import pytest
@@ -8,7 +9,7 @@ from kareus_b200.plan import (CommConfig, PipelineCommScheduler, emit_freqs_text
                               parse_config_string, parse_freqs_text, parse_schedule_text, read_trailer,
                               sample_frontier, uniform_schedule)
 
-REF = Path("/root/reference/tests")
+REF = Path(os.environ.get("KAREUS_REFERENCE_DIR", "/nonexistent")) / "tests"
 
 SCHED = """
 [

@@ -55,7 +55,6 @@ struct FusedParams {
   uint64_t cnt_off;       // counters [world][Ms/128][tiles_n] (uint32) in every heap
   uint32_t* go;           // local flag: peers have entered this call
   __nv_bfloat16* out;     // [Ms, N]
-  int debug;              // timing experiments only (KB_RS_DEBUG): 1 = keep peer tiles local, 2 = skip peer reads
 };
 
 template <int BN>
@@ -131,71 +130,6 @@ __device__ void ag_copy_role(const FusedParams& p, int K, uint8_t* smem, uint64_
   // peers may still be reading this rank's shard: do not let the kernel (and the next writer of the
   // shard) get ahead of them
   peer_barrier(c, cta, static_cast<uint64_t>(p.epoch) * 4 + 2, ok_slot);
-}
-
-// ----------------------------------------------------------------------------- reducer (RS)
-// Work items are (row tile, column tile) pairs of this rank's shard, dealt round-robin to ALL CTAs of
-// the kernel: the dedicated reducer CTAs start on them at once, the GEMM CTAs join when their tiles
-// are done, so the tail of the reduction runs on the whole chip.
-__device__ void rs_reduce_items(const FusedParams& p, int N, int tiles_n, int BN, int* ok_slot) {
-  const PeerCtx& c = p.peer;
-  const int tiles_m = p.rows_per_rank / FG_BM;
-  const uint32_t want = p.epoch * 4u;                         // 4 epilogue warps per tile per call
-  const uint32_t* cnt = reinterpret_cast<const uint32_t*>(c.base[c.rank] + p.cnt_off);
-  const __nv_bfloat16* stage = reinterpret_cast<const __nv_bfloat16*>(c.base[c.rank] + p.stage_off);
-  const long slot_elems = static_cast<long>(p.rows_per_rank) * N;
-  for (int item = blockIdx.x; item < tiles_m * tiles_n; item += gridDim.x) {
-    const int tm = item % tiles_m, tn = item / tiles_m;
-    if (threadIdx.x < c.world) {
-      const uint32_t* q = cnt + (static_cast<long>(threadIdx.x) * tiles_m + tm) * tiles_n + tn;
-      if (!wait_u32_ge(q, want, true, c.status, ST_TIMEOUT_PEER)) *ok_slot = 0;
-    }
-    __syncthreads();
-    if (*ok_slot == 0) return;
-    const int cols = min(BN, N - tn * BN);
-    const int vec_per_row = cols >> 3;
-    const int nvec = FG_BM * vec_per_row;
-    // four independent vectors per thread and step: world x 4 loads are in flight before the first
-    // add, which is what lets 192 threads per SM pull HBM bandwidth
-    for (int v0 = threadIdx.x; v0 < nvec; v0 += 4 * blockDim.x) {
-      uint4 u[4][MAX_PEERS];
-      long offs[4];
-      bool on[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int v = v0 + j * blockDim.x;
-        on[j] = v < nvec;
-        const int row = tm * FG_BM + (on[j] ? v / vec_per_row : 0);
-        const int col = tn * BN + (on[j] ? (v % vec_per_row) * 8 : 0);
-        offs[j] = static_cast<long>(row) * N + col;
-#pragma unroll
-        for (int s2 = 0; s2 < MAX_PEERS; ++s2)
-          if (s2 < c.world && on[j]) u[j][s2] = *reinterpret_cast<const uint4*>(stage + s2 * slot_elems + offs[j]);
-      }
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        if (!on[j]) continue;
-        float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#pragma unroll
-        for (int s2 = 0; s2 < MAX_PEERS; ++s2) {
-          if (s2 < c.world) {
-            const __nv_bfloat162* x = reinterpret_cast<const __nv_bfloat162*>(&u[j][s2]);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float2 t = __bfloat1622float2(x[i]);
-              f[2 * i] += t.x;
-              f[2 * i + 1] += t.y;
-            }
-          }
-        }
-        uint4 o;
-        o.x = pack_bf16x2(f[0], f[1]); o.y = pack_bf16x2(f[2], f[3]);
-        o.z = pack_bf16x2(f[4], f[5]); o.w = pack_bf16x2(f[6], f[7]);
-        *reinterpret_cast<uint4*>(p.out + offs[j]) = o;
-      }
-    }
-    __syncthreads();
-  }
 }
 
 // ----------------------------------------------------------------------------- kernel
@@ -369,7 +303,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         const int owner = tm / tiles_per_rank;
         own = owner == c.rank;
         if (!own) {
-          __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(c.base[p.debug == 1 ? c.rank : owner] + p.stage_off) +
+          __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(c.base[owner] + p.stage_off) +
                                  static_cast<long>(c.rank) * p.rows_per_rank * N;
           cbase = stage + static_cast<long>(m0 + q * 32 - owner * p.rows_per_rank) * N;
         } else {
@@ -398,7 +332,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         // independent 16-byte loads per lane and peer in flight, so their latency hides behind the
         // accumulator drain below
         float pacc[8][8];
-        if (own && p.debug != 2) {
+        if (own) {
 #pragma unroll
           for (int a = 0; a < 8; ++a)
 #pragma unroll
@@ -455,7 +389,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           const int r = it4 * 4 + (lane >> 3);
           uint4 o = *reinterpret_cast<const uint4*>(stg + r * 128 + ((u ^ (r & 7)) << 4));
           if (m0 + q * 32 + r < M && col + 8 <= N) {
-            if (own && p.debug != 2) {
+            if (own) {
               const __nv_bfloat162* x = reinterpret_cast<const __nv_bfloat162*>(&o);
               float f[8];
 #pragma unroll
@@ -587,7 +521,6 @@ extern "C" int kb_gemm_rs_bf16(void* const* bases, int rank, int world, uint64_t
   p.cnt_off = cnt_off;
   p.go = go;
   p.out = reinterpret_cast<__nv_bfloat16*>(out);
-  { const char* e = getenv("KB_RS_DEBUG"); p.debug = e ? atoi(e) : 0; }
   const bool narrow = (N <= 128) || (N % 256 != 0 && N % 256 <= 128);
   const int bn = narrow ? 128 : 256;
   const int tiles = (M / FG_BM) * ((N + bn - 1) / bn);

@@ -64,8 +64,9 @@ def main(argv=None) -> int:
         from ..parallel.symm_heap import SymmetricHeap
         heap = SymmetricHeap.create(mesh.group("tp"), device)
     base = run_dir(a.out, a.model_name, cp, tp, a.batch_size, a.seq_len)
-    monitor = EnergyMonitor([local] if cuda else [0])
-    ctl = FrequencyController(local, a.clock_mode)
+    from ..energy.nvml import FakeNVML
+    monitor = EnergyMonitor([local] if cuda else [0], nvml=None if cuda else FakeNVML(1))
+    ctl = FrequencyController(local if cuda else 0, a.clock_mode, nvml=monitor.nvml)
     freqs = list(a.freqs) if a.freqs else get_freq_grid(a.gpu_type)
 
     if a.nonpartition:

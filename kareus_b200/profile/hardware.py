@@ -34,7 +34,10 @@ class HardwareEvaluator:
 
     def _executor(self, nano: int):
         if nano not in self._executors:
-            self._executors[nano] = self.make_executor(nano)
+            ex = self.make_executor(nano)
+            for _ in range(3):          # first calls pay for lazy initialisation (buffers, function attributes)
+                ex.execute(("first", "none"), (16, 1024))
+            self._executors[nano] = ex
         return self._executors[nano]
 
     def __call__(self, configs: Sequence[Config]) -> List[Tuple[float, float]]:

@@ -40,6 +40,8 @@ def main(argv=None) -> int:
     ap.add_argument("--enable-power-monitor", action="store_true")
     ap.add_argument("--enable-timers", action="store_true")
     ap.add_argument("--recompute-layers", type=int, default=4)
+    ap.add_argument("--keep-process-group", action="store_true",
+                    help="leave torch.distributed initialised (when called from another driver)")
     a = ap.parse_args(argv)
 
     import torch.distributed as dist
@@ -111,7 +113,8 @@ def main(argv=None) -> int:
             timers.export(out, rank, local)
         if world > 1:
             dist.barrier()
-            dist.destroy_process_group()
+            if not a.keep_process_group:
+                dist.destroy_process_group()
     return 0
 
 

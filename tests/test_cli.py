@@ -47,3 +47,35 @@ def test_perseus_profile_and_frequency_only_plan(tmp_path, capsys):
                                use_native=False, max_iterations=5)
     assert (tmp_path / "plans" / "freqs_pipeline_00000.py").exists() or summary == []
     assert not list((tmp_path / "plans").glob("scheds_pipeline_*.py"))
+
+
+def test_run_kareus_end_to_end_cpu(tmp_path, capsys):
+    """Synthetic partition profiles → compose → plan → train under the max-throughput plan."""
+    import json
+    import random
+    from kareus_b200.cli import run_kareus
+    rng = random.Random(0)
+    freqs = [1500, 1200, 900]
+    base = tmp_path / "bo" / "logs" / "tiny" / "cp1-tp1-bs2-seq32"
+    for part, (t, e) in {"fwd_attn": (2e-3, 1.0), "fwd_mlp": (3e-3, 1.5), "bwd_attn": (4e-3, 2.0), "bwd_mlp": (6e-3, 3.0)}.items():
+        (base / part).mkdir(parents=True)
+        with (base / part / "eval_results.jsonl").open("w") as f:
+            for fr in freqs:
+                for sm in (6, 12):
+                    tt = t * 1500 / fr * (1 + 0.05 * (sm == 6) + 0.01 * rng.random())
+                    f.write(json.dumps({"freq": fr, "overlap_start": "norm_0", "overlap_end": "none", "sm": sm,
+                                        "block": 1024, "time_s": tt, "energy_j": e * (fr / 1500) ** 2 + 190 * tt}) + "\n")
+    for fr in freqs:
+        d = base / "nonpartition" / str(fr)
+        d.mkdir(parents=True)
+        for fname in ("preprocess_energy.csv", "postprocess_energy.csv", "loss_energy.csv",
+                      "preprocess_backward_energy.csv", "postprocess_backward_energy.csv"):
+            (d / fname).write_text(f"time (s),total_energy (J),per_rank_energy (J)\n{1e-3 * 1500 / fr},0.5,0.5\n")
+    rc = run_kareus.main(["--model", "tiny", "--mbs", "2", "--gbs", "4", "--seq", "32", "--steps", "2",
+                          "--bayesian-dir", str(tmp_path / "bo"), "--workdir", str(tmp_path / "exp"),
+                          "--max-iterations", "12", "--comm-backend", "nccl"])
+    assert rc == 0
+    out = capsys.readouterr().out
+    assert "planned 12 frontier points" in out and "step 1 loss" in out
+    plans = tmp_path / "exp" / "tiny" / "cp1_tp1_mbs2_seq32" / "kareus" / "lowtime"
+    assert (plans / "freqs_pipeline_00011.py").exists() and (plans / "scheds_pipeline_00011.py").exists()

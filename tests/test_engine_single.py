@@ -113,3 +113,31 @@ def test_gelu_and_geglu_ops_match_autograd():
         want.backward(g)
         (dx,) = op.backward(ctx, g)
         torch.testing.assert_close(dx, x.grad, rtol=1e-8, atol=1e-9)
+
+
+def test_layernorm_and_bias_ops_match_autograd():
+    from kareus_b200.engine.context import OpContext
+    from kareus_b200.ops.extras import BiasOp, LayerNormOp, make_norm
+    x = torch.randn(6, 3, 32, dtype=torch.float64, requires_grad=True)
+    ln = make_norm("LayerNorm", 32, 1e-5, "ln", dtype=torch.float64)
+    with torch.no_grad():
+        ln.weight.mul_(1.3)
+        ln.bias.add_(0.2)
+    ctx = OpContext()
+    (y,) = ln.forward(ctx, x.detach())
+    want = torch.nn.functional.layer_norm(x, (32,), ln.weight.detach(), ln.bias.detach(), 1e-5)
+    torch.testing.assert_close(y, want.detach(), rtol=1e-9, atol=1e-10)
+    g = torch.randn_like(want)
+    w_ref = ln.weight.detach().clone().requires_grad_(True)
+    b_ref = ln.bias.detach().clone().requires_grad_(True)
+    torch.nn.functional.layer_norm(x, (32,), w_ref, b_ref, 1e-5).backward(g)
+    (dx,) = ln.backward(ctx, g)
+    torch.testing.assert_close(dx, x.grad, rtol=1e-8, atol=1e-9)
+    torch.testing.assert_close(ln.weight.main_grad, w_ref.grad, rtol=1e-8, atol=1e-9)
+    torch.testing.assert_close(ln.bias.main_grad, b_ref.grad, rtol=1e-8, atol=1e-9)
+    b = BiasOp(32, dtype=torch.float64)
+    (z,) = b.forward(OpContext(), x.detach())
+    torch.testing.assert_close(z, x.detach() + b.bias.detach())
+    b.backward(OpContext(), g)
+    torch.testing.assert_close(b.bias.main_grad, g.reshape(-1, 32).sum(0))
+    assert type(make_norm("RMSNorm", 32, 1e-5, "n")).__name__ == "RMSNormOp"

@@ -262,3 +262,30 @@ def test_gelu_geglu_kernels():
         (dx,) = op.backward(ctx, g)
         (dxr,) = op.backward(ctx2, g.float())
         assert _rel(dx, dxr) < 5e-3
+
+
+def test_layernorm_and_bias_kernels():
+    from kareus_b200.engine.context import OpContext
+    from kareus_b200.ops.extras import BiasOp, LayerNormOp
+    for rows, H in ((300, 1024), (64, 3072)):
+        x = torch.randn(rows, H, device="cuda").bfloat16()
+        g = torch.randn(rows, H, device="cuda").bfloat16()
+        ln = LayerNormOp(H, dtype=torch.bfloat16, device="cuda")
+        ref = LayerNormOp(H, dtype=torch.float32, device="cuda")
+        with torch.no_grad():
+            ln.weight.mul_(1.25); ln.bias.add_(0.5); ref.weight.mul_(1.25); ref.bias.add_(0.5)
+        c1, c2 = OpContext(), OpContext()
+        (y,) = ln.forward(c1, x)
+        (yr,) = ref.forward(c2, x.float())
+        assert _rel(y, yr) < 5e-3
+        (dx,) = ln.backward(c1, g)
+        (dxr,) = ref.backward(c2, g.float())
+        assert _rel(dx, dxr) < 1e-2
+        assert _rel(ln.weight.main_grad, ref.weight.main_grad) < 1e-2 and _rel(ln.bias.main_grad, ref.bias.main_grad) < 1e-2
+        b = BiasOp(H, dtype=torch.bfloat16, device="cuda")
+        with torch.no_grad():
+            b.bias.add_(0.75)
+        (z,) = b.forward(OpContext(), x)
+        assert _rel(z, x.float() + 0.75) < 5e-3
+        b.backward(OpContext(), g)
+        assert _rel(b.bias.main_grad, g.float().sum(0)) < 1e-2

@@ -195,7 +195,6 @@ class FusedAGDgrad(_FusedBase):
         lead = dy.shape[:-1]
         dx, dyg = self._ag_gemm(dy.reshape(-1, dy.shape[-1]), lin.weight, lin.in_features, True, sm_num, nb)
         _wgrad(dyg, a2, lin.weight)
-        dx.record_stream(torch.cuda.current_stream(dx.device))
         ctx.clear()
         return (dx.reshape((lead[0] * self.heap.world,) + tuple(lead[1:]) + (lin.in_features,)),)
 

@@ -5,11 +5,12 @@ schedules.py:1775-2085``): ``min(pp - rank - 1, M)`` warm-up forwards, ``M - war
 forward/backward pairs, then the cool-down backwards.  That order is also the order of the
 entries of a stage in ``freqs_pipeline_*.py`` / ``scheds_pipeline_*.py``.
 
-Transfers are asynchronous: a receive for the next activation (or gradient) is posted before the
-current instruction's compute is enqueued and waited for only when its data is needed; sends are
-completed at the end of the step.  On GPUs this is NCCL ``batch_isend_irecv`` running under the
-compute (the reference only removes a ``cuda.synchronize`` after its blocking p2p calls:
-``p2p_communication.py:401-412``).  The message is the list of nanobatch tensors of one
+Transfers are batched like Megatron's (a send and the matching receive of the opposite direction go
+into one ``batch_isend_irecv``, which keeps neighbouring stages' pairs matched and the schedule
+deadlock free) but never block the host: waiting on a receive only orders the compute stream after
+the NCCL stream, sends are completed at the end of the step, so the transfers run under the compute
+that is already enqueued (the reference only removes a ``cuda.synchronize`` after its blocking p2p
+calls: ``p2p_communication.py:401-412``).  The message is the list of nanobatch tensors of one
 microbatch, ``[s/cp(/tp), mbs/N, h]`` each.
 """
 from __future__ import annotations

@@ -195,6 +195,12 @@ class FusedAGDgrad(_FusedBase):
         lead = dy.shape[:-1]
         dx, dyg = self._ag_gemm(dy.reshape(-1, dy.shape[-1]), lin.weight, lin.in_features, True, sm_num, nb)
         _wgrad(dyg, a2, lin.weight)
+        if dyg.is_cuda:
+            # `dyg` lives in this call site's heap buffer, which the site's next call overwrites: when
+            # the weight-gradient GEMM was moved to the ordered stream, this stream must not run ahead
+            from ..engine.program import _per_nb_streams, _shared_comm_stream
+            if _per_nb_streams():
+                torch.cuda.current_stream(dyg.device).wait_stream(_shared_comm_stream(dyg.device, slot=0))
         ctx.clear()
         return (dx.reshape((lead[0] * self.heap.world,) + tuple(lead[1:]) + (lin.in_features,)),)
 

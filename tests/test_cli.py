@@ -79,3 +79,28 @@ def test_run_kareus_end_to_end_cpu(tmp_path, capsys):
     assert "planned 12 frontier points" in out and "step 1 loss" in out
     plans = tmp_path / "exp" / "tiny" / "cp1_tp1_mbs2_seq32" / "kareus" / "lowtime"
     assert (plans / "freqs_pipeline_00011.py").exists() and (plans / "scheds_pipeline_00011.py").exists()
+
+
+def test_pretrain_from_yaml(tmp_path, capsys):
+    from kareus_b200.cli import pretrain
+    (tmp_path / "c.yaml").write_text("""
+name: tiny_yaml
+trainer: {devices: 1, num_nodes: 1, precision: 32, max_steps: 2}
+model:
+  micro_batch_size: 2
+  global_batch_size: 4
+  tensor_model_parallel_size: 1
+  pipeline_model_parallel_size: 1
+  encoder_seq_length: 32
+  num_layers: 2
+  hidden_size: 64
+  ffn_hidden_size: 128
+  num_attention_heads: 4
+  num_query_groups: 2
+  vocab_size: 256
+  activations_checkpoint_granularity: full
+  enable_megatron_timers: true
+""")
+    rc = pretrain.main(["--config", str(tmp_path / "c.yaml"), "--out", str(tmp_path / "exp"), "model.hidden_dropout=0.0"])
+    assert rc == 0 and "step 1 loss" in capsys.readouterr().out
+    assert (tmp_path / "exp" / "tiny_yaml" / "cp1_tp1_mbs2_seq32" / "nanobatch" / "timers" / "instructions-0-0.csv").exists()

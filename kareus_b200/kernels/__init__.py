@@ -3,9 +3,16 @@
 Every function takes torch tensors.  CUDA tensors go to the hand-written sm_100a kernels in
 ``libkareus_b200.so`` (built from ``kernels/csrc`` and loaded through :mod:`.cuda`); CPU tensors
 go to the PyTorch statements in :mod:`.ref`.  There is no silent fallback on a GPU: if the
-library is missing the call raises.  ``KAREUS_B200_LIBRARY_BASELINE=1`` switches GEMM and attention
-to the vendor libraries (cuBLAS through ``torch.matmul``, the flash-attention wheel or SDPA); that
-is the A/B baseline configured like the reference, never the default.
+library is missing the call raises, and bf16 attention shapes the hand-written kernels do not
+cover (head dim other than 128, rows that are not 16-byte aligned) raise too unless
+``KAREUS_B200_ATTENTION_FALLBACK=1`` opts into the flash-attention wheel, which is logged once.
+``KAREUS_B200_LIBRARY_BASELINE=1`` switches GEMM and attention to the vendor libraries (cuBLAS
+through ``torch.matmul``, the flash-attention wheel); that is the A/B baseline configured like the
+reference, never the default.
+
+Operands that live in another GPU's memory (peer views of the symmetric heap) must be announced
+with ``peer=True``; such calls run this package's own kernels or raise, whatever the switches say:
+a vendor-library kernel never receives a peer's memory.
 """
 from __future__ import annotations
 
@@ -111,7 +118,21 @@ def gemm(a, b, trans_a=False, trans_b=True, out_dtype=None, accumulate=None, out
 
 
 # ----------------------------------------------------------------------------- attention
-def attention_fwd(q, k, v, scale, causal=True, q_offset=0, kv_len=None):
+def _peer_guard(q, what: str) -> None:
+    """A call that announces peer-memory operands may only reach this package's own kernels."""
+    from .cuda import KernelError
+    if not is_cuda(q):
+        raise KernelError(f"{what}: peer-memory operands need CUDA tensors")
+    if library_baseline():
+        raise KernelError(f"{what}: KAREUS_B200_LIBRARY_BASELINE=1 would hand another GPU's memory to a "
+                          "vendor-library kernel; refused")
+
+
+def attention_fwd(q, k, v, scale, causal=True, q_offset=0, kv_len=None, peer=False):
+    """``peer=True``: ``k``/``v`` may be views of another GPU's memory; only the native kernel may run."""
+    if peer:
+        _peer_guard(q, "attention_fwd")
+        return _cuda().attention_fwd(q, k, v, scale, causal, q_offset, kv_len, strict=True)
     if is_cuda(q):
         if library_baseline():
             return _cuda().attention_fwd_library(q, k, v, scale, causal, q_offset, kv_len)
@@ -119,8 +140,12 @@ def attention_fwd(q, k, v, scale, causal=True, q_offset=0, kv_len=None):
     return ref.attention_fwd(q, k, v, scale, causal, q_offset, kv_len)
 
 
-def attention_bwd(do, q, k, v, o, lse, scale, causal=True, q_offset=0, kv_len=None, out=None):
-    """Returns ``(dq, dk, dv)``; ``out`` may provide preallocated (strided) destinations."""
+def attention_bwd(do, q, k, v, o, lse, scale, causal=True, q_offset=0, kv_len=None, out=None, peer=False):
+    """Returns ``(dq, dk, dv)``; ``out`` may provide preallocated (strided) destinations.
+    ``peer=True`` as in :func:`attention_fwd`."""
+    if peer:
+        _peer_guard(q, "attention_bwd")
+        return _cuda().attention_bwd(do, q, k, v, o, lse, scale, causal, q_offset, kv_len, out, strict=True)
     if is_cuda(q):
         if library_baseline():
             return _cuda().attention_bwd_library(do, q, k, v, o, lse, scale, causal, q_offset, kv_len, out)

@@ -39,10 +39,13 @@ def _ok(t):
     return t.stride(-1) == 1 and t.data_ptr() % 16 == 0 and all(st % 8 == 0 for st in t.stride()[:-1])
 
 
-def backward(do, q, k, v, o, lse, scale, causal=True, q_offset=0, kv_len=None, out=None):
+def backward(do, q, k, v, o, lse, scale, causal=True, q_offset=0, kv_len=None, out=None, strict=False):
     kg = k.shape[2]
     sq, b, g, rep, d, qs = _geom5(q, kg)
-    if d != 128 or not (_ok(q) and _ok(k) and _ok(v)):
+    from .attention_native import unsupported_reason
+    why = unsupported_reason(d, g, kg, q, k, v)
+    if why is not None:
+        KC.attention_fallback_allowed(why, strict)
         return KC.attention_bwd_library(do, q, k, v, o, lse, scale, causal, q_offset, kv_len, out)
     skv = k.shape[0] if kv_len is None else int(kv_len)
     hq = g * rep

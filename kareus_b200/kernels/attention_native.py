@@ -44,7 +44,18 @@ def _usable(t) -> bool:
     return t.stride(-1) == 1 and t.data_ptr() % 16 == 0 and all(st % 8 == 0 for st in t.stride()[:-1])
 
 
-def forward(q, k, v, scale, causal=True, q_offset=0, kv_len=None):
+def unsupported_reason(d, g, kg, *tensors):
+    """Why the native kernels cannot take a call, or ``None``."""
+    if d != 128:
+        return f"head dim {d} (the kernels are specialised for 128)"
+    if g != kg:
+        return f"query groups {g} do not match key groups {kg}"
+    if not all(_usable(t) for t in tensors):
+        return "an operand's head dim is not contiguous or a stride/base is not 16-byte aligned"
+    return None
+
+
+def forward(q, k, v, scale, causal=True, q_offset=0, kv_len=None, strict=False):
     sq, b, g, rep, d, qs = _q_geometry(q)
     kg = k.shape[2]
     if q.dim() == 4:
@@ -52,7 +63,9 @@ def forward(q, k, v, scale, causal=True, q_offset=0, kv_len=None):
         rep = q.shape[2] // kg
         g = kg
         qs = (q.stride(0), q.stride(1), q.stride(2) * rep, q.stride(2))
-    if d != 128 or not (_usable(q) and _usable(k) and _usable(v)) or g != kg:
+    why = unsupported_reason(d, g, kg, q, k, v)
+    if why is not None:
+        KC.attention_fallback_allowed(why, strict)
         return KC.attention_fwd_library(q, k, v, scale, causal, q_offset, kv_len)
     skv = k.shape[0] if kv_len is None else int(kv_len)
     out = torch.empty(sq, b, g * rep, d, dtype=q.dtype, device=q.device)
@@ -67,6 +80,6 @@ def forward(q, k, v, scale, causal=True, q_offset=0, kv_len=None):
     return out, lse
 
 
-def backward(do, q, k, v, o, lse, scale, causal=True, q_offset=0, kv_len=None, out=None):
+def backward(do, q, k, v, o, lse, scale, causal=True, q_offset=0, kv_len=None, out=None, strict=False):
     from . import attention_bwd_native
-    return attention_bwd_native.backward(do, q, k, v, o, lse, scale, causal, q_offset, kv_len, out)
+    return attention_bwd_native.backward(do, q, k, v, o, lse, scale, causal, q_offset, kv_len, out, strict=strict)

@@ -386,15 +386,39 @@ def attention_bwd_library(do, q, k, v, o, lse, scale, causal=True, q_offset=0, k
     return dq.reshape(q.shape), dk, dv
 
 
-def attention_fwd(q, k, v, scale, causal=True, q_offset=0, kv_len=None):
+_FALLBACK_LOGGED = [False]
+
+
+def attention_fallback_allowed(reason: str, strict: bool) -> None:
+    """Gate of the only route from the native attention entry points to the flash-attention wheel.
+
+    ``strict`` calls (operands may be peer memory) never pass.  Other calls pass only with
+    ``KAREUS_B200_ATTENTION_FALLBACK=1`` and say so once on stderr."""
+    if strict:
+        raise KernelError(f"native attention kernel cannot take this call ({reason}) and the operands may be "
+                          "another GPU's memory: no library or PyTorch route is allowed")
+    if os.environ.get("KAREUS_B200_ATTENTION_FALLBACK", "0") != "1":
+        raise KernelError(f"native attention kernel cannot take this call ({reason}); set "
+                          "KAREUS_B200_ATTENTION_FALLBACK=1 to run such shapes on the flash-attention wheel")
+    if not _FALLBACK_LOGGED[0]:
+        import sys
+        print(f"kareus_b200: attention falls back to the flash-attention wheel ({reason})", file=sys.stderr)
+        _FALLBACK_LOGGED[0] = True
+
+
+def attention_fwd(q, k, v, scale, causal=True, q_offset=0, kv_len=None, strict=False):
     if not _bf16(q):
+        if strict:
+            raise KernelError(f"attention on peer-memory operands needs bf16, got {q.dtype}")
         return ref.attention_fwd(q, k, v, scale, causal, q_offset, kv_len)
     from . import attention_cuda
-    return attention_cuda.forward(q, k, v, scale, causal, q_offset, kv_len)
+    return attention_cuda.forward(q, k, v, scale, causal, q_offset, kv_len, strict=strict)
 
 
-def attention_bwd(do, q, k, v, o, lse, scale, causal=True, q_offset=0, kv_len=None, out=None):
+def attention_bwd(do, q, k, v, o, lse, scale, causal=True, q_offset=0, kv_len=None, out=None, strict=False):
     if not _bf16(q):
+        if strict:
+            raise KernelError(f"attention on peer-memory operands needs bf16, got {q.dtype}")
         dq, dk, dv = ref.attention_bwd(do, q, k, v, o, lse, scale, causal, q_offset, kv_len)
         if out is not None:
             out[0].copy_(dq.reshape(out[0].shape))
@@ -403,7 +427,7 @@ def attention_bwd(do, q, k, v, o, lse, scale, causal=True, q_offset=0, kv_len=No
             return out
         return dq, dk, dv
     from . import attention_cuda
-    return attention_cuda.backward(do, q, k, v, o, lse, scale, causal, q_offset, kv_len, out)
+    return attention_cuda.backward(do, q, k, v, o, lse, scale, causal, q_offset, kv_len, out, strict=strict)
 
 
 # ----------------------------------------------------------------------------- cross entropy

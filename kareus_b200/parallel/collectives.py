@@ -29,6 +29,11 @@ class CollectiveBase:
         self.world = int(world)
         self.rank = int(rank)
         self.backend = backend
+        if heap is not None and (int(heap.world) != int(world) or int(heap.rank) != int(rank)):
+            # a heap maps the memory of ONE process group; running this collective over it would sum
+            # or gather across the wrong set of ranks
+            raise ValueError(f"{name or type(self).__name__}: symmetric heap spans {heap.world} ranks (rank "
+                             f"{heap.rank}) but the collective's group has {world} (rank {rank})")
         self.heap = heap
         self.name = name or type(self).__name__
         # heap buffers are shared by the same call site of every layer (layers run one after another
@@ -47,8 +52,11 @@ class CollectiveBase:
     staging_kind: Optional[str] = None
 
     def _use_kernel(self, t, sm_num) -> bool:
+        # the heap kernels sum and move bf16 only; every other dtype (fp32/fp64 numerics runs) takes
+        # the torch.distributed path
         return (self.backend == "kernel" and self.heap is not None and sm_num is not None
-                and isinstance(t, torch.Tensor) and t.is_cuda and self.world > 1)
+                and isinstance(t, torch.Tensor) and t.is_cuda and self.world > 1
+                and t.dtype == torch.bfloat16)
 
 
 class AllReduce(CollectiveBase):
@@ -195,10 +203,15 @@ class ReduceScatterKV(CollectiveBase):
 class CommFactory:
     """Creates the collective operators of one model for a mesh/backend pair."""
 
-    def __init__(self, mesh=None, backend: str = "nccl", heap=None):
+    def __init__(self, mesh=None, backend: str = "nccl", heap=None, heap_cp=None):
         self.mesh = mesh
         self.backend = backend
-        self.heap = heap
+        self.heap = heap              # symmetric heap of the tensor-parallel group
+        self.heap_cp = heap_cp        # symmetric heap of the context-parallel group
+
+    def heap_for(self, axis: str):
+        """The heap that maps the memory of ``axis``'s group, or ``None`` (library collectives)."""
+        return {"tp": self.heap, "cp": self.heap_cp}.get(axis)
 
     def _args(self, axis: str):
         if self.mesh is None:
@@ -207,4 +220,4 @@ class CommFactory:
 
     def make(self, cls, axis: str, name: str):
         g, w, r = self._args(axis)
-        return cls(g, w, r, backend=self.backend, heap=self.heap, name=name)
+        return cls(g, w, r, backend=self.backend, heap=self.heap_for(axis), name=name)

@@ -25,6 +25,7 @@ import torch.distributed as dist
 
 from .. import kernels as K
 from ..kernels import ref
+from ..kernels.cuda import KernelError
 from .collectives import ReduceScatterKV, dual_chunk_ids
 
 
@@ -44,6 +45,12 @@ class RingAttention:
     def _publish(self, k, v, nb: int, tag: str) -> List[Tuple[torch.Tensor, torch.Tensor]]:
         """Returns ``[(K_r, V_r) for r in ranks]`` — peer-memory views on GPUs, gathered copies on CPU."""
         if self.heap is not None and k.is_cuda:
+            if K.library_baseline():
+                raise KernelError("ring attention over the symmetric heap is refused with "
+                                  "KAREUS_B200_LIBRARY_BASELINE=1: the library attention kernels would receive "
+                                  "peer memory; use cp_comm='all_gather' for the library baseline")
+            if k.dtype != torch.bfloat16:
+                raise KernelError(f"ring attention over the symmetric heap needs bf16 K/V, got {k.dtype}")
             heap = self.heap
             ch = heap.channel(f"{self.name}/{tag}/{nb}")
             n = k.numel() * k.element_size()
@@ -60,6 +67,11 @@ class RingAttention:
         dist.all_gather(vs, v.contiguous(), group=self.group)
         return list(zip(ks, vs))
 
+    def _peer(self, k) -> bool:
+        """True when ``_publish`` hands out views of other GPUs' memory: every attention call must then
+        be announced as such (``peer=True``), which pins it to this package's own kernels."""
+        return self.heap is not None and k.is_cuda
+
     def _kv_chunk(self, kv, j: int, c: int):
         r, half = chunk_owner(j, self.cp)
         return kv[r][0][half * c:(half + 1) * c], kv[r][1][half * c:(half + 1) * c]
@@ -69,13 +81,14 @@ class RingAttention:
         s = q.shape[0]
         c = s // 2
         kv = self._publish(k, v, nb, "fwd")
+        peer = self._peer(k)
         outs, lses = [], []
         for half, cid in enumerate(dual_chunk_ids(self.cp, self.rank)):
             qc = q[half * c:(half + 1) * c]
             o = lse = None
             for j in range(cid + 1):
                 kj, vj = self._kv_chunk(kv, j, c)
-                oj, lj = K.attention_fwd(qc, kj, vj, scale, causal=(j == cid))
+                oj, lj = K.attention_fwd(qc, kj, vj, scale, causal=(j == cid), peer=peer)
                 if o is None:
                     o, lse = oj, lj
                 else:
@@ -88,6 +101,7 @@ class RingAttention:
         s = q.shape[0]
         c = s // 2
         kv = self._publish(k, v, nb, "bwd")
+        peer = self._peer(k)
         acc = torch.float64 if q.dtype == torch.float64 else torch.float32
         dk_full = torch.zeros((2 * self.cp * c,) + tuple(k.shape[1:]), dtype=acc, device=k.device)
         dv_full = torch.zeros_like(dk_full)
@@ -97,7 +111,8 @@ class RingAttention:
             dq = None
             for j in range(cid + 1):
                 kj, vj = self._kv_chunk(kv, j, c)
-                dqj, dkj, dvj = K.attention_bwd(do[sl], q[sl], kj, vj, out[sl], lse[half], scale, causal=(j == cid))
+                dqj, dkj, dvj = K.attention_bwd(do[sl], q[sl], kj, vj, out[sl], lse[half], scale, causal=(j == cid),
+                                                peer=peer)
                 dq = dqj.to(acc) if dq is None else dq + dqj.to(acc)
                 dk_full[j * c:(j + 1) * c] += dkj.to(acc)
                 dv_full[j * c:(j + 1) * c] += dvj.to(acc)

@@ -132,8 +132,14 @@ class SymmetricHeap:
         return cur[0], self.local[cur[0]:cur[0] + nbytes]
 
     def peer_view(self, rank: int, off: int, shape, dtype) -> torch.Tensor:
-        """The same buffer in rank ``rank``'s heap, addressed through the peer mapping.  Kernels of this
-        package may read it (plain or TMA loads without multicast); never hand it to a library kernel."""
+        """The same buffer in rank ``rank``'s heap, addressed through the peer mapping.  Only kernels of
+        this package may read it (plain or TMA loads without multicast), through entry points called
+        with ``peer=True``; those refuse every library or PyTorch route.  With the library baseline
+        switched on no peer view is handed out at all."""
+        from ..kernels import library_baseline
+        if library_baseline():
+            raise KC.KernelError("peer views are not available with KAREUS_B200_LIBRARY_BASELINE=1: a vendor-library "
+                                 "kernel must never receive another GPU's memory as an operand")
         if rank == self.rank:
             return self.view(off, shape, dtype)
         n = 1
@@ -172,10 +178,18 @@ class SymmetricHeap:
     def _launch_shape(self, sm_num, block_size):
         return int(sm_num or 16), int(block_size or 1024)
 
+    @staticmethod
+    def _require_bf16(x: torch.Tensor, what: str) -> None:
+        """The all-pairs kernels add and move bf16 elements; any other dtype would be reinterpreted."""
+        if x.dtype != torch.bfloat16:
+            raise KC.KernelError(f"symmetric-heap {what} supports bf16 only, got {x.dtype}; use the "
+                                 "torch.distributed backend for other dtypes")
+
     def all_reduce(self, x: torch.Tensor, nb: int = 0, sm_num=None, block_size=None, tag: str = "ar") -> torch.Tensor:
+        self._require_bf16(x, "all_reduce")
         ch = self.channel(f"{tag}/{nb}")
         n = x.numel()
-        off, _ = self.buffer(ch, "x", n * 2)
+        off, _ = self.buffer(ch, "x", n * x.element_size())
         buf = self.view(off, x.shape, x.dtype)
         if x.data_ptr() != buf.data_ptr():
             buf.copy_(x)
@@ -199,6 +213,7 @@ class SymmetricHeap:
 
     def all_gather(self, x: torch.Tensor, nb: int = 0, sm_num=None, block_size=None, tag: str = "ag",
                    keep: bool = False) -> torch.Tensor:
+        self._require_bf16(x, "all_gather")
         ch = self.channel(f"{tag}/{nb}")
         shard = x.numel() * x.element_size()
         off, _ = self.buffer(ch, "x", shard * self.world)
@@ -214,9 +229,10 @@ class SymmetricHeap:
         return out.clone() if keep else out
 
     def reduce_scatter(self, x: torch.Tensor, nb: int = 0, sm_num=None, block_size=None, tag: str = "rs") -> torch.Tensor:
+        self._require_bf16(x, "reduce_scatter")
         ch = self.channel(f"{tag}/{nb}")
         n = x.numel()
-        off, _ = self.buffer(ch, "x", n * 2)
+        off, _ = self.buffer(ch, "x", n * x.element_size())
         buf = self.view(off, x.shape, x.dtype)
         if x.data_ptr() != buf.data_ptr():
             buf.copy_(x)

@@ -53,8 +53,7 @@ class Trainer:
         self.dtype = dtype or train_cfg.dtype
         self.monitor, self.freq_client, self.comm_scheduler = monitor, freq_client, comm_scheduler
         mesh = self.mesh
-        comm = CommFactory(mesh, par.comm_backend, heap=heap)
-        comm.heap_cp = heap_cp        # symmetric heap of the context-parallel group (ring attention)
+        comm = CommFactory(mesh, par.comm_backend, heap=heap, heap_cp=heap_cp)
         self.model = GPTModel(model_cfg, par, mesh=mesh, comm=comm, dtype=self.dtype, device=self.device,
                               seed=train_cfg.seed, pre_process=mesh.is_first_stage,
                               post_process=mesh.is_last_stage,

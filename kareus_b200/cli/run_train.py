@@ -40,6 +40,9 @@ def main(argv=None) -> int:
     ap.add_argument("--enable-power-monitor", action="store_true")
     ap.add_argument("--enable-timers", action="store_true")
     ap.add_argument("--recompute-layers", type=int, default=4)
+    ap.add_argument("--save", default=None, help="write a distributed checkpoint (model + optimizer) here at the end")
+    ap.add_argument("--save-interval", type=int, default=0, help="also save every N steps")
+    ap.add_argument("--load", default=None, help="resume from this distributed checkpoint (any TP x PP x DP layout)")
     ap.add_argument("--keep-process-group", action="store_true",
                     help="leave torch.distributed initialised (when called from another driver)")
     a = ap.parse_args(argv)
@@ -98,12 +101,22 @@ def main(argv=None) -> int:
     if timers is not None:
         trainer._hooks.append(timers)
     power = PowerMonitor(local).start() if (a.enable_power_monitor and cuda) else None
+    first = 0
+    if a.load:
+        trainer.load_checkpoint(a.load)
+        first = trainer.step_index
+        if rank == 0:
+            print(f"resumed from {a.load} at step {first}", flush=True)
     try:
-        for step in range(a.steps):
+        for step in range(first, a.steps):
             batch = synthetic_batch(cfg, tc, M, seed=step, cp=a.cp, cp_rank=mesh.cp_rank)
             loss = trainer.train_step(batch, loss_denominator=float(a.gbs * a.seq))
             if rank == 0:
                 print(f"step {step} loss {loss:.4f}", flush=True)
+            if a.save and a.save_interval and (step + 1) % a.save_interval == 0 and step + 1 < a.steps:
+                trainer.save_checkpoint(a.save)
+        if a.save:
+            trainer.save_checkpoint(a.save)
     finally:
         ctl.close()
         if power is not None:

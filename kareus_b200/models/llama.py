@@ -297,7 +297,19 @@ class GPTModel(nn.Module):
             self.final_norm = RMSNormOp(cfg.hidden_size, cfg.norm_eps, "final_layernorm", dtype=dt,
                                         device=device, sequence_parallel=self.par.sequence_parallel)
             tied = self.embedding.weight if (cfg.tie_embeddings and pre_process) else None
-            self.output_layer = OutputHead(cfg, self.par, self.comm, dt, device, seed + 2, tied_weight=tied)
+            # tied weights on different pipeline stages: the last stage holds a copy with the same
+            # initial values (same seed as the embedding); finalize_grads sums the two gradients so
+            # both copies take identical updates (Megatron: copy of the init + all-reduce of the shared
+            # embedding gradients over the embedding group)
+            head_seed = seed + 1 if (cfg.tie_embeddings and not pre_process) else seed + 2
+            self.output_layer = OutputHead(cfg, self.par, self.comm, dt, device, head_seed, tied_weight=tied)
+        self.tied_across_stages = bool(cfg.tie_embeddings and (pre_process != post_process)
+                                       and mesh is not None and mesh.pp > 1)
+        if self.tied_across_stages:
+            w = self.embedding.weight if pre_process else self.output_layer.weight
+            w.shared_embedding = True
+            # the copy on the last stage is left out of the global gradient norm (counted once)
+            w.norm_exclude = not pre_process
         self._rope_cache: Dict[Tuple, torch.Tensor] = {}
 
     # ------------------------------------------------------------------ helpers
@@ -380,6 +392,9 @@ class GPTModel(nn.Module):
                 or getattr(p, "tp_partial_grad", False)
             if partial and getattr(p, "main_grad", None) is not None:
                 sp_params.append(p)
+        if self.tied_across_stages:
+            w = self.embedding.weight if self.pre_process else self.output_layer.weight
+            dist.all_reduce(ensure_main_grad(w), group=self.mesh.group("embd"))
         tp_group, tp, _ = self.comm._args("tp")
         if tp > 1 and sp_params:
             flat = torch.cat([p.main_grad.reshape(-1) for p in sp_params])

@@ -52,6 +52,17 @@ class Mesh:
                     mine = (ranks, g)
             self.group_ranks[name] = mine[0]
             self.groups[name] = mine[1]
+        # first and last pipeline stage of every (tp, cp, dp) column: the two holders of a tied
+        # embedding / output weight (Megatron's embedding group, parallel_state.py)
+        self.group_ranks["embd"], self.groups["embd"] = [rank], None
+        if pp > 1:
+            for t in range(tp):
+                for c in range(cp):
+                    for d in range(dp):
+                        ranks = [self.rank_of(t, c, d, 0), self.rank_of(t, c, d, pp - 1)]
+                        g = dist.new_group(ranks) if create_groups and dist.is_initialized() else None
+                        if rank in ranks:
+                            self.group_ranks["embd"], self.groups["embd"] = ranks, g
 
     # coordinates ------------------------------------------------------------
     def coord_of(self, rank: int) -> Coord:

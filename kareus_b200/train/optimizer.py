@@ -52,7 +52,11 @@ class DistributedAdamW:
         dev, dt = self.params[0].device, self.params[0].dtype
         self.offsets, o = [], 0
         self.replicated_start = None
+        # flat ranges left out of the gradient norm (second copy of a weight tied across stages)
+        self.norm_exclude = []
         for p in self.params:
+            if getattr(p, "norm_exclude", False):
+                self.norm_exclude.append((o, o + p.numel()))
             if replicated(p) and self.replicated_start is None:
                 self.replicated_start = o
             self.offsets.append(o)
@@ -108,6 +112,10 @@ class DistributedAdamW:
             a, b = max(self.replicated_start, self.lo), self.hi
             if b > a:
                 total = total - K.sumsq(g[a - self.lo:b - self.lo] if self.dp > 1 else self.grad_flat[a:b])
+        for a0, b0 in self.norm_exclude:
+            a, b = max(a0, self.lo), min(b0, self.hi)
+            if b > a:
+                total = total - K.sumsq(g[a - self.lo:b - self.lo] if self.dp > 1 else self.grad_flat[a:b])
         total = total.reshape(1).clone()
         if self.dp > 1:
             dist.all_reduce(total, group=self.dp_group)
@@ -140,6 +148,35 @@ class DistributedAdamW:
         return norm
 
     # ------------------------------------------------------------------ checkpoint
+    def gather_state(self) -> dict:
+        """Full-length flat AdamW state ``{exp_avg, exp_avg_sq, fp32_param}`` (length ``total``) on every
+        rank: the data-parallel shards all-gathered.  Collective over the data-parallel group."""
+        out = {}
+        for name, t in (("exp_avg", self.m), ("exp_avg_sq", self.v), ("fp32_param", self.master)):
+            if self.dp == 1:
+                out[name] = t
+            else:
+                full = torch.empty(self.total, dtype=t.dtype, device=t.device)
+                dist.all_gather_into_tensor(full, t.contiguous(), group=self.dp_group)
+                out[name] = full
+        return out
+
+    def empty_full_state(self) -> dict:
+        """Destination buffers for :meth:`scatter_state` (a checkpoint loader fills them in model space)."""
+        return {name: torch.zeros(self.total, dtype=self.master.dtype, device=self.master.device)
+                for name in ("exp_avg", "exp_avg_sq", "fp32_param")}
+
+    def scatter_state(self, full: dict, step: int) -> None:
+        """Take this data-parallel rank's shard of full-length state and refresh the parameters from the
+        fp32 master values."""
+        self.m.copy_(full["exp_avg"][self.lo:self.hi])
+        self.v.copy_(full["exp_avg_sq"][self.lo:self.hi])
+        self.master.copy_(full["fp32_param"][self.lo:self.hi])
+        self.step_count = int(step)
+        self.param_flat[self.lo:self.hi].copy_(self.master.to(self.param_flat.dtype))
+        if self.dp > 1:
+            dist.all_gather_into_tensor(self.param_flat, self.param_flat[self.lo:self.hi].clone(), group=self.dp_group)
+
     def state_dict(self) -> dict:
         return {"step": self.step_count, "master": self.master, "exp_avg": self.m, "exp_avg_sq": self.v,
                 "shard": (self.lo, self.hi), "total": self.total}

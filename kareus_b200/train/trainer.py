@@ -141,6 +141,26 @@ class Trainer:
         self.step_index += 1
         return out
 
+    # ------------------------------------------------------------------ checkpoint
+    def save_checkpoint(self, ckpt_dir, common: Optional[dict] = None) -> None:
+        """Collective over all ranks: model and optimizer state in the Megatron distributed-checkpoint
+        layout (reshardable), plus the step index."""
+        from ..models import checkpoint as ck
+        mesh = self.mesh
+        c = dict(common or {})
+        c["iteration"] = self.step_index
+        ck.save(self.model, ckpt_dir, rank=mesh.rank, tp_rank=mesh.tp_rank, tp=mesh.tp,
+                dp_rank=mesh.axis_rank("dp_cp"), common=c, optimizer=self.optimizer)
+
+    def load_checkpoint(self, ckpt_dir, strict: bool = True) -> dict:
+        """Resume from a checkpoint written under any TP x PP x DP layout."""
+        from ..models import checkpoint as ck
+        mesh = self.mesh
+        common = ck.load(self.model, ckpt_dir, tp_rank=mesh.tp_rank, tp=mesh.tp, strict=strict,
+                         optimizer=self.optimizer, dp_rank=mesh.axis_rank("dp_cp"))
+        self.step_index = int(common.get("iteration", 0))
+        return common
+
     def reduce_loss(self, loss: torch.Tensor) -> float:
         """Global mean token loss on every rank (sum over dp×cp shares; broadcast from the last stage)."""
         mesh = self.mesh

@@ -6,11 +6,13 @@ import torch.distributed as dist
 from dist_utils import run_distributed
 
 
-def _run_steps(tp, pp, dp, steps=2, n=2):
+def _run_steps(tp, pp, dp, steps=2, n=2, tie=False, want_trainer=False):
     from kareus_b200.config import ParallelConfig, TrainConfig, get_model_config
     from kareus_b200.parallel.mesh import Mesh
     from kareus_b200.train.trainer import Trainer, synthetic_batch
     cfg = get_model_config("tiny")
+    if tie:
+        cfg = cfg.replace(tie_embeddings=True)
     par = ParallelConfig(tp=tp, pp=pp, dp=dp, num_nanobatches=n, recompute=True)
     tc = TrainConfig(micro_batch_size=2, global_batch_size=8, seq_len=32, lr=2e-3, warmup_steps=0, max_steps=10,
                      dtype="fp64")
@@ -23,7 +25,7 @@ def _run_steps(tp, pp, dp, steps=2, n=2):
         lo = mesh.dp_rank * share
         batch = {k: v[lo:lo + share] for k, v in full.items()}
         losses.append(tr.train_step(batch, loss_denominator=float(full["loss_mask"].sum())))
-    return losses
+    return (losses, tr) if want_trainer else losses
 
 
 EXPECTED = {}
@@ -47,3 +49,24 @@ def test_parallel_layouts_match_single(tp, pp, dp):
     if tp > 1:
         pytest.skip("tp shards use rank-dependent init; covered by test_engine_distributed")
     run_distributed(_worker, tp * pp * dp, tp, pp, dp, want)
+
+
+def _tied_worker(rank, world, want):
+    got, tr = _run_steps(1, 2, 1, tie=True, want_trainer=True)
+    for a, b in zip(got, want):
+        assert abs(a - b) < 1e-8, (got, want)
+    # both holders of the tied weight still carry the same values after the updates
+    m = tr.model
+    w = (m.embedding.weight if m.pre_process else m.output_layer.weight).detach().clone()
+    both = [torch.empty_like(w) for _ in range(2)]
+    dist.all_gather(both, w)
+    assert torch.equal(both[0], both[1])
+    assert m.tied_across_stages
+
+
+def test_tied_embedding_across_pipeline_stages_matches_single():
+    """Embedding and output weight tied (Qwen3-style) with the two on different pipeline stages: same
+    losses as one stage holding one weight, which needs the same init, the summed gradient on both
+    copies and the copy counted once in the gradient norm."""
+    want = _run_steps(1, 1, 1, tie=True)
+    run_distributed(_tied_worker, 2, want)

@@ -12,6 +12,12 @@ tokens and random-init weights.  The global batch is fixed, so scaling over GPUs
 Two measurements are reported: ``value`` times K steps on the device (CUDA events, inputs staged
 on the device beforehand, max over ranks); ``e2e`` times K calls of ``Trainer.train_step`` with
 pinned host inputs copied every step and the loss read back every step.
+
+A third, shorter region re-times the same model in the reference-like configuration (all-reduce
+tensor parallelism over NCCL, cuBLAS GEMMs, flash-attention wheel, no launch lists) in the same
+process and reports it as ``nccl_cublas_baseline``, because the reference's own stack cannot be
+installed here.  Other layouts of the same engine: ``--tp/--pp/--cp`` (product = number of GPUs
+times 1/dp), ``--model``, ``--seq``, ``--mbs``, ``--gbs``, ``--cp-comm``.
 """
 from __future__ import annotations
 
@@ -109,6 +115,12 @@ def main() -> int:
     ap.add_argument("--comm-sm", type=int, default=int(os.environ.get("KAREUS_COMM_SM", "16")),
                     help="CTAs given to a collective (plan knob sm_num) when no plan file is loaded")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--tp", type=int, default=0, help="tensor-parallel size (default: all GPUs not used by pp/cp)")
+    ap.add_argument("--pp", type=int, default=1)
+    ap.add_argument("--cp", type=int, default=1)
+    ap.add_argument("--cp-comm", default="all_gather", choices=["all_gather", "ring"])
+    ap.add_argument("--baseline-steps", type=int, default=int(os.environ.get("KAREUS_BASELINE_STEPS", "5")),
+                    help="timed steps of the NCCL + cuBLAS + flash-attention configuration (0: skip)")
     args = ap.parse_args()
     if args.impl == "reference":
         return _reference_arm(args)
@@ -135,9 +147,10 @@ def main() -> int:
         args.tp_comm = "sp_fused"
     if args.comm_backend is None:
         args.comm_backend = "kernel"
-    if world > 1 and args.tp_comm == "sp_fused":
+    tp = args.tp or max(1, world // (args.pp * args.cp))
+    if tp > 1 and args.tp_comm == "sp_fused":
         os.environ.setdefault("KAREUS_SYNC", "lazy")
-        if world >= 4:
+        if tp >= 4:
             # two nanobatches' fused kernels side by side, each on half of the SMs
             os.environ.setdefault("KAREUS_COMM_STREAMS", "per_nanobatch")
             os.environ.setdefault("KAREUS_FUSED_SMS", "72")
@@ -145,18 +158,32 @@ def main() -> int:
                 args.comm_sm = 12
     cfg = get_model_config(args.model)
     tc = TrainConfig(micro_batch_size=args.mbs, global_batch_size=args.gbs, seq_len=args.seq, dtype="bf16")
-    par = ParallelConfig(tp=world, num_nanobatches=args.nano, tp_comm=args.tp_comm if world > 1 else "allreduce",
-                         comm_backend=args.comm_backend, recompute=True)
-    mesh = Mesh(tp=world)
-    heap = None
-    if world > 1 and (par.comm_backend == "kernel" or par.tp_comm == "sp_fused"):
+    if world % (tp * args.pp * args.cp):
+        raise SystemExit(f"tp {tp} x pp {args.pp} x cp {args.cp} does not divide {world} GPUs")
+    dp = world // (tp * args.pp * args.cp)
+    mesh = Mesh(tp=tp, cp=args.cp, dp=dp, pp=args.pp)
+    heap = heap_cp = None
+    if tp > 1 and (args.comm_backend == "kernel" or args.tp_comm == "sp_fused"):
         from kareus_b200.parallel.symm_heap import SymmetricHeap
         heap = SymmetricHeap.create(mesh.group("tp"), device)
-    trainer = Trainer(cfg, par, tc, mesh=mesh, device=device, heap=heap, recompute_layers=args.recompute_layers,
-                      sync=os.environ.get("KAREUS_SYNC", "partition_end"))
-    trainer.model.decoder.engine.default_shape = (args.comm_sm, 1024)
+    if args.cp > 1 and args.cp_comm == "ring":
+        from kareus_b200.parallel.symm_heap import SymmetricHeap
+        heap_cp = SymmetricHeap.create(mesh.group("cp"), device, size_bytes=2 << 30)
+
+    def make_trainer(tp_comm, comm_backend):
+        par = ParallelConfig(tp=tp, cp=args.cp, dp=dp, pp=args.pp, num_nanobatches=args.nano,
+                             tp_comm=tp_comm if tp > 1 else "allreduce", comm_backend=comm_backend, recompute=True,
+                             cp_comm=args.cp_comm)
+        t = Trainer(cfg, par, tc, mesh=mesh, device=device, heap=heap if comm_backend == "kernel" or tp_comm == "sp_fused" else None,
+                    heap_cp=heap_cp, recompute_layers=args.recompute_layers,
+                    sync=os.environ.get("KAREUS_SYNC", "partition_end"))
+        t.model.decoder.engine.default_shape = (args.comm_sm, 1024)
+        return t, par
+
+    trainer, par = make_trainer(args.tp_comm, args.comm_backend)
     M = trainer.num_microbatches
-    host_batches = [synthetic_batch(cfg, tc, M, seed=1000 + i) for i in range(2)]
+    host_batches = [synthetic_batch(cfg, tc, M, seed=1000 + i + 17 * mesh.dp_rank, cp=args.cp, cp_rank=mesh.cp_rank)
+                    for i in range(2)]
     tokens_per_step = args.gbs * args.seq
     denom = float(tokens_per_step)
 
@@ -168,9 +195,12 @@ def main() -> int:
 
     # ------------------------------------------------------------- device-timed region
     dev_batches = [trainer.to_device(b) for b in host_batches]
+    first_loss = None
     for i in range(args.warmup):
         trainer.optimizer.zero_grad()
-        trainer.forward_backward(dev_batches[i % 2], denom)
+        l = trainer.forward_backward(dev_batches[i % 2], denom)
+        if first_loss is None:
+            first_loss = trainer.reduce_loss(l)       # random-init model: about ln(vocab)
         trainer.model.finalize_grads()
         trainer.optimizer.step()
     sync_all()
@@ -181,12 +211,14 @@ def main() -> int:
     l0 = launch_count()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
+    h0 = time.perf_counter()
     for i in range(args.steps):
         trainer.optimizer.zero_grad()
         loss = trainer.forward_backward(dev_batches[i % 2], denom)
         trainer.model.finalize_grads()
         trainer.optimizer.step()
     end.record()
+    host_ms = (time.perf_counter() - h0) * 1000.0      # time the host needed to enqueue the K steps
     sync_all()
     e1 = sampler.energy_mj()
     launches = launch_count() - l0
@@ -223,14 +255,71 @@ def main() -> int:
                "d2h_bytes_per_step": 4, "ms_per_step": dt * 1000.0 / args.steps}
         KC.check_status()
 
+    # ------------------------------------------------------------- reference-like configuration, same process
+    baseline = None
+    if args.baseline_steps > 0:
+        replayed = trainer.model.decoder.engine.replayed_regions
+        del trainer, dev_batches
+        torch.cuda.empty_cache()
+        os.environ["KAREUS_B200_LIBRARY_BASELINE"] = "1"
+        streams_mode = os.environ.get("KAREUS_COMM_STREAMS")
+        os.environ["KAREUS_COMM_STREAMS"] = "shared"          # one ordered side stream, like the reference
+        try:
+            bt, _ = make_trainer("allreduce", "nccl")
+            bt.model.decoder.engine.replay = False
+            bdev = [bt.to_device(b) for b in host_batches]
+
+            def bstep(i):
+                bt.optimizer.zero_grad()
+                l_ = bt.forward_backward(bdev[i % 2], denom)
+                bt.model.finalize_grads()
+                bt.optimizer.step()
+                return l_
+
+            for i in range(3):
+                bstep(i)
+            sync_all()
+            be0 = sampler.energy_mj()
+            bs, be = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            bs.record()
+            for i in range(args.baseline_steps):
+                bl = bstep(i)
+            be.record()
+            sync_all()
+            be1 = sampler.energy_mj()
+            bt_ms = torch.tensor([bs.elapsed_time(be)], device=device, dtype=torch.float64)
+            ben = torch.tensor([(be1 - be0) / 1000.0 if (be0 is not None and be1 is not None) else 0.0],
+                               device=device, dtype=torch.float64)
+            if world > 1:
+                dist.all_reduce(bt_ms, op=dist.ReduceOp.MAX)
+                dist.all_reduce(ben, op=dist.ReduceOp.SUM)
+            bms = float(bt_ms.item())
+            baseline = {"value": tokens_per_step * args.baseline_steps / (bms / 1000.0), "unit": "tokens/s",
+                        "ms_per_step": bms / args.baseline_steps, "steps": args.baseline_steps, "warmup": 3,
+                        "energy_j_per_step": float(ben.item()) / args.baseline_steps, "loss": bt.reduce_loss(bl),
+                        "config": "same model, batch and layout; all-reduce tensor parallelism over NCCL, cuBLAS "
+                                  "GEMMs, flash-attention wheel, interpreter-driven launches"}
+            del bt, bdev
+        finally:
+            os.environ.pop("KAREUS_B200_LIBRARY_BASELINE", None)
+            if streams_mode is None:
+                os.environ.pop("KAREUS_COMM_STREAMS", None)
+            else:
+                os.environ["KAREUS_COMM_STREAMS"] = streams_mode
+    else:
+        replayed = trainer.model.decoder.engine.replayed_regions
+
+    layout = "".join(f"{k}{v}" for k, v in (("tp", tp), ("pp", args.pp), ("cp", args.cp), ("dp", dp)) if v > 1) or "tp1"
     if rank == 0:
         out = {
-            "metric": "tokens/s (Llama-3.2-3B training throughput)", "value": value, "unit": "tokens/s",
+            "metric": f"tokens/s ({cfg.name} training throughput)" if args.model != "llama3.2_3b" else
+                      "tokens/s (Llama-3.2-3B training throughput)", "value": value, "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": value / BASELINE_TOKENS_PER_S,
             "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights",
             "config": {"model": args.model, "global_batch": args.gbs, "micro_batch": args.mbs, "seq_len": args.seq,
-                       "parallelism": f"tp{world}", "nanobatches": args.nano, "tp_comm": par.tp_comm,
+                       "parallelism": layout, "nanobatches": args.nano, "tp_comm": par.tp_comm,
+                       "cp_comm": args.cp_comm if args.cp > 1 else None,
                        "comm_backend": par.comm_backend, "comm_sm": args.comm_sm,
                        "sync": os.environ.get("KAREUS_SYNC", "partition_end"),
                        "comm_streams": os.environ.get("KAREUS_COMM_STREAMS", "shared"),
@@ -239,6 +328,11 @@ def main() -> int:
                        "l2": "inputs larger than L2 (6.4 GB of weights and multi-GB activations per step)"},
             "energy_j_per_step": float(en.item()) / args.steps,
             "clocks": sampler.summary(), "e2e": e2e, "gpu_launches": launches, "loss": final_loss,
+            "first_step_loss": first_loss, "launches_per_step": launches / args.steps,
+            "host_enqueue_ms_per_step": host_ms / args.steps,
+            "host_us_per_launch": host_ms * 1000.0 / max(1, launches),
+            "launch_list_regions_replayed": replayed,
+            "nccl_cublas_baseline": baseline,
             "impl": "ours",
         }
         print(json.dumps(out))

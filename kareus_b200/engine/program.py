@@ -114,6 +114,36 @@ def split_segments(nodes: Sequence[Node], trail_key: str) -> List[Segment]:
     return segs
 
 
+def _rec():
+    from ..kernels import replay
+    return replay
+
+
+def record_event(stream):
+    """New event recorded on ``stream`` (mirrored into an open launch-list recording)."""
+    ev = torch.cuda.Event()
+    ev.record(stream)
+    _rec().note_event_record(ev, stream)
+    return ev
+
+
+def wait_event(stream, ev) -> None:
+    stream.wait_event(ev)
+    _rec().note_stream_wait(stream, ev)
+
+
+def wait_stream(stream, other) -> None:
+    """``stream`` waits for everything enqueued on ``other`` so far."""
+    wait_event(stream, record_event(other))
+
+
+def record_stream(t, stream) -> None:
+    """``t`` is used on ``stream`` although it was allocated on another one."""
+    if isinstance(t, torch.Tensor) and t.is_cuda:
+        t.record_stream(stream)
+        _rec().note_cross_stream_use(t)
+
+
 class StreamSet:
     """Compute/side stream pair.  On CPU everything is ``None`` and waits are no-ops."""
 
@@ -145,9 +175,7 @@ class StreamSet:
     def record(self, stream):
         if not self.cuda:
             return None
-        ev = torch.cuda.Event()
-        ev.record(stream)
-        return ev
+        return record_event(stream)
 
 
 _COMM_STREAMS: Dict[tuple, "torch.cuda.Stream"] = {}
@@ -285,7 +313,7 @@ class PartitionProgram:
             ev = store.event(p.tensor_id)
             if ev is not None:
                 if streams.cuda:
-                    streams.compute().wait_event(ev)
+                    wait_event(streams.compute(), ev)
                 store.clear_event(p.tensor_id)
             ins.append(store.get(p.tensor_id))
         op = node.operator
@@ -325,13 +353,13 @@ class PartitionProgram:
         if streams.cuda:
             ready = nbctx.ready_event.get(st.comm_segment)
             if ready is not None:
-                side.wait_event(ready)
+                wait_event(side, ready)
             else:
-                side.wait_stream(streams.compute())
+                wait_stream(side, streams.compute())
             for p in node.inputs:           # input produced by an earlier collective
                 ev = store.event(p.tensor_id)
                 if ev is not None:
-                    side.wait_event(ev)
+                    wait_event(side, ev)
         sm_num, block = shape if shape is not None else (None, None)
         ctx = nbctx.ctx_for(node.op_id) if getattr(node.operator, "needs_ctx", False) else None
         if streams.cuda:
@@ -340,8 +368,7 @@ class PartitionProgram:
                                          nb=nb, ctx=ctx)
             done = streams.record(side)
             for t in ins:
-                if isinstance(t, torch.Tensor):
-                    t.record_stream(side)
+                record_stream(t, side)
         else:
             outs = node.operator.run(ins, sm_num=sm_num, block_size=block, backward=self.backward,
                                      nb=nb, ctx=ctx)
@@ -350,15 +377,15 @@ class PartitionProgram:
             outs = (outs,)
         for p, t in zip(node.outputs, outs):
             store.put(p.tensor_id, t, event=done)
-            if streams.cuda and isinstance(t, torch.Tensor):
-                t.record_stream(streams.compute())
+            if streams.cuda:
+                record_stream(t, streams.compute())
         self._free_dead(node, store)
         pending.append((node, nb, done))
 
     def _wait_all(self, pending, ctxs, streams: StreamSet) -> None:
         for node, nb, done in pending:
             if done is not None and streams.cuda:
-                streams.compute().wait_event(done)
+                wait_event(streams.compute(), done)
             for p in node.outputs:
                 ctxs[nb].store.clear_event(p.tensor_id)
         pending.clear()

@@ -55,10 +55,15 @@ def rmsnorm_fwd(x, w, eps):
     return ref.rmsnorm_fwd(x, w, eps)
 
 
-def rmsnorm_bwd(dy, x, rstd, w):
+def rmsnorm_bwd(dy, x, rstd, w, dw_accum=None):
+    """``(dx, dw)``; with ``dw_accum`` the weight gradient is added into that buffer and ``dw`` is None."""
     if is_cuda(x):
-        return _cuda().rmsnorm_bwd(dy, x, rstd, w)
-    return ref.rmsnorm_bwd(dy, x, rstd, w)
+        return _cuda().rmsnorm_bwd(dy, x, rstd, w, dw_accum)
+    dx, dw = ref.rmsnorm_bwd(dy, x, rstd, w)
+    if dw_accum is not None:
+        dw_accum.add_(dw.reshape(dw_accum.shape).to(dw_accum.dtype))
+        dw = None
+    return dx, dw
 
 
 # ----------------------------------------------------------------------------- rope

@@ -49,8 +49,10 @@ def backward(do, q, k, v, o, lse, scale, causal=True, q_offset=0, kv_len=None, o
         return KC.attention_bwd_library(do, q, k, v, o, lse, scale, causal, q_offset, kv_len, out)
     skv = k.shape[0] if kv_len is None else int(kv_len)
     hq = g * rep
-    o4 = o.reshape(sq, b, hq, d).contiguous()
-    do4 = do.reshape(sq, b, hq, d).contiguous()
+    o4, do4 = o.reshape(sq, b, hq, d), do.reshape(sq, b, hq, d)
+    if not (o4.is_contiguous() and do4.is_contiguous()):
+        KC._no_recording("making attention outputs contiguous")
+        o4, do4 = o4.contiguous(), do4.contiguous()
     if out is None:
         dq = torch.empty(sq, b, g, rep, d, dtype=q.dtype, device=q.device)
         dk = torch.empty_like(k, memory_format=torch.contiguous_format)
@@ -58,6 +60,7 @@ def backward(do, q, k, v, o, lse, scale, causal=True, q_offset=0, kv_len=None, o
     else:
         dq, dk, dv = out
     if skv < k.shape[0]:
+        KC._no_recording("zero-filling the unseen keys' gradients")
         dk[skv:].zero_()
         dv[skv:].zero_()
     _, _, _, _, _, dqs = _geom5(dq, kg)

@@ -2,6 +2,7 @@
 // The Llama/Qwen models of the benchmarks use SwiGLU (elementwise.cu); these cover the reference's
 // other activation operators (kareus/megatron/core/extensions/ops/bias_gelu.py, bias_geglu.py).
 #include <cuda_bf16.h>
+#include "launch.h"
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -55,7 +56,7 @@ extern "C" int kb_gelu_fwd(const void* x, void* y, long rows, int F, int gated, 
   long b = (rows * F + 255) / 256;
   if (b > 148 * 16) b = 148 * 16;
   if (b < 1) b = 1;
-  kb::gelu_fwd_kernel<<<(int)b, 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, rows, F, gated);
+  KB_LAUNCH(kb::gelu_fwd_kernel, (int)b, 256, 0, st, (const __nv_bfloat16*)x, (__nv_bfloat16*)y, rows, F, gated);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 2000 + (int)e;
 }
@@ -63,7 +64,7 @@ extern "C" int kb_gelu_bwd(const void* dy, const void* x, void* dx, long rows, i
   long b = (rows * F + 255) / 256;
   if (b > 148 * 16) b = 148 * 16;
   if (b < 1) b = 1;
-  kb::gelu_bwd_kernel<<<(int)b, 256, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (__nv_bfloat16*)dx, rows,
+  KB_LAUNCH(kb::gelu_bwd_kernel, (int)b, 256, 0, st, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (__nv_bfloat16*)dx, rows,
                                               F, gated);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 2000 + (int)e;

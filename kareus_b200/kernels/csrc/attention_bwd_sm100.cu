@@ -16,6 +16,7 @@
 // Replaces the FlashAttention-2 backward the reference calls through its wheel
 // (kareus/flash_attn/flash_attn_interface.py:147-199).
 #include "sm100.cuh"
+#include "launch.h"
 #include "host_utils.h"
 
 namespace kb {
@@ -354,13 +355,13 @@ extern "C" int kb_flash_attn_bwd(const void* q, long qs_s, long qs_b, long qs_g,
   float* dk_acc = dq_acc + n_dq;
   float* dv_acc = dk_acc + n_dkv;
   float* delta = dv_acc + n_dkv;
-  cudaError_t e = cudaMemsetAsync(work, 0, sizeof(float) * (n_dq + 2 * n_dkv), stream);
+  cudaError_t e = kb::memset_async(work, 0, sizeof(float) * (n_dq + 2 * n_dkv), stream);
   if (e != cudaSuccess) return 1000 + (int)e;
   {
     const long rows = (long)sq * b * hq;
     long blocks = (rows * 32 + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
-    attn_delta_kernel<<<(int)blocks, 256, 0, stream>>>((const __nv_bfloat16*)dO, (const __nv_bfloat16*)o, delta, sq, b, hq);
+    KB_LAUNCH(attn_delta_kernel, (int)blocks, 256, 0, stream, (const __nv_bfloat16*)dO, (const __nv_bfloat16*)o, delta, sq, b, hq);
   }
   CUtensorMap tmQ, tmK, tmV, tmDO;
   int rc = make_qkv_map(&tmQ, q, d, rep, g, b, sq, qs_r, qs_g, qs_b, qs_s, 1);
@@ -389,13 +390,13 @@ extern "C" int kb_flash_attn_bwd(const void* q, long qs_s, long qs_b, long qs_g,
   }
   if (n_kv > 0) {
     dim3 grid(n_kv, hq, b);
-    flash_attn_bwd_kernel<<<grid, FB_THREADS, FbSmem::TOTAL, stream>>>(tmQ, tmK, tmV, tmDO, p);
+    KB_LAUNCH(flash_attn_bwd_kernel, grid, FB_THREADS, FbSmem::TOTAL, stream, tmQ, tmK, tmV, tmDO, p);
   }
   auto conv = [&](const float* acc, void* out, long n, int G, int R, long s_s, long s_b, long s_g, long s_r) {
     long nvec = n / 4;
     long blocks = (nvec + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
-    attn_convert_kernel<<<(int)blocks, 256, 0, stream>>>(acc, (__nv_bfloat16*)out, nvec, b, G, R, s_s, s_b, s_g, s_r);
+    KB_LAUNCH(attn_convert_kernel, (int)blocks, 256, 0, stream, acc, (__nv_bfloat16*)out, nvec, b, G, R, s_s, s_b, s_g, s_r);
   };
   conv(dq_acc, dq, n_dq, g, rep, dqs_s, dqs_b, dqs_g, dqs_r);
   conv(dk_acc, dk, n_dkv, g, 1, dks_s, dks_b, dks_g, 0);

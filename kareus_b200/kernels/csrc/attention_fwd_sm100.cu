@@ -15,6 +15,7 @@
 // transposes sbhd→bshd and calls the FlashAttention-2 wheel:
 // kareus/transformer_engine/pytorch/attention/dot_product_attention/backends.py:179-186,328-333).
 #include "sm100.cuh"
+#include "launch.h"
 #include "host_utils.h"
 
 namespace kb {
@@ -437,7 +438,7 @@ extern "C" int kb_flash_attn_fwd(const void* q, long qs_s, long qs_b, long qs_g,
     configured = true;
   }
   dim3 grid((sq + FA_BM - 1) / FA_BM, g * rep, b);
-  flash_attn_fwd_kernel<<<grid, FA_THREADS, FaSmem::TOTAL, stream>>>(tmQ, tmK, tmV, p);
+  KB_LAUNCH(flash_attn_fwd_kernel, grid, FA_THREADS, FaSmem::TOTAL, stream, tmQ, tmK, tmV, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 2000 + (int)e;
 }

@@ -9,6 +9,7 @@
 //
 // Also here: the host side of the heap (allocation, CUDA IPC handle exchange is done by the caller).
 #include <cuda_bf16.h>
+#include "launch.h"
 #include <string.h>
 #include "peer.cuh"
 
@@ -158,14 +159,16 @@ static int clamp_block(int b) { return b < 32 ? 32 : (b > 1024 ? 1024 : (b / 32)
 extern "C" int kb_allreduce(void* const* bases, int rank, int world, uint64_t flag_off, uint64_t off, long n,
                             uint64_t epoch, int sm_num, int block, int* status, cudaStream_t st) {
   if (world < 1 || world > MAX_PEERS || (off & 15)) return ST_BAD_ARG;
-  allreduce_kernel<<<clamp_grid(sm_num), clamp_block(block), 0, st>>>(make_ctx(bases, rank, world, flag_off, status),
+  KB_LAUNCH_EPOCH(allreduce_kernel, clamp_grid(sm_num), clamp_block(block), 0, st, (EpochLoc{3, 0, 8}),
+                  make_ctx(bases, rank, world, flag_off, status),
                                                                       off, n, epoch);
   KB_RET_LAUNCH();
 }
 extern "C" int kb_allgather(void* const* bases, int rank, int world, uint64_t flag_off, uint64_t off, long shard_bytes,
                             uint64_t epoch, int sm_num, int block, int* status, cudaStream_t st) {
   if (world < 1 || world > MAX_PEERS || (off & 15) || (shard_bytes & 15)) return ST_BAD_ARG;
-  allgather_kernel<<<clamp_grid(sm_num), clamp_block(block), 0, st>>>(make_ctx(bases, rank, world, flag_off, status),
+  KB_LAUNCH_EPOCH(allgather_kernel, clamp_grid(sm_num), clamp_block(block), 0, st, (EpochLoc{3, 0, 8}),
+                  make_ctx(bases, rank, world, flag_off, status),
                                                                       off, shard_bytes, epoch);
   KB_RET_LAUNCH();
 }
@@ -173,18 +176,18 @@ extern "C" int kb_reducescatter(void* const* bases, int rank, int world, uint64_
                                 long shard_elems, void* out, uint64_t epoch, int sm_num, int block, int* status,
                                 cudaStream_t st) {
   if (world < 1 || world > MAX_PEERS || (off & 15) || ((shard_elems * 2) & 15)) return ST_BAD_ARG;
-  reducescatter_kernel<<<clamp_grid(sm_num), clamp_block(block), 0, st>>>(
+  KB_LAUNCH_EPOCH(reducescatter_kernel, clamp_grid(sm_num), clamp_block(block), 0, st, (EpochLoc{4, 0, 8}),
       make_ctx(bases, rank, world, flag_off, status), off, shard_elems, reinterpret_cast<__nv_bfloat16*>(out), epoch);
   KB_RET_LAUNCH();
 }
 extern "C" int kb_peer_barrier(void* const* bases, int rank, int world, uint64_t flag_off, uint64_t epoch, int* status,
                                cudaStream_t st) {
   if (world < 1 || world > MAX_PEERS) return ST_BAD_ARG;
-  barrier_kernel<<<1, 32, 0, st>>>(make_ctx(bases, rank, world, flag_off, status), epoch);
+  KB_LAUNCH_EPOCH(barrier_kernel, 1, 32, 0, st, (EpochLoc{1, 0, 8}), make_ctx(bases, rank, world, flag_off, status), epoch);
   KB_RET_LAUNCH();
 }
 extern "C" int kb_wait_flag(const void* slot, uint64_t want, uint64_t limit_ns, int* status, cudaStream_t st) {
-  wait_flag_kernel<<<1, 1, 0, st>>>(reinterpret_cast<const uint64_t*>(slot), want, limit_ns, status);
+  KB_LAUNCH(wait_flag_kernel, 1, 1, 0, st, reinterpret_cast<const uint64_t*>(slot), want, limit_ns, status);
   KB_RET_LAUNCH();
 }
 

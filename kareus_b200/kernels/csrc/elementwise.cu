@@ -6,6 +6,7 @@
 //   embedding gather / scatter-add, vocab-parallel cross entropy (reference: TE Triton CE)
 //   fused AdamW over flat buffers, sum of squares (reference: TE/Apex multi_tensor kernels)
 #include <cuda_bf16.h>
+#include "launch.h"
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -207,13 +208,14 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
   }
 }
 
+// `accumulate`: add the column sums to dw (the fp32 main gradient of the weight) instead of storing them.
 __global__ void rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dw, int nparts,
-                                         int H) {
+                                         int H, int accumulate) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= H) return;
   float s = 0.f;
   for (int p = 0; p < nparts; ++p) s += partial[static_cast<size_t>(p) * H + c];
-  dw[c] = s;
+  dw[c] = accumulate ? dw[c] + s : s;
 }
 
 // General (slow) backward for narrow rows: one warp per row, dw via atomics.
@@ -561,10 +563,10 @@ using namespace kb;
 extern "C" int kb_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int rows, int H, float eps,
                               cudaStream_t st) {
   if (H % 8 == 0 && H >= 512) {
-    rmsnorm_fwd_kernel<<<grid_for(rows, 1, 148 * 8), NORM_THREADS, 0, st>>>(
+    KB_LAUNCH(rmsnorm_fwd_kernel, grid_for(rows, 1, 148 * 8), NORM_THREADS, 0, st, 
         (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, rstd, rows, H, eps);
   } else {
-    rmsnorm_fwd_warp_kernel<<<grid_for(rows, 8, 148 * 8), 256, 0, st>>>(
+    KB_LAUNCH(rmsnorm_fwd_warp_kernel, grid_for(rows, 8, 148 * 8), 256, 0, st, 
         (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, rstd, rows, H, eps);
   }
   KB_CHECK_LAUNCH();
@@ -576,21 +578,28 @@ extern "C" long kb_rmsnorm_bwd_scratch_elems(int rows, int H) {
   return 0;
 }
 
-extern "C" int kb_rmsnorm_bwd(const void* dy, const void* x, const float* rstd, const void* w, void* dx, float* dw,
-                              float* scratch, int rows, int H, cudaStream_t st) {
+// dx and the weight gradient of RMSNorm.  accumulate = 0: dw receives the gradient; 1: the gradient is
+// added to dw (callers pass the weight's fp32 main gradient and save a separate add).
+extern "C" int kb_rmsnorm_bwd_acc(const void* dy, const void* x, const float* rstd, const void* w, void* dx, float* dw,
+                                  float* scratch, int rows, int H, int accumulate, cudaStream_t st) {
   if (H % 8 == 0 && H >= 512 && H <= NORM_THREADS * NORM_VPT * 8) {
     const int grid = grid_for(rows, 1, 148 * 2);
     if (!scratch) return 7;
-    rmsnorm_bwd_kernel<<<grid, NORM_THREADS, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, rstd,
+    KB_LAUNCH(rmsnorm_bwd_kernel, grid, NORM_THREADS, 0, st, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, rstd,
                                                       (const __nv_bfloat16*)w, (__nv_bfloat16*)dx, scratch, rows, H);
-    rmsnorm_dw_reduce_kernel<<<(H + 255) / 256, 256, 0, st>>>(scratch, dw, grid, H);
+    KB_LAUNCH(rmsnorm_dw_reduce_kernel, (H + 255) / 256, 256, 0, st, scratch, dw, grid, H, accumulate);
   } else {
-    cudaMemsetAsync(dw, 0, sizeof(float) * H, st);
-    rmsnorm_bwd_warp_kernel<<<grid_for(rows, 8, 148 * 4), 256, sizeof(float) * H, st>>>(
+    if (!accumulate) kb::memset_async(dw, 0, sizeof(float) * H, st);    // the kernel adds with atomics
+    KB_LAUNCH(rmsnorm_bwd_warp_kernel, grid_for(rows, 8, 148 * 4), 256, sizeof(float) * H, st, 
         (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, rstd, (const __nv_bfloat16*)w, (__nv_bfloat16*)dx, dw,
         rows, H);
   }
   KB_CHECK_LAUNCH();
+}
+
+extern "C" int kb_rmsnorm_bwd(const void* dy, const void* x, const float* rstd, const void* w, void* dx, float* dw,
+                              float* scratch, int rows, int H, cudaStream_t st) {
+  return kb_rmsnorm_bwd_acc(dy, x, rstd, w, dx, dw, scratch, rows, H, 0, st);
 }
 
 extern "C" int kb_rope(void* q, long qs_s, long qs_b, long qs_g, long qs_r, int G, int R, void* k, long ks_s,
@@ -598,7 +607,7 @@ extern "C" int kb_rope(void* q, long qs_s, long qs_b, long qs_g, long qs_r, int 
                        int inverse, cudaStream_t st) {
   if (D % 4) return 7;
   const long warps = (long)S * B * (G * R + KG);
-  rope_kernel<<<grid_for(warps * 32, 256, 148 * 16), 256, 0, st>>>(
+  KB_LAUNCH(rope_kernel, grid_for(warps * 32, 256, 148 * 16), 256, 0, st, 
       (__nv_bfloat16*)q, qs_s, qs_b, qs_g, qs_r, G, R, (__nv_bfloat16*)k, ks_s, ks_b, ks_g, KG, cosb, sinb, S, B, D,
       inverse ? -1.f : 1.f);
   KB_CHECK_LAUNCH();
@@ -606,70 +615,70 @@ extern "C" int kb_rope(void* q, long qs_s, long qs_b, long qs_g, long qs_r, int 
 
 extern "C" int kb_swiglu_fwd(const void* x, void* y, long rows, int F, cudaStream_t st) {
   if (F % 8) return 7;
-  swiglu_fwd_kernel<<<grid_for(rows * (F / 8), 256, 148 * 16), 256, 0, st>>>((const __nv_bfloat16*)x,
+  KB_LAUNCH(swiglu_fwd_kernel, grid_for(rows * (F / 8), 256, 148 * 16), 256, 0, st, (const __nv_bfloat16*)x,
                                                                               (__nv_bfloat16*)y, rows, F);
   KB_CHECK_LAUNCH();
 }
 extern "C" int kb_swiglu_bwd(const void* dy, const void* x, void* dx, long rows, int F, cudaStream_t st) {
   if (F % 8) return 7;
-  swiglu_bwd_kernel<<<grid_for(rows * (F / 8), 256, 148 * 16), 256, 0, st>>>(
+  KB_LAUNCH(swiglu_bwd_kernel, grid_for(rows * (F / 8), 256, 148 * 16), 256, 0, st, 
       (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (__nv_bfloat16*)dx, rows, F);
   KB_CHECK_LAUNCH();
 }
 extern "C" int kb_dropout_add_fwd(const void* x, const void* res, void* y, long n, float p, unsigned seed,
                                   cudaStream_t st) {
   if (n % 8) return 7;
-  dropout_add_fwd_kernel<<<grid_for(n / 8, 256, 148 * 16), 256, 0, st>>>(
+  KB_LAUNCH(dropout_add_fwd_kernel, grid_for(n / 8, 256, 148 * 16), 256, 0, st, 
       (const __nv_bfloat16*)x, (const __nv_bfloat16*)res, (__nv_bfloat16*)y, n / 8, p, seed);
   KB_CHECK_LAUNCH();
 }
 extern "C" int kb_dropout_bwd(const void* dy, void* dx, long n, float p, unsigned seed, cudaStream_t st) {
   if (n % 8) return 7;
-  dropout_bwd_kernel<<<grid_for(n / 8, 256, 148 * 16), 256, 0, st>>>((const __nv_bfloat16*)dy, (__nv_bfloat16*)dx,
+  KB_LAUNCH(dropout_bwd_kernel, grid_for(n / 8, 256, 148 * 16), 256, 0, st, (const __nv_bfloat16*)dy, (__nv_bfloat16*)dx,
                                                                       n / 8, p, seed);
   KB_CHECK_LAUNCH();
 }
 extern "C" int kb_add(const void* a, const void* b, void* y, long n, cudaStream_t st) {
   if (n % 8) return 7;
-  add_kernel<<<grid_for(n / 8, 256, 148 * 16), 256, 0, st>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)b,
+  KB_LAUNCH(add_kernel, grid_for(n / 8, 256, 148 * 16), 256, 0, st, (const __nv_bfloat16*)a, (const __nv_bfloat16*)b,
                                                               (__nv_bfloat16*)y, n / 8);
   KB_CHECK_LAUNCH();
 }
 extern "C" int kb_embedding_fwd(const long* tokens, const void* w, void* out, long ntok, int H, long vocab_start,
                                 long vlocal, cudaStream_t st) {
   if (H % 8) return 7;
-  embedding_fwd_kernel<<<grid_for(ntok, 1, 148 * 16), 128, 0, st>>>(tokens, (const __nv_bfloat16*)w,
+  KB_LAUNCH(embedding_fwd_kernel, grid_for(ntok, 1, 148 * 16), 128, 0, st, tokens, (const __nv_bfloat16*)w,
                                                                      (__nv_bfloat16*)out, ntok, H, vocab_start, vlocal);
   KB_CHECK_LAUNCH();
 }
 extern "C" int kb_embedding_bwd(const long* tokens, const void* dout, float* gw, long ntok, int H, long vocab_start,
                                 long vlocal, cudaStream_t st) {
-  embedding_bwd_kernel<<<grid_for(ntok, 1, 148 * 16), 256, 0, st>>>(tokens, (const __nv_bfloat16*)dout, gw, ntok, H,
+  KB_LAUNCH(embedding_bwd_kernel, grid_for(ntok, 1, 148 * 16), 256, 0, st, tokens, (const __nv_bfloat16*)dout, gw, ntok, H,
                                                                      vocab_start, vlocal);
   KB_CHECK_LAUNCH();
 }
 extern "C" int kb_ce_stats(const void* logits, const long* targets, float* omax, float* osum, float* otgt, long rows,
                            int V, long vocab_start, cudaStream_t st) {
-  ce_stats_kernel<<<grid_for(rows, 1, 148 * 4), CE_THREADS, 0, st>>>((const __nv_bfloat16*)logits, targets, omax, osum,
+  KB_LAUNCH(ce_stats_kernel, grid_for(rows, 1, 148 * 4), CE_THREADS, 0, st, (const __nv_bfloat16*)logits, targets, omax, osum,
                                                                       otgt, rows, V, vocab_start);
   KB_CHECK_LAUNCH();
 }
 extern "C" int kb_ce_grad(void* logits, const long* targets, const float* gmax, const float* gsum, const float* scale,
                           long rows, int V, long vocab_start, cudaStream_t st) {
-  ce_grad_kernel<<<grid_for(rows, 1, 148 * 4), CE_THREADS, 0, st>>>((__nv_bfloat16*)logits, targets, gmax, gsum, scale,
+  KB_LAUNCH(ce_grad_kernel, grid_for(rows, 1, 148 * 4), CE_THREADS, 0, st, (__nv_bfloat16*)logits, targets, gmax, gsum, scale,
                                                                      rows, V, vocab_start);
   KB_CHECK_LAUNCH();
 }
 extern "C" int kb_adamw(void* p, const float* g, float* m, float* v, float* master, long n, float lr, float b1,
                         float b2, float eps, float wd, float bc1, float bc2, const float* grad_scale_ptr,
                         float grad_scale, cudaStream_t st) {
-  adamw_kernel<<<grid_for(n / 4 + 1, 256, 148 * 16), 256, 0, st>>>((__nv_bfloat16*)p, g, m, v, master, n, lr, b1, b2,
+  KB_LAUNCH(adamw_kernel, grid_for(n / 4 + 1, 256, 148 * 16), 256, 0, st, (__nv_bfloat16*)p, g, m, v, master, n, lr, b1, b2,
                                                                     eps, wd, bc1, bc2, grad_scale_ptr, grad_scale);
   KB_CHECK_LAUNCH();
 }
 extern "C" int kb_sumsq(const void* x, long n, int is_f32, float* out, cudaStream_t st) {
-  if (is_f32) sumsq_f32_kernel<<<grid_for(n / 4 + 1, 256, 148 * 8), 256, 0, st>>>((const float*)x, n, out);
-  else sumsq_bf16_kernel<<<grid_for(n, 256, 148 * 8), 256, 0, st>>>((const __nv_bfloat16*)x, n, out);
+  if (is_f32) KB_LAUNCH(sumsq_f32_kernel, grid_for(n / 4 + 1, 256, 148 * 8), 256, 0, st, (const float*)x, n, out);
+  else KB_LAUNCH(sumsq_bf16_kernel, grid_for(n, 256, 148 * 8), 256, 0, st, (const __nv_bfloat16*)x, n, out);
   KB_CHECK_LAUNCH();
 }
 
@@ -698,8 +707,8 @@ extern "C" int kb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const float
   }
   float* partial = g_rmsnorm_bwd_partial_addr[dev];
   const int grid = rows < NOALLOC_MAX_CTAS ? rows : NOALLOC_MAX_CTAS;
-  rmsnorm_bwd_kernel<<<grid, NORM_THREADS, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, rstd,
+  KB_LAUNCH(rmsnorm_bwd_kernel, grid, NORM_THREADS, 0, st, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, rstd,
                                                     (const __nv_bfloat16*)w, (__nv_bfloat16*)dx, partial, rows, H);
-  rmsnorm_dw_reduce_kernel<<<(H + 255) / 256, 256, 0, st>>>(partial, dw, grid, H);
+  KB_LAUNCH(rmsnorm_dw_reduce_kernel, (H + 255) / 256, 256, 0, st, partial, dw, grid, H, 0);
   KB_CHECK_LAUNCH();
 }

@@ -24,6 +24,7 @@
 // or preceded by an all-reduce kernel (kareus/megatron/core/extensions/ops/te_linear.py:303-445,
 // 3rdparty/mscclpp/python/mscclpp_benchmark/allreduce.cu:155-246).
 #include "sm100.cuh"
+#include "launch.h"
 #include "peer.cuh"
 #include "host_utils.h"
 #include <stdlib.h>
@@ -452,7 +453,8 @@ static int launch_fused(const void* A, const void* W, const FusedParams& p, int 
     configured = true;
   }
   const int grid = p.n_first + p.n_gemm + p.n_last;
-  kern<<<grid, FG_THREADS, smem, stream>>>(tmA, tmB, p, M, N, K);
+  KB_LAUNCH_EPOCH(kern, grid, FG_THREADS, smem, stream,
+                  (EpochLoc{2, static_cast<int>(offsetof(FusedParams, epoch)), 4}), tmA, tmB, p, M, N, K);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 2000 + (int)e;
 }

@@ -7,6 +7,7 @@
 // loop; with K >= 1024 that costs a few percent and the traffic saving wins.  Used for large
 // problems (kb_gemm_bf16 picks it); same operand layouts as gemm_sm100.cu.
 #include "sm100.cuh"
+#include "launch.h"
 #include "host_utils.h"
 
 namespace kb {
@@ -277,7 +278,7 @@ static int launch256(const void* A, const void* B, void* C, int M, int N, int K,
   int group_m = (int)((40L << 20) / (panel > 0 ? panel : 1));
   if (group_m < 2) group_m = 2;
   if (group_m > tiles_m) group_m = tiles_m;
-  kern<<<grid, G2_THREADS, G2_SMEM, stream>>>(tmA, tmB, C, M, N, K, ldc, group_m, status);
+  KB_LAUNCH(kern, grid, G2_THREADS, G2_SMEM, stream, tmA, tmB, C, M, N, K, ldc, group_m, status);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 2000 + static_cast<int>(e);
 }

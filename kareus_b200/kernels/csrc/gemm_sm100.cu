@@ -12,6 +12,7 @@
 // (3rdparty/TransformerEngine/transformer_engine/common/gemm/cublaslt_gemm.cu; layouts TN/NN/NT
 // at kareus/transformer_engine/pytorch/ops/basic/basic_linear.py:572-582,848-859,899-909).
 #include "sm100.cuh"
+#include "launch.h"
 #include "host_utils.h"
 #include <stdlib.h>
 
@@ -311,7 +312,7 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
   int group_m = (int)((40L << 20) / (panel > 0 ? panel : 1));
   if (group_m < 4) group_m = 4;
   if (group_m > tiles_m) group_m = tiles_m;
-  kern<<<grid, GEMM_THREADS, smem, stream>>>(tmA, tmB, C, M, N, K, ldc, group_m, status);
+  KB_LAUNCH(kern, grid, GEMM_THREADS, smem, stream, tmA, tmB, C, M, N, K, ldc, group_m, status);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 2000 + static_cast<int>(e);
 }

@@ -3,6 +3,7 @@
 // kernels cover the reference's LayerNorm option and bias-carrying linear layers
 // (kareus/megatron/core/extensions/ops/te_norm.py, kareus/transformer_engine/pytorch/ops/basic/bias.py).
 #include <cuda_bf16.h>
+#include "launch.h"
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -133,7 +134,7 @@ using namespace kb;
 extern "C" int kb_layernorm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, int rows,
                                 int H, float eps, cudaStream_t st) {
   const int grid = rows < 148 * 8 ? rows : 148 * 8;
-  layernorm_fwd_kernel<<<grid, LN_THREADS, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
+  KB_LAUNCH(layernorm_fwd_kernel, grid, LN_THREADS, 0, st, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
                                                     (const __nv_bfloat16*)b, (__nv_bfloat16*)y, mean, rstd, rows, H, eps);
   LN_RET();
 }
@@ -144,20 +145,20 @@ extern "C" long kb_layernorm_bwd_scratch_elems(int rows, int H) {
 extern "C" int kb_layernorm_bwd(const void* dy, const void* x, const float* mean, const float* rstd, const void* w,
                                 void* dx, float* dw, float* db, float* scratch, int rows, int H, cudaStream_t st) {
   const int grid = rows < 148 * 2 ? rows : 148 * 2;
-  layernorm_bwd_kernel<<<grid, LN_THREADS, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, mean, rstd,
+  KB_LAUNCH(layernorm_bwd_kernel, grid, LN_THREADS, 0, st, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, mean, rstd,
                                                     (const __nv_bfloat16*)w, (__nv_bfloat16*)dx, scratch, rows, H);
-  ln_reduce_kernel<<<(H + 255) / 256, 256, 0, st>>>(scratch, dw, db, grid, H);
+  KB_LAUNCH(ln_reduce_kernel, (H + 255) / 256, 256, 0, st, scratch, dw, db, grid, H);
   LN_RET();
 }
 extern "C" int kb_bias_add(const void* x, const void* b, void* y, long rows, int H, cudaStream_t st) {
   long blocks = (rows * H + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  bias_add_kernel<<<(int)blocks, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)b, (__nv_bfloat16*)y, rows, H);
+  KB_LAUNCH(bias_add_kernel, (int)blocks, 256, 0, st, (const __nv_bfloat16*)x, (const __nv_bfloat16*)b, (__nv_bfloat16*)y, rows, H);
   LN_RET();
 }
 extern "C" int kb_colsum_accumulate(const void* dy, float* db, long rows, int H, cudaStream_t st) {
   const int rpb = 256;
   dim3 grid((H + 255) / 256, (unsigned)((rows + rpb - 1) / rpb));
-  colsum_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)dy, db, rows, H, rpb);
+  KB_LAUNCH(colsum_kernel, grid, 256, 0, st, (const __nv_bfloat16*)dy, db, rows, H, rpb);
   LN_RET();
 }

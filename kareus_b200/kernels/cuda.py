@@ -53,6 +53,7 @@ def _declare(L) -> None:
         "kb_gemm_bf16": [P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, P],
         "kb_rmsnorm_fwd": [P, P, P, P, I, I, F, P],
         "kb_rmsnorm_bwd": [P, P, P, P, P, P, P, I, I, P],
+        "kb_rmsnorm_bwd_acc": [P, P, P, P, P, P, P, I, I, I, P],
         "kb_rope": [P, LNG, LNG, LNG, LNG, I, I, P, LNG, LNG, LNG, I, P, P, I, I, I, I, P],
         "kb_swiglu_fwd": [P, P, LNG, I, P],
         "kb_swiglu_bwd": [P, P, P, LNG, I, P],
@@ -112,6 +113,12 @@ def _bf16(t: torch.Tensor) -> bool:
     return t.dtype == torch.bfloat16
 
 
+def _no_recording(what: str) -> None:
+    """Guard of wrapper paths that launch PyTorch kernels (invisible to a launch-list recording)."""
+    from . import replay
+    replay.require_recordable(what)
+
+
 # per-device status word that kernels with bounded waits write to
 _STATUS: Dict[int, torch.Tensor] = {}
 
@@ -146,7 +153,9 @@ def sm_count(device=None) -> int:
 def rmsnorm_fwd(x, w, eps):
     if not _bf16(x):
         return ref.rmsnorm_fwd(x, w, eps)
-    x = x.contiguous()
+    if not x.is_contiguous():
+        _no_recording("making a norm input contiguous")
+        x = x.contiguous()
     rows, H = x.shape
     y = torch.empty_like(x)
     rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
@@ -157,20 +166,34 @@ def rmsnorm_fwd(x, w, eps):
     return y, rstd
 
 
-def rmsnorm_bwd(dy, x, rstd, w):
+def rmsnorm_bwd(dy, x, rstd, w, dw_accum=None):
+    """Returns ``(dx, dw)``.  With ``dw_accum`` (contiguous fp32 ``[H]``, the weight's main gradient) the
+    weight gradient is added there by the kernel and ``dw`` is ``None``."""
     if not _bf16(x):
-        return ref.rmsnorm_bwd(dy, x, rstd, w)
-    dy = dy.contiguous()
+        dx, dw = ref.rmsnorm_bwd(dy, x, rstd, w)
+        if dw_accum is not None:
+            dw_accum.add_(dw.to(dw_accum.dtype))
+            dw = None
+        return dx, dw
+    if not dy.is_contiguous():
+        _no_recording("making a gradient contiguous")
+        dy = dy.contiguous()
     rows, H = x.shape
     dx = torch.empty_like(x)
-    dw = torch.empty(H, dtype=torch.float32, device=x.device)
+    acc = dw_accum is not None and dw_accum.dtype == torch.float32 and dw_accum.is_contiguous()
+    dw = dw_accum if acc else torch.empty(H, dtype=torch.float32, device=x.device)
     L = lib()
     n = L.kb_rmsnorm_bwd_scratch_elems(rows, H)
     scratch = torch.empty(max(n, 1), dtype=torch.float32, device=x.device)
     wb = w if _bf16(w) else w.to(torch.bfloat16)
-    _check(L.kb_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), rstd.data_ptr(), wb.data_ptr(), dx.data_ptr(), dw.data_ptr(),
-                            scratch.data_ptr(), rows, H, _stream()), "rmsnorm_bwd")
+    _check(L.kb_rmsnorm_bwd_acc(dy.data_ptr(), x.data_ptr(), rstd.data_ptr(), wb.data_ptr(), dx.data_ptr(),
+                                dw.data_ptr(), scratch.data_ptr(), rows, H, 1 if acc else 0, _stream()), "rmsnorm_bwd")
     _count(2)
+    if acc:
+        return dx, None
+    if dw_accum is not None:
+        dw_accum.add_(dw.to(dw_accum.dtype))
+        return dx, None
     return dx, dw
 
 
@@ -221,7 +244,9 @@ def rope_inplace(q, k, freqs, inverse=False):
 def swiglu_fwd(x):
     if not _bf16(x):
         return ref.swiglu_fwd(x)
-    x = x.contiguous()
+    if not x.is_contiguous():
+        _no_recording("making a SwiGLU input contiguous")
+        x = x.contiguous()
     rows, F2 = x.shape
     y = torch.empty(rows, F2 // 2, dtype=x.dtype, device=x.device)
     _check(lib().kb_swiglu_fwd(x.data_ptr(), y.data_ptr(), rows, F2 // 2, _stream()), "swiglu_fwd")
@@ -232,7 +257,9 @@ def swiglu_fwd(x):
 def swiglu_bwd(dy, x):
     if not _bf16(x):
         return ref.swiglu_bwd(dy, x)
-    dy = dy.contiguous()
+    if not dy.is_contiguous():
+        _no_recording("making a SwiGLU gradient contiguous")
+        dy = dy.contiguous()
     rows, F2 = x.shape
     dx = torch.empty_like(x)
     _check(lib().kb_swiglu_bwd(dy.data_ptr(), x.data_ptr(), dx.data_ptr(), rows, F2 // 2, _stream()), "swiglu_bwd")
@@ -243,7 +270,9 @@ def swiglu_bwd(dy, x):
 def dropout_add_fwd(x, residual, p, seed):
     if not _bf16(x):
         return ref.dropout_add_fwd(x, residual, p, seed)
-    x, residual = x.contiguous(), residual.contiguous()
+    if not (x.is_contiguous() and residual.is_contiguous()):
+        _no_recording("making a dropout-add operand contiguous")
+        x, residual = x.contiguous(), residual.contiguous()
     y = torch.empty_like(x)
     _check(lib().kb_dropout_add_fwd(x.data_ptr(), residual.data_ptr(), y.data_ptr(), x.numel(), float(p),
                                     int(seed) & 0xFFFFFFFF, _stream()), "dropout_add_fwd")
@@ -265,9 +294,9 @@ def dropout_add_bwd(dy, p, seed):
 
 
 def add(a, b):
-    if not _bf16(a) or a.numel() % 8:
+    if not _bf16(a) or a.numel() % 8 or not (a.is_contiguous() and b.is_contiguous()):
+        _no_recording("an elementwise add outside the library")
         return a + b
-    a, b = a.contiguous(), b.contiguous()
     y = torch.empty_like(a)
     _check(lib().kb_add(a.data_ptr(), b.data_ptr(), y.data_ptr(), a.numel(), _stream()), "add")
     _count()
@@ -290,8 +319,10 @@ def gemm(a, b, trans_a=False, trans_b=True, out_dtype=None, accumulate=None, out
             return out
         return r
     if not _rowmajor_ok(a):
+        _no_recording("making a GEMM operand contiguous")
         a = a.contiguous()
     if not _rowmajor_ok(b):
+        _no_recording("making a GEMM operand contiguous")
         b = b.contiguous()
     if not (_rowmajor_ok(a) and _rowmajor_ok(b)):
         raise KernelError(f"gemm operands need 16-byte aligned rows: a{tuple(a.shape)} b{tuple(b.shape)}")
@@ -322,6 +353,7 @@ def gemm(a, b, trans_a=False, trans_b=True, out_dtype=None, accumulate=None, out
 
 def gemm_library(a, b, trans_a=False, trans_b=True, out_dtype=None, accumulate=None, out=None):
     """cuBLAS through torch: the A/B baseline, never the default."""
+    _no_recording("a cuBLAS GEMM")
     A = a.t() if trans_a else a
     B = b.t() if trans_b else b
     if accumulate is not None:
@@ -351,6 +383,7 @@ def _heads4(t):
 
 def attention_fwd_library(q, k, v, scale, causal=True, q_offset=0, kv_len=None):
     """flash-attention wheel (bshd views, no copies for the common strides)."""
+    _no_recording("the flash-attention wheel")
     from flash_attn.flash_attn_interface import _flash_attn_forward
     q4 = _heads4(q)
     sk = k.shape[0] if kv_len is None else kv_len
@@ -363,6 +396,7 @@ def attention_fwd_library(q, k, v, scale, causal=True, q_offset=0, kv_len=None):
 
 
 def attention_bwd_library(do, q, k, v, o, lse, scale, causal=True, q_offset=0, kv_len=None, out=None):
+    _no_recording("the flash-attention wheel")
     from flash_attn.flash_attn_interface import _flash_attn_backward
     q4 = _heads4(q)
     sk = k.shape[0] if kv_len is None else kv_len

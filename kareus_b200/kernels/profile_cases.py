@@ -6,6 +6,13 @@
 
 Each case touches more than the 126 MB L2 where DRAM figures matter but holds at most a few GB,
 and launches its kernel a handful of times so a ``--set full`` capture ends within minutes.
+
+Timing tables (CUDA events, no profiler; L2 flushed between launches):
+
+    python -m kareus_b200.kernels.profile_cases gemm_table      # model GEMM shapes at TP 1 and TP 8, vs cuBLAS
+    python -m kareus_b200.kernels.profile_cases attn_table      # flash attention forward/backward, vs the wheel
+    python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 \
+        -m kareus_b200.kernels.profile_cases fused                # the eight fused GEMM+collective kernels at TP N
 """
 from __future__ import annotations
 
@@ -14,9 +21,185 @@ import sys
 import torch
 
 
+def _timed(fn, flush, iters: int = 7, skip: int = 3) -> float:
+    """Median CUDA-event time in ms of ``fn()`` with the L2 flushed before every launch."""
+    times = []
+    for i in range(iters + skip):
+        flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda._sleep(2_000_000)          # the launch is enqueued while the GPU is still busy
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        if i >= skip:
+            times.append(a.elapsed_time(b))
+    times.sort()
+    return times[len(times) // 2]
+
+
+def gemm_table() -> None:
+    """Forward, dgrad and wgrad GEMMs of one Llama-3.2-3B layer and the LM head at TP 1 and TP 8 shapes:
+    this library's tcgen05 kernels vs cuBLAS (torch.matmul) on the same tensors."""
+    from . import cuda as KC
+    dev = "cuda"
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    M = 16384
+    rows = []
+    for tp in (1, 8):
+        shapes = {"qkv": (M, 5120 // tp, 3072), "proj": (M, 3072, 3072 // tp), "fc1": (M, 16384 // tp, 3072),
+                  "fc2": (M, 3072, 8192 // tp)}
+        if tp == 1:
+            shapes["head"] = (M, 128256, 3072)
+            shapes["square"] = (8192, 8192, 8192)
+        for name, (m, n, k) in shapes.items():
+            a = torch.randn(m, k, device=dev).bfloat16()
+            w = torch.randn(n, k, device=dev).bfloat16()
+            dy = torch.randn(m, n, device=dev).bfloat16()
+            acc = torch.zeros(n, k, device=dev)
+            flops = 2.0 * m * n * k
+            cases = {"fprop": (lambda: KC.gemm(a, w), lambda: torch.matmul(a, w.t())),
+                     "dgrad": (lambda: KC.gemm(dy, w, trans_b=False), lambda: torch.matmul(dy, w)),
+                     "wgrad": (lambda: KC.gemm(dy, a, trans_a=True, trans_b=False, accumulate=acc),
+                               lambda: torch.matmul(dy.t(), a))}
+            for kind, (ours, lib_) in cases.items():
+                t_o, t_l = _timed(ours, flush), _timed(lib_, flush)
+                rows.append((f"tp{tp} {name} {kind}", m, n, k, flops / t_o / 1e9, flops / t_l / 1e9))
+            del a, w, dy, acc
+    KC.check_status()
+    print("| GEMM | M | N | K | this library TFLOP/s | cuBLAS TFLOP/s |\n|---|---|---|---|---|---|")
+    for r in rows:
+        print(f"| {r[0]} | {r[1]} | {r[2]} | {r[3]} | {r[4]:.0f} | {r[5]:.0f} |")
+
+
+def attn_table() -> None:
+    """Causal GQA flash attention at the 3B shapes (per nanobatch of 4 sequences): TP 1 (24/8 heads) and
+    TP 8 (3/1 heads), forward and backward, vs the flash-attention wheel when it is installed."""
+    from . import attention_cuda, cuda as KC
+    dev = "cuda"
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    print("| case | this library ms | TFLOP/s | wheel ms | TFLOP/s |\n|---|---|---|---|---|")
+    for (s, b, g, rep) in [(4096, 4, 8, 3), (4096, 4, 1, 3), (16384, 1, 2, 3)]:
+        d = 128
+        packed = torch.randn(s, b, g, (rep + 2) * d, device=dev).bfloat16()
+        q = packed[..., : rep * d].unflatten(-1, (rep, d))
+        k = packed[..., rep * d:(rep + 1) * d]
+        v = packed[..., (rep + 1) * d:]
+        o, lse = attention_cuda.forward(q, k, v, d ** -0.5)
+        do = torch.randn_like(o)
+        fl_f = 4.0 * s * s * d * g * rep * b / 2
+        t_f = _timed(lambda: attention_cuda.forward(q, k, v, d ** -0.5), flush)
+        t_b = _timed(lambda: attention_cuda.backward(do, q, k, v, o, lse, d ** -0.5), flush)
+        try:
+            ol, lsel = KC.attention_fwd_library(q, k, v, d ** -0.5)
+            w_f = _timed(lambda: KC.attention_fwd_library(q, k, v, d ** -0.5), flush)
+            w_b = _timed(lambda: KC.attention_bwd_library(do, q, k, v, ol, lsel, d ** -0.5), flush)
+        except Exception:
+            w_f = w_b = float("nan")
+        tag = f"S{s} B{b} heads {g * rep}/{g}"
+        print(f"| fwd {tag} | {t_f:.3f} | {fl_f / t_f / 1e9:.0f} | {w_f:.3f} | {fl_f / w_f / 1e9:.0f} |")
+        print(f"| bwd {tag} | {t_b:.3f} | {2.5 * fl_f / t_b / 1e9:.0f} | {w_b:.3f} | {2.5 * fl_f / w_b / 1e9:.0f} |")
+    KC.check_status()
+
+
+def fused_table() -> None:
+    """The eight fused GEMM+collective kernels (QKV, FC1, out-proj, FC2 and their backward mirrors) at
+    the 3B layer shapes for TP = world size: time (CUDA events, max over ranks), GEMM TFLOP/s, NVLink
+    GB/s per direction and the fraction of max(FLOPs / measured GEMM peak, bytes / 770 GB/s)."""
+    import json
+    import os
+    from pathlib import Path
+    from types import SimpleNamespace
+    import torch.distributed as dist
+    from ..engine.context import OpContext
+    from ..ops.fused import FusedAGDgrad, FusedAGGemm, FusedDgradRS, FusedGemmRS
+    from ..parallel.mesh import init_distributed
+    from ..parallel.symm_heap import SymmetricHeap
+    from . import cuda as KC
+    rank, world, local = init_distributed(timeout_s=120)
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    heap = SymmetricHeap.create(dist.group.WORLD, dev, size_bytes=3 << 30)
+    peak = 1669.2e12
+    pk = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    if pk.exists():
+        peak = float(json.loads(pk.read_text()).get("bf16_tflops", 1669.2)) * 1e12
+    sm = int(os.environ.get("KAREUS_COMM_SM", "12" if world >= 4 else "16"))
+    M, H, F, HEADS, KV, D = 16384, 3072, 8192, 24, 8, 128
+    q_out, f_out = (HEADS + 2 * KV) * D // world, 2 * F // world
+    # name -> (in_features, out_features, class, kind of collective, is backward)
+    cases = [("qkv fwd: AG->GEMM", H, q_out, FusedAGGemm, "ag"), ("fc1 fwd: AG->GEMM", H, f_out, FusedAGGemm, "ag"),
+             ("proj fwd: GEMM->RS", HEADS * D // world, H, FusedGemmRS, "rs"),
+             ("fc2 fwd: GEMM->RS", F // world, H, FusedGemmRS, "rs"),
+             ("qkv bwd: dgrad->RS", H, q_out, FusedDgradRS, "rs"), ("fc1 bwd: dgrad->RS", H, f_out, FusedDgradRS, "rs"),
+             ("proj bwd: AG->dgrad", HEADS * D // world, H, FusedAGDgrad, "ag"),
+             ("fc2 bwd: AG->dgrad", F // world, H, FusedAGDgrad, "ag")]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    if rank == 0:
+        print(f"| kernel (TP{world}, M={M}, {sm} comm CTAs) | N | K | us | GEMM TFLOP/s | NVLink GB/s/dir | roofline us "
+              "(gemm, link) | fraction |\n|---|---|---|---|---|---|---|---|")
+    for name, k_in, n_out, cls, kind in cases:
+        w = (torch.randn(n_out, k_in, device=dev) * 0.02).bfloat16()
+        w.main_grad = torch.zeros(n_out, k_in, device=dev)
+        lin = SimpleNamespace(name="prof_" + name.split(":")[0].replace(" ", "_"), out_features=n_out,
+                              in_features=k_in, weight=w)
+        op = cls(lin, heap, sm)
+        bwd = cls in (FusedDgradRS, FusedAGDgrad)
+        # GEMM dims of the fused kernel itself (the backward's wgrad GEMM is a separate plain launch and is
+        # excluded by timing a variant without saved input)
+        red, out = (n_out, k_in) if bwd else (k_in, n_out)      # reduction dim, output features
+        rows_in = M // world if kind == "ag" else M
+        x = torch.randn(rows_in, 1, red, device=dev).bfloat16()
+
+        def call():
+            if not bwd:
+                ctx = OpContext()
+                ctx.requires_grad = False
+                op.run((x,), sm_num=sm, nb=0, ctx=ctx)
+            elif cls is FusedDgradRS:
+                op._gemm_rs(x.reshape(-1, red), w, out, True, sm, 0)
+            else:
+                op._ag_gemm(x.reshape(-1, red), w, out, True, sm, 0)
+
+        times = []
+        for i in range(9):
+            flush.zero_()
+            dist.barrier()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda._sleep(3_000_000)
+            a.record()
+            call()
+            b.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([a.elapsed_time(b)], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            if i >= 3:
+                times.append(t.item())
+        times.sort()
+        ms = times[len(times) // 2]
+        flops = 2.0 * M * out * red
+        link = (world - 1) / world * M * (red if kind == "ag" else out) * 2
+        t_gemm, t_link = flops / peak * 1e6, link / 770e9 * 1e6
+        if rank == 0:
+            print(f"| {name} | {out} | {red} | {ms * 1e3:.0f} | {flops / 1e9 / ms:.0f} | {link / 1e6 / ms:.0f} | "
+                  f"{t_gemm:.0f}, {t_link:.0f} | {max(t_gemm, t_link) / (ms * 1e3):.2f} |", flush=True)
+        del w, x
+    KC.check_status()
+    dist.barrier()
+    heap.close()
+    dist.destroy_process_group()
+
+
 def main(case: str, reps: int = 3) -> None:
     from . import cuda as KC
     dev = "cuda"
+    if case == "gemm_table":
+        return gemm_table()
+    if case == "attn_table":
+        return attn_table()
+    if case == "fused":
+        return fused_table()
     if case == "gemm":
         a = torch.randn(8192, 8192, device=dev).bfloat16()
         b = torch.randn(8192, 8192, device=dev).bfloat16()

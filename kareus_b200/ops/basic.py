@@ -82,8 +82,7 @@ class RMSNormOp(nn.Module, GraphOperator):
     def backward(self, ctx, dy):
         x2, rstd = ctx.saved_tensors
         shp = dy.shape
-        dx, dw = K.rmsnorm_bwd(dy.reshape(-1, shp[-1]), x2, rstd, self.weight)
-        accumulate_grad(self.weight, dw)
+        dx, _ = K.rmsnorm_bwd(dy.reshape(-1, shp[-1]), x2, rstd, self.weight, dw_accum=ensure_main_grad(self.weight))
         return (dx.reshape(shp),)
 
     def parameters_list(self):

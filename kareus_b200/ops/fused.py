@@ -22,6 +22,7 @@ import torch
 from .. import kernels as K
 from ..engine.graph import operator_uid
 from ..kernels import cuda as KC
+from ..kernels import replay as _replay
 from .basic import ensure_main_grad
 
 _DECLARED = False
@@ -58,18 +59,18 @@ def _wgrad(dy2, x, weight) -> None:
     """``main_grad += dy2ᵀ·x``.  With one side stream per nanobatch two nanobatches' wgrads of the same
     weight could overlap and lose updates, so they are funnelled through one ordered stream; the block
     engine makes the compute stream wait for it at the end of backward."""
-    from ..engine.program import _per_nb_streams, _shared_comm_stream
+    from ..engine.program import _per_nb_streams, _shared_comm_stream, record_stream, wait_stream
     acc = ensure_main_grad(weight)
     if not (_per_nb_streams() and dy2.is_cuda):
         K.gemm(dy2, x, trans_a=True, trans_b=False, accumulate=acc)
         return
     cur = torch.cuda.current_stream(dy2.device)
     ws = _shared_comm_stream(dy2.device, slot=0)
-    ws.wait_stream(cur)
+    wait_stream(ws, cur)
     with torch.cuda.stream(ws):
         K.gemm(dy2, x, trans_a=True, trans_b=False, accumulate=acc)
-    dy2.record_stream(ws)
-    x.record_stream(ws)
+    record_stream(dy2, ws)
+    record_stream(x, ws)
 
 
 class _FusedBase:
@@ -105,9 +106,9 @@ class _FusedBase:
         ch = heap.channel(f"{self.tag}/{nb}")
         off, _ = heap.buffer(ch, "xg", m * k * 2)
         xg = heap.view(off, (m, k), torch.bfloat16)
-        xg[rank * ms:(rank + 1) * ms].copy_(x2)
+        _replay.copy_(xg[rank * ms:(rank + 1) * ms], x2 if x2.is_contiguous() else x2.contiguous())
         ready = self._local_flags(("ready", nb), m // 128)
-        ch.epoch += 1
+        ch.bump()
         y = torch.empty(m, n_out, dtype=torch.bfloat16, device=x2.device)
         st = KC.status_word(x2.device)
         rc = _lib().kb_ag_gemm_bf16(heap._bases_arr, rank, world, ch.flag_off, off, w.data_ptr(), y.data_ptr(), m,
@@ -122,6 +123,7 @@ class _FusedBase:
         heap = self.heap
         world, rank = heap.world, heap.rank
         if not KC._rowmajor_ok(a2):
+            _replay.require_recordable("making a GEMM operand contiguous")
             a2 = a2.contiguous()
         m, k = a2.shape
         ms = m // world
@@ -133,7 +135,7 @@ class _FusedBase:
         stage_off, _ = heap.buffer(ch, "stage", m * n_out * 2)
         cnt_off, _ = heap.buffer(ch, "cnt", world * (ms // 128) * tiles_n * 4)
         go = self._local_flags(("go", nb), 1)
-        ch.epoch += 1
+        ch.bump()
         out = torch.empty(ms, n_out, dtype=torch.bfloat16, device=a2.device)
         st = KC.status_word(a2.device)
         rc = L.kb_gemm_rs_bf16(heap._bases_arr, rank, world, ch.flag_off, stage_off, cnt_off, a2.data_ptr(),
@@ -154,7 +156,7 @@ class FusedAGGemm(_FusedBase):
         lead = x.shape[:-1]
         y, xg = self._ag_gemm(x.reshape(-1, x.shape[-1]), lin.weight, lin.out_features, False, sm_num, nb)
         if ctx is not None and ctx.requires_grad:
-            ctx.save_for_backward(xg.clone())         # gathered input for the wgrad GEMM
+            ctx.save_for_backward(_replay.clone(xg))  # gathered input for the wgrad GEMM
         return (y.reshape((lead[0] * self.heap.world,) + tuple(lead[1:]) + (lin.out_features,)),)
 
 
@@ -198,9 +200,9 @@ class FusedAGDgrad(_FusedBase):
         if dyg.is_cuda:
             # `dyg` lives in this call site's heap buffer, which the site's next call overwrites: when
             # the weight-gradient GEMM was moved to the ordered stream, this stream must not run ahead
-            from ..engine.program import _per_nb_streams, _shared_comm_stream
+            from ..engine.program import _per_nb_streams, _shared_comm_stream, wait_stream
             if _per_nb_streams():
-                torch.cuda.current_stream(dyg.device).wait_stream(_shared_comm_stream(dyg.device, slot=0))
+                wait_stream(torch.cuda.current_stream(dyg.device), _shared_comm_stream(dyg.device, slot=0))
         ctx.clear()
         return (dx.reshape((lead[0] * self.heap.world,) + tuple(lead[1:]) + (lin.in_features,)),)
 

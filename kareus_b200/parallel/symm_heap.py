@@ -22,6 +22,7 @@ import torch
 import torch.distributed as dist
 
 from ..kernels import cuda as KC
+from ..kernels import replay as _replay
 
 MAX_PEERS = 8
 MAX_SIGNAL_CTAS = 64
@@ -38,10 +39,27 @@ class _Raw:
 
 
 class Channel:
+    """One call site's flag block and buffers.  ``epoch`` counts the calls made on the channel; it lives
+    in a ``c_uint64`` so that a launch-list replay (C++) can advance the same counter."""
+
     def __init__(self, index: int, flag_off: int):
         self.index, self.flag_off = index, flag_off
-        self.epoch = 0
+        self.counter = c_uint64(0)
         self.buffers: Dict[str, Tuple[int, int]] = {}     # name -> (offset, nbytes)
+
+    @property
+    def epoch(self) -> int:
+        return self.counter.value
+
+    @epoch.setter
+    def epoch(self, v: int) -> None:
+        self.counter.value = v
+
+    def bump(self) -> int:
+        """Advance the epoch for one more call and tell an open recording where it lives."""
+        self.counter.value += 1
+        _replay.next_epoch(self.counter)
+        return self.counter.value
 
 
 class SymmetricHeap:
@@ -151,7 +169,7 @@ class SymmetricHeap:
 
     def barrier(self, ch: Channel) -> None:
         """Stream-ordered barrier among the ranks (a one-CTA kernel on the current stream)."""
-        ch.epoch += 1
+        ch.bump()
         st = KC.status_word(self.device)
         KC._check(self.lib.kb_peer_barrier(self._bases_arr, self.rank, self.world, ch.flag_off, ch.epoch,
                                            st.data_ptr(), KC._stream()), "peer barrier")
@@ -192,8 +210,8 @@ class SymmetricHeap:
         off, _ = self.buffer(ch, "x", n * x.element_size())
         buf = self.view(off, x.shape, x.dtype)
         if x.data_ptr() != buf.data_ptr():
-            buf.copy_(x)
-        ch.epoch += 1
+            _replay.copy_(buf, x)
+        ch.bump()
         sm, blk = self._launch_shape(sm_num, block_size)
         st = KC.status_word(self.device)
         KC._check(self.lib.kb_allreduce(self._bases_arr, self.rank, self.world, ch.flag_off, off, n, ch.epoch, sm, blk,
@@ -218,15 +236,15 @@ class SymmetricHeap:
         shard = x.numel() * x.element_size()
         off, _ = self.buffer(ch, "x", shard * self.world)
         out = self.view(off, (x.shape[0] * self.world,) + tuple(x.shape[1:]), x.dtype)
-        out[self.rank * x.shape[0]:(self.rank + 1) * x.shape[0]].copy_(x)
-        ch.epoch += 1
+        _replay.copy_(out[self.rank * x.shape[0]:(self.rank + 1) * x.shape[0]], x)
+        ch.bump()
         sm, blk = self._launch_shape(sm_num, block_size)
         st = KC.status_word(self.device)
         KC._check(self.lib.kb_allgather(self._bases_arr, self.rank, self.world, ch.flag_off, off, shard, ch.epoch, sm,
                                         blk, st.data_ptr(), KC._stream()), "allgather")
         KC._count()
         # the buffer is reused by the next call of this site: callers that keep the result ask for a copy
-        return out.clone() if keep else out
+        return _replay.clone(out) if keep else out
 
     def reduce_scatter(self, x: torch.Tensor, nb: int = 0, sm_num=None, block_size=None, tag: str = "rs") -> torch.Tensor:
         self._require_bf16(x, "reduce_scatter")
@@ -235,9 +253,9 @@ class SymmetricHeap:
         off, _ = self.buffer(ch, "x", n * x.element_size())
         buf = self.view(off, x.shape, x.dtype)
         if x.data_ptr() != buf.data_ptr():
-            buf.copy_(x)
+            _replay.copy_(buf, x)
         out = torch.empty((x.shape[0] // self.world,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
-        ch.epoch += 1
+        ch.bump()
         sm, blk = self._launch_shape(sm_num, block_size)
         st = KC.status_word(self.device)
         KC._check(self.lib.kb_reducescatter(self._bases_arr, self.rank, self.world, ch.flag_off, off, n // self.world,

@@ -115,26 +115,35 @@ def test_model_modes(heap, rank, world, dev):
     from kareus_b200.parallel.mesh import Mesh
     from kareus_b200.train.trainer import Trainer, synthetic_batch
     from kareus_b200.kernels import cuda as KC
-    cfg = get_model_config("tiny128").replace(num_attention_heads=8, num_query_groups=4)
+    cfg = get_model_config("tiny128").replace(num_attention_heads=8, num_query_groups=max(4, world))
     tc = TrainConfig(micro_batch_size=4, global_batch_size=8, seq_len=512, warmup_steps=0, lr=1e-3)
     mesh = Mesh(tp=world)
     losses = {}
-    for tp_comm, backend in [("allreduce", "nccl"), ("allreduce", "kernel"), ("sp", "nccl"), ("sp", "kernel"),
-                             ("sp_fused", "kernel")]:
+    for tp_comm, backend, replay in [("allreduce", "nccl", True), ("allreduce", "kernel", True), ("sp", "nccl", True),
+                                     ("sp", "kernel", True), ("sp_fused", "kernel", False),
+                                     ("sp_fused", "kernel", True)]:
         par = ParallelConfig(tp=world, num_nanobatches=2, tp_comm=tp_comm, comm_backend=backend, recompute=True)
         try:
             tr = Trainer(cfg, par, tc, mesh=mesh, device=dev, heap=heap,
                          sync=os.environ.get("KAREUS_SYNC", "partition_end"))
         except NotImplementedError:
             continue
-        tr.model.decoder.engine.default_shape = (8, 1024)
+        eng = tr.model.decoder.engine
+        eng.default_shape = (8, 1024)
+        eng.replay = replay
         batch = synthetic_batch(cfg, tc, tr.num_microbatches, seed=7)
-        l = [tr.train_step(batch) for _ in range(3)]
+        l = [tr.train_step(batch) for _ in range(4)]
         torch.cuda.synchronize()
         KC.check_status()
-        losses[(tp_comm, backend)] = l
+        losses[(tp_comm, backend, replay)] = l
+        if tp_comm == "sp_fused":
+            # with launch lists on, the fused path must really have been replayed from C++; NCCL
+            # collectives can never be part of a list
+            assert (eng.replayed_regions > 0) == replay, (tp_comm, replay, eng.replayed_regions)
+        else:
+            assert eng.replayed_regions == 0
         del tr
-    base = losses[("allreduce", "nccl")]
+    base = losses[("allreduce", "nccl", True)]
     if rank == 0:
         print("losses:", {k: [round(x, 4) for x in v] for k, v in losses.items()}, flush=True)
     assert base[-1] < base[0]
@@ -150,14 +159,15 @@ def test_ring_attention(heap, rank, world, dev):
     from kareus_b200.train.trainer import Trainer, synthetic_batch
     from kareus_b200.kernels import cuda as KC
     cfg = get_model_config("tiny128")
-    tc = TrainConfig(micro_batch_size=2, global_batch_size=4, seq_len=1024, warmup_steps=0, lr=1e-3)
+    seq = max(1024, 256 * world)         # sequence chunks (2 per rank) of at least one 128-row tile
+    tc = TrainConfig(micro_batch_size=2, global_batch_size=4, seq_len=seq, warmup_steps=0, lr=1e-3)
     mesh = Mesh(cp=world)
     losses = {}
     for cp_comm in ("all_gather", "ring"):
         par = ParallelConfig(cp=world, num_nanobatches=2, recompute=True, cp_comm=cp_comm)
         tr = Trainer(cfg, par, tc, mesh=mesh, device=dev, heap_cp=heap if cp_comm == "ring" else None)
         batch = synthetic_batch(cfg, tc, tr.num_microbatches, seed=3, cp=world, cp_rank=mesh.cp_rank)
-        losses[cp_comm] = [tr.train_step(batch, loss_denominator=float(4 * 1024)) for _ in range(3)]
+        losses[cp_comm] = [tr.train_step(batch, loss_denominator=float(4 * seq)) for _ in range(3)]
         torch.cuda.synchronize()
         KC.check_status()
         del tr
@@ -166,42 +176,6 @@ def test_ring_attention(heap, rank, world, dev):
     for a, b in zip(losses["ring"], losses["all_gather"]):
         assert abs(a - b) < 0.05, losses
     assert losses["ring"][-1] < losses["ring"][0]
-
-
-def perf_fused(heap, rank, world, dev):
-    """CUDA-event timings (max over ranks) of the fused kernels on the 3B layer shapes for this TP size."""
-    from types import SimpleNamespace
-    from kareus_b200.engine.context import OpContext
-    from kareus_b200.ops.fused import FusedAGGemm, FusedGemmRS
-    M, H, F, HEADS, KV, D = 16384, 3072, 8192, 24, 8, 128
-    shapes = {"qkv": (H, (HEADS + 2 * KV) * D // world, "ag"), "fc1": (H, 2 * F // world, "ag"),
-              "proj": (HEADS * D // world, H, "rs"), "fc2": (F // world, H, "rs")}
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
-    for name, (k, n, kind) in shapes.items():
-        w = (torch.randn(n, k, device=dev) * 0.02).bfloat16()
-        lin = SimpleNamespace(name=f"perf_{name}", out_features=n, in_features=k, weight=w)
-        op = FusedAGGemm(lin, heap, 16) if kind == "ag" else FusedGemmRS(lin, heap, 16)
-        x = torch.randn(M // world if kind == "ag" else M, 1, k, device=dev).bfloat16()
-        ctx = OpContext(); ctx.requires_grad = False
-        times = []
-        for i in range(8):
-            flush.zero_()
-            dist.barrier(); torch.cuda.synchronize()
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            torch.cuda._sleep(3_000_000)      # keep the GPU busy while the host prepares the launch
-            a.record(); op.run((x,), sm_num=16, nb=0, ctx=ctx); b.record(); torch.cuda.synchronize()
-            t = torch.tensor([a.elapsed_time(b)], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            if i >= 3:
-                times.append(t.item())
-        times.sort()
-        ms = times[len(times) // 2]
-        flops = 2.0 * M * n * k
-        link_bytes = (world - 1) / world * M * (k if kind == "ag" else n) * 2
-        if rank == 0:
-            print(f"fused {kind}_{name} tp{world}: M={M} N={n} K={k}: {ms*1e3:.1f} us; gemm {flops/1e12/ (ms/1e3):.0f} TFLOP/s; "
-                  f"link {link_bytes/1e6:.0f} MB -> {link_bytes/1e9/(ms/1e3):.0f} GB/s per direction; "
-                  f"roofline max(gemm@1669TF {flops/1669e12*1e6:.0f} us, link@770GB/s {link_bytes/770e9*1e6:.0f} us)", flush=True)
 
 
 def main():
@@ -218,8 +192,6 @@ def main():
         test_fused_gemm_collectives(heap, rank, world, dev)
     if which in ("all", "ring"):
         test_ring_attention(heap, rank, world, dev)
-    if which == "perf":
-        perf_fused(heap, rank, world, dev)
     if which in ("all", "wait"):
         test_bounded_wait(heap, dev)
     if which in ("all", "model"):

@@ -17,7 +17,9 @@ def _rel(a, b):
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 512), (384, 640, 3072), (1000, 328, 200),
-                                   (4096, 3072, 1024), (130, 72, 136)])
+                                   (4096, 3072, 1024), (130, 72, 136),
+                                   # long-K problems with at least one 256x256 tile per SM: the 256x256 kernel
+                                   (4096, 4096, 4096), (4500, 4096, 2304)])
 @pytest.mark.parametrize("ta,tb", [(False, True), (False, False), (True, False), (True, True)])
 def test_gemm_layouts(M, N, K, ta, tb):
     KC = _K()

@@ -19,8 +19,13 @@ def _run(which, n):
     assert "multigpu worker ok" in r.stdout
 
 
+@pytest.mark.parametrize("world", [2, 4, 8])
 @pytest.mark.parametrize("which", ["collectives", "fused", "ring", "wait", "model"])
-def test_two_gpus(which):
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
-    _run(which, 2)
+def test_multi_gpu(which, world):
+    """Every case at 2, 4 and 8 ranks (own-row epilogue with up to 7 peers, rank-rotated tile order,
+    half-GPU co-residency of the fused kernels); a box with fewer GPUs skips the larger worlds."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    if which == "wait" and world > 2:
+        pytest.skip("the bounded-wait probe involves no peer; covered at 2 ranks")
+    _run(which, world)

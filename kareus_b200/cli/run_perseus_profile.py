@@ -30,10 +30,14 @@ def main(argv=None) -> int:
     ap.add_argument("--freqs", type=int, nargs="*", default=None)
     ap.add_argument("--clock-mode", default="advisory", choices=["advisory", "locked"])
     ap.add_argument("--out", default="perseus_profile.csv")
+    ap.add_argument("--route", default="windows", choices=["windows", "timers"],
+                    help="windows: one measurement window per instruction; timers: the reference's route - "
+                         "instruction timers + energy-counter poller files, integrated with a piecewise-linear model")
+    ap.add_argument("--timer-dir", default="perseus_timers", help="where the timers route writes <freq>/timers/*.csv")
     a = ap.parse_args(argv)
 
     import torch.distributed as dist
-    from ..compose.perseus import InstructionRecorder, write_frequency_profile
+    from ..compose.perseus import InstructionRecorder, profile_from_timer_files, write_frequency_profile
     from ..config import ParallelConfig, TrainConfig, get_freq_grid, get_model_config
     from ..energy import EnergyMonitor, FrequencyController
     from ..parallel.mesh import Mesh, init_distributed
@@ -54,6 +58,35 @@ def main(argv=None) -> int:
     monitor = EnergyMonitor([local] if cuda else [0], nvml=None if cuda else FakeNVML(1))
     ctl = FrequencyController(local, a.clock_mode, nvml=monitor.nvml)
     trainer = Trainer(cfg, par, tc, mesh=mesh, device=device)
+    if a.route == "timers":
+        from pathlib import Path
+        from ..energy.power import EnergyPoller
+        from ..utils.timers import Timers
+        for f in (a.freqs or get_freq_grid(a.gpu_type)):
+            ctl.set_frequency(f)
+            timers = Timers()
+            trainer._hooks = [timers]
+            poller = EnergyPoller(local if cuda else 0, period_s=0.005, nvml=monitor.nvml).start()
+            poller.sample()
+            for step in range(a.steps):
+                trainer.train_step(synthetic_batch(cfg, tc, trainer.num_microbatches, seed=step),
+                                   loss_denominator=float(a.gbs * a.seq))
+            poller.sample()
+            poller.stop()
+            d = Path(a.timer_dir) / str(f)
+            timers.export(d, rank, local)
+            poller.dump(d / "timers" / f"time-energy-{rank}-{local}.csv")
+        ctl.close()
+        if world > 1:
+            dist.barrier()
+        if rank == 0:
+            p = profile_from_timer_files(a.timer_dir, num_microbatches=trainer.num_microbatches,
+                                         prof_iters=a.steps - a.skip, warmup_iters=a.skip,
+                                         ranks_per_stage=a.tp, out=a.out)
+            print(f"profile written: {p}")
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
     samples = {}
     for f in (a.freqs or get_freq_grid(a.gpu_type)):
         ctl.set_frequency(f)

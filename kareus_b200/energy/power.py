@@ -98,7 +98,8 @@ class GpuStatsMonitor(_Sampler):
 
 
 class EnergyPoller(_Sampler):
-    """Polls the cumulative energy counter; CSV ``time,energy_mj``."""
+    """Polls the cumulative energy counter; ``dump`` writes ``time,energy`` (unix seconds, joules), the
+    ``timers/time-energy-<global rank>-<local rank>.csv`` file of the reference's energy poller."""
 
     def __init__(self, nvml_index: int = 0, period_s: float = 0.01, nvml=None):
         super().__init__(period_s)
@@ -113,6 +114,6 @@ class EnergyPoller(_Sampler):
         p = Path(path)
         p.parent.mkdir(parents=True, exist_ok=True)
         with p.open("w") as f:
-            f.write("time,energy_mj\n")
+            f.write("time,energy\n")
             for t, e in self.samples:
-                f.write(f"{t},{e}\n")
+                f.write(f"{t},{e / 1000.0}\n")

@@ -57,8 +57,10 @@ class Timers:
         p = d / f"instructions-{global_rank}-{local_rank}.csv"
         with p.open("w", newline="") as f:
             w = csv.writer(f)
-            w.writerow(["name", "start", "end", "elapsed"])
-            for name, recs in self.records.items():
-                for a, b in recs:
-                    w.writerow([name, a, b, b - a])
+            # columns of the reference's file (tests/perseus/generate_profile_csv.py:203-212 reads
+            # instruction, start, end in this order)
+            w.writerow(["instruction", "start", "end"])
+            rows = [(a, name, b) for name, recs in self.records.items() for a, b in recs]
+            for a, name, b in sorted(rows):
+                w.writerow([name, a, b])
         return p

@@ -49,6 +49,23 @@ def test_perseus_profile_and_frequency_only_plan(tmp_path, capsys):
     assert not list((tmp_path / "plans").glob("scheds_pipeline_*.py"))
 
 
+def test_perseus_profile_through_timer_and_poller_files(tmp_path):
+    """Same table through the reference's route: instruction timers + energy poller files per frequency."""
+    from kareus_b200.cli import run_perseus_profile
+    out = tmp_path / "perseus.csv"
+    rc = run_perseus_profile.main(["--model", "tiny", "--mbs", "2", "--gbs", "4", "--seq", "32", "--steps", "3",
+                                   "--skip", "1", "--freqs", "1500", "900", "--route", "timers",
+                                   "--timer-dir", str(tmp_path / "sweep"), "--out", str(out)])
+    assert rc == 0
+    assert (tmp_path / "sweep" / "900" / "timers" / "instructions-0-0.csv").read_text().startswith("instruction,start,end")
+    assert (tmp_path / "sweep" / "900" / "timers" / "time-energy-0-0.csv").read_text().startswith("time,energy")
+    rows = out.read_text().strip().splitlines()
+    assert rows[0] == "stage,instruction,frequency,time,energy" and len(rows) == 1 + 2 * 2
+    for r in rows[1:]:
+        st, inst, f, t, e = r.split(",")
+        assert float(t) > 0 and float(e) >= 0
+
+
 def test_run_kareus_end_to_end_cpu(tmp_path, capsys):
     """Synthetic partition profiles → compose → plan → train under the max-throughput plan."""
     import json

@@ -1,4 +1,5 @@
 """Composer arithmetic, Pareto filter, the time–cost solver and plan emission on synthetic profiles."""
+import csv
 import json
 import math
 import random
@@ -177,3 +178,44 @@ def test_compare_methods(tmp_path):
     assert dominates(ours, base)
     cmp = compare_frontiers(ours, base)
     assert cmp["iso_time_energy_reduction_pct"] > 0
+
+
+def test_frequency_profile_from_timer_and_poller_files(tmp_path):
+    """The reference's baseline route: a piecewise-linear curve through the energy poller's samples,
+    evaluated at the instruction timers' start/end stamps; stage time = max over its ranks, stage
+    energy = mean per rank; warm-up iterations skipped."""
+    from kareus_b200.compose.perseus import PiecewiseLinearEnergy, profile_from_timer_files
+    m = PiecewiseLinearEnergy([0.0, 1.0, 3.0], [0.0, 100.0, 500.0])
+    assert m(0.5) == 50.0 and m(2.0) == 300.0 and abs(m.between(0.5, 2.0) - 250.0) < 1e-12
+    with pytest.raises(ValueError):
+        m(3.5)
+    with pytest.raises(ValueError):
+        PiecewiseLinearEnergy([0.0, 1.0], [5.0, 4.0])
+    mb, warm, prof = 2, 1, 2
+    for node, ranks in (("node0", (0, 1)), ("node1", (2, 3))):           # 2 stages x 2 ranks
+        for freq, watts in ((1200, 400.0), (1500, 600.0)):
+            d = tmp_path / node / str(freq) / "timers"
+            d.mkdir(parents=True)
+            for r in ranks:
+                p_r = watts + 10.0 * r                                     # constant power per rank
+                (d / f"time-energy-{r}-{r % 2}.csv").write_text(
+                    "time,energy\n" + "\n".join(f"{t / 10.0},{p_r * t / 10.0}" for t in range(0, 400)))
+                rows, t = ["instruction,start,end"], 1.0
+                for it in range(warm + prof):
+                    for _ in range(mb):
+                        f_len = (0.9 if it < warm else 0.2 + 0.01 * r) * 1500.0 / freq
+                        rows.append(f"forward-compute,{t},{t + f_len}")
+                        t += f_len + 0.05
+                        rows.append(f"backward-compute,{t},{t + 2 * f_len}")
+                        t += 2 * f_len + 0.05
+                (d / f"instructions-{r}-{r % 2}.csv").write_text("\n".join(rows))
+    out = profile_from_timer_files(tmp_path, num_microbatches=mb, prof_iters=prof, warmup_iters=warm, ranks_per_stage=2)
+    got = {(int(r["stage"]), r["instruction"], int(r["frequency"])): (float(r["time"]), float(r["energy"]))
+           for r in csv.DictReader(out.open())}
+    assert len(got) == 2 * 2 * 2
+    t, e = got[(0, "forward", 1500)]
+    assert abs(t - 0.21) < 1e-9                                           # slower rank of stage 0 (rank 1)
+    assert abs(e - (600.0 * 0.20 + 610.0 * 0.21) / 2) < 1e-6             # mean per rank of P x dt
+    t, e = got[(1, "backward", 1200)]
+    assert abs(t - 2 * 0.23 * 1500 / 1200) < 1e-9
+    assert abs(e - (420.0 * 2 * 0.22 + 430.0 * 2 * 0.23) * 1500 / 1200 / 2) < 1e-6

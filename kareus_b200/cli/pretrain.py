@@ -50,6 +50,9 @@ def main(argv=None) -> int:
         argv2 += ["--pfo-url", extra.get("pfo_url") or sw.perseus_server_url]
     if sw.enable_power_monitor:
         argv2.append("--enable-power-monitor")
+    if sw.nsys_profile:
+        argv2 += ["--profile-start-step", str(sw.nsys_start_step), "--profile-end-step", str(sw.nsys_end_step),
+                  "--profile-ranks", *map(str, sw.nsys_ranks)]
     if sw.enable_megatron_timers:
         argv2.append("--enable-timers")
     return run_train.main(argv2)

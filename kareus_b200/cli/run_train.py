@@ -40,6 +40,10 @@ def main(argv=None) -> int:
     ap.add_argument("--enable-power-monitor", action="store_true")
     ap.add_argument("--enable-timers", action="store_true")
     ap.add_argument("--recompute-layers", type=int, default=4)
+    ap.add_argument("--profile-start-step", type=int, default=None,
+                    help="open the CUDA profiler capture range at this step (nsys --capture-range=cudaProfilerApi)")
+    ap.add_argument("--profile-end-step", type=int, default=None)
+    ap.add_argument("--profile-ranks", type=int, nargs="*", default=[0])
     ap.add_argument("--save", default=None, help="write a distributed checkpoint (model + optimizer) here at the end")
     ap.add_argument("--save-interval", type=int, default=0, help="also save every N steps")
     ap.add_argument("--load", default=None, help="resume from this distributed checkpoint (any TP x PP x DP layout)")
@@ -100,6 +104,10 @@ def main(argv=None) -> int:
     timers = Timers() if a.enable_timers else None
     if timers is not None:
         trainer._hooks.append(timers)
+    if a.profile_start_step is not None:
+        from ..utils.debug import ProfilerStepWindow
+        end = a.profile_end_step if a.profile_end_step is not None else a.profile_start_step
+        trainer._hooks.append(ProfilerStepWindow(a.profile_start_step, end, a.profile_ranks, rank))
     power = PowerMonitor(local).start() if (a.enable_power_monitor and cuda) else None
     first = 0
     if a.load:

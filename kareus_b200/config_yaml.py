@@ -6,7 +6,7 @@ The reference drives runs with ``tests/artifact/conf/*.yaml`` plus ``model.key=v
 keys this runtime uses onto ``ModelConfig`` / ``ParallelConfig`` / ``TrainConfig`` and the energy
 plane switches: ``enable_zeus_monitor, enable_power_monitor, enable_perseus_optimizer,
 enable_kareus_scheduler, kareus_scheduler_kwargs.solution_path, enable_megatron_timers, cp_comm_type,
-num_layers_in_first_pipeline_stage, sequence_parallel``.
+num_layers_in_first_pipeline_stage, sequence_parallel, nsys_profile.{enabled,start_step,end_step,ranks}``.
 """
 from __future__ import annotations
 
@@ -29,6 +29,10 @@ class RunSwitches:
     solution_path: Optional[str] = None
     perseus_server_url: Optional[str] = None
     max_steps: int = 30
+    nsys_profile: bool = False          # model.nsys_profile.{enabled,start_step,end_step,ranks}
+    nsys_start_step: int = 10
+    nsys_end_step: int = 10
+    nsys_ranks: Tuple[int, ...] = (0,)
 
 
 def _set_path(d: dict, dotted: str, value) -> None:
@@ -101,4 +105,10 @@ def load_run_config(path, overrides: Iterable[str] = (), world_size: Optional[in
                      kareus_debug=bool(m.get("kareus_debug", False)),
                      solution_path=(m.get("kareus_scheduler_kwargs") or {}).get("solution_path"),
                      perseus_server_url=m.get("perseus_server_url"), max_steps=int(tr.get("max_steps", 30)))
+    ns = m.get("nsys_profile") or {}
+    if ns:
+        sw.nsys_profile = bool(ns.get("enabled", False))
+        sw.nsys_start_step = int(ns.get("start_step", 10))
+        sw.nsys_end_step = int(ns.get("end_step", 10))
+        sw.nsys_ranks = tuple(int(r) for r in (ns.get("ranks") or [0]))
     return model, par, train, sw

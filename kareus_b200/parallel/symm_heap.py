@@ -38,6 +38,37 @@ class _Raw:
                                          "strides": None}
 
 
+GUARD_BYTES = 1024
+GUARD_PATTERN = 0xA5
+
+
+class GuardMap:
+    """Canary words between heap buffers (race / overrun detection).
+
+    Every buffer carved out of the heap is followed by ``GUARD_BYTES`` painted with a fixed pattern.
+    No kernel has a reason to write there, so a guard that changed means some kernel, on this GPU or
+    on a peer that maps this heap, wrote past the end of the buffer in front of it (or before the
+    start of the one behind it).  ``check`` names the damaged guards.  The reference has no such
+    check: its collective buffers are separate allocations and an overrun there is silent
+    (``kareus/msccl/msccl_comm.py:44-206``)."""
+
+    def __init__(self):
+        self.guards: List[Tuple[int, int, str]] = []     # (offset, nbytes, name of the buffer in front)
+
+    def add(self, off: int, nbytes: int, name: str) -> None:
+        self.guards.append((off, nbytes, name))
+
+    def paint(self, heap_bytes: torch.Tensor, off: int, nbytes: int) -> None:
+        heap_bytes[off:off + nbytes].fill_(GUARD_PATTERN)
+
+    def check(self, heap_bytes: torch.Tensor) -> List[str]:
+        """Names of the buffers whose trailing guard no longer holds the pattern (one device sync)."""
+        if not self.guards:
+            return []
+        bad = torch.stack([(heap_bytes[o:o + n] != GUARD_PATTERN).any() for o, n, _ in self.guards])
+        return [self.guards[i][2] for i in torch.nonzero(bad.cpu()).flatten().tolist()]
+
+
 class Channel:
     """One call site's flag block and buffers.  ``epoch`` counts the calls made on the channel; it lives
     in a ``c_uint64`` so that a launch-list replay (C++) can advance the same counter."""
@@ -92,6 +123,7 @@ class SymmetricHeap:
         self.local = torch.as_tensor(_Raw(self.local_ptr, self.size), device=self.device)
         self._flag_top = 0
         self._data_top = FLAG_REGION
+        self.guards = GuardMap()
         self.channels: Dict[str, Channel] = {}
         self._views: Dict[tuple, torch.Tensor] = {}
         self.closed = False
@@ -142,9 +174,13 @@ class SymmetricHeap:
         cur = ch.buffers.get(name)
         if cur is None or cur[1] < nbytes:
             off = (self._data_top + 1023) // 1024 * 1024
-            if off + nbytes > self.size:
+            end = (off + nbytes + 15) // 16 * 16
+            if end + GUARD_BYTES > self.size:
                 raise MemoryError(f"symmetric heap of {self.size >> 20} MiB is full (asked {nbytes >> 20} MiB for {name})")
-            self._data_top = off + nbytes
+            # canary words behind the buffer (see GuardMap); painted once, checked on demand
+            self.guards.paint(self.local, end, GUARD_BYTES)
+            self.guards.add(end, GUARD_BYTES, f"channel {ch.index} buffer {name!r} at {off}")
+            self._data_top = end + GUARD_BYTES
             ch.buffers[name] = (off, nbytes)
             cur = (off, nbytes)
         return cur[0], self.local[cur[0]:cur[0] + nbytes]
@@ -290,6 +326,14 @@ class SymmetricHeap:
                 table[(sm, blk)] = float(t.item())
         best = min(table, key=table.get)
         return best, table
+
+    def check_guards(self) -> None:
+        """Raise if any kernel wrote into the canary words between heap buffers (synchronises)."""
+        torch.cuda.synchronize(self.device)
+        bad = self.guards.check(self.local)
+        if bad:
+            raise KC.KernelError("symmetric heap: canary words overwritten behind " + "; ".join(bad[:4]) +
+                                 (f" (+{len(bad) - 4} more)" if len(bad) > 4 else ""))
 
     def wait_flag_probe(self, limit_ns: int = 200_000_000) -> None:
         """Launch a kernel that waits (bounded) on a flag nobody sets; the status word then holds the

@@ -87,6 +87,23 @@ def test_debug_and_timers(tmp_path):
     assert out.name == "instructions-3-1.csv" and "forward-compute" in out.read_text()
 
 
+def test_profiler_step_window():
+    from kareus_b200.utils.debug import ProfilerStepWindow
+    calls = []
+    w = ProfilerStepWindow(2, 3, ranks=(0, 4), rank=4, start_fn=lambda: calls.append("start"),
+                           stop_fn=lambda: calls.append("stop"))
+    for step in range(6):
+        w.on_step_begin()
+        w.on_instruction_begin("forward"); w.on_instruction_end("forward")
+        calls.append(("step", step, w.open))
+        w.on_step_end()
+    assert calls == [("step", 0, False), ("step", 1, False), "start", ("step", 2, True), ("step", 3, True), "stop",
+                     ("step", 4, False), ("step", 5, False)]
+    off = ProfilerStepWindow(0, 0, ranks=(0,), rank=1, start_fn=lambda: calls.append("x"))
+    off.on_step_begin(); off.on_step_end()
+    assert "x" not in calls
+
+
 def test_yaml_run_config(tmp_path):
     from kareus_b200.config_yaml import load_run_config
     (tmp_path / "c.yaml").write_text("""
@@ -114,6 +131,7 @@ model:
   kareus_scheduler_kwargs: {solution_path: null}
   activations_checkpoint_granularity: full
   sequence_parallel: false
+  nsys_profile: {enabled: true, start_step: 12, end_step: 14, ranks: [0, 8]}
   optim: {lr: 2e-4, weight_decay: 0.01, betas: [0.9, 0.98], sched: {warmup_steps: 500, min_lr: 2e-5}}
 """)
     model, par, train, sw = load_run_config(tmp_path / "c.yaml", ["model.enable_kareus_scheduler=True",
@@ -123,6 +141,7 @@ model:
     assert (par.tp, par.pp, par.dp, par.recompute, par.tp_comm) == (8, 2, 1, True, "allreduce")
     assert train.micro_batch_size == 4 and train.num_microbatches(1) == 16 and train.betas == (0.9, 0.98)
     assert sw.enable_zeus_monitor and sw.enable_kareus_scheduler and sw.solution_path == "/p/s.py"
+    assert (sw.nsys_profile, sw.nsys_start_step, sw.nsys_end_step, sw.nsys_ranks) == (True, 12, 14, (0, 8))
 
 
 def _ckpt_trainer(tp, dp):

@@ -174,3 +174,17 @@ def test_kernel_backend_is_bf16_only():
     assert not op._use_kernel(bf, None)                 # no launch shape: library call
     for dt in (torch.float32, torch.float64, torch.float16):
         assert not op._use_kernel(torch.zeros(1, dtype=dt).as_subclass(_CudaClaim), 8)
+
+
+def test_guard_words_between_heap_buffers_name_the_overrun():
+    from kareus_b200.parallel.symm_heap import GUARD_BYTES, GuardMap
+    heap = torch.zeros(16384, dtype=torch.uint8)
+    g = GuardMap()
+    for i, (off, n) in enumerate([(1024, 3000), (6144, 2048)]):
+        end = (off + n + 15) // 16 * 16
+        g.paint(heap, end, GUARD_BYTES)
+        g.add(end, GUARD_BYTES, f"buffer {i}")
+    heap[1024:1024 + 3000] = 7                      # writing inside a buffer is fine
+    assert g.check(heap) == []
+    heap[6144 + 2048 + 5] = 1                       # one byte past the end of buffer 1
+    assert g.check(heap) == ["buffer 1"]

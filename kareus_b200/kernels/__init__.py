@@ -164,6 +164,40 @@ def attention_bwd(do, q, k, v, o, lse, scale, causal=True, q_offset=0, kv_len=No
     return dq, dk, dv
 
 
+def attention_fwd_chunked(q, sources, table, chunk_rows, q_positions, scale, causal=True, peer=False):
+    """Attention over K/V stored as chunks in several buffers (``ref.attention_fwd_chunked`` states the
+    math).  On GPUs this is ONE launch of the native kernel, which fetches each chunk's tiles from its
+    buffer; with ``peer=True`` the buffers may be other GPUs' memory.  No library route exists."""
+    if is_cuda(q):
+        if library_baseline() or peer:
+            _peer_guard(q, "attention_fwd_chunked")
+        from . import attention_native
+        return attention_native.forward_chunked(q, sources, table, chunk_rows, q_positions, scale, causal)
+    if peer:
+        _peer_guard(q, "attention_fwd_chunked")
+    return ref.attention_fwd_chunked(q, sources, table, chunk_rows, q_positions, scale, causal)
+
+
+def attention_bwd_chunked(do, q, sources, table, chunk_rows, q_positions, o, lse, scale, dq, dkv, dk_row_base,
+                          dv_row_base, causal=True, peer=False):
+    """Backward of :func:`attention_fwd_chunked`.  dQ goes to the view ``dq``; dK and dV of the logical key
+    range go to the rows of ``dkv`` named by ``dk_row_base`` / ``dv_row_base`` (one entry per logical chunk)."""
+    if is_cuda(q):
+        if library_baseline() or peer:
+            _peer_guard(q, "attention_bwd_chunked")
+        from . import attention_bwd_native
+        return attention_bwd_native.backward_chunked(do, q, sources, table, chunk_rows, q_positions, o, lse, scale,
+                                                     dq, dkv, dk_row_base, dv_row_base, causal)
+    if peer:
+        _peer_guard(q, "attention_bwd_chunked")
+    g_q, g_k, g_v = ref.attention_bwd_chunked(do, q, sources, table, chunk_rows, q_positions, o, lse, scale, causal)
+    dq.copy_(g_q.reshape(dq.shape))
+    for c, (bk, bv) in enumerate(zip(dk_row_base, dv_row_base)):
+        dkv[bk:bk + chunk_rows].copy_(g_k[c * chunk_rows:(c + 1) * chunk_rows])
+        dkv[bv:bv + chunk_rows].copy_(g_v[c * chunk_rows:(c + 1) * chunk_rows])
+    return dq, dkv
+
+
 # ----------------------------------------------------------------------------- cross entropy
 def cross_entropy_local_stats(logits, targets, vocab_start):
     if is_cuda(logits):

@@ -78,3 +78,43 @@ def backward(do, q, k, v, o, lse, scale, causal=True, q_offset=0, kv_len=None, o
     if out is not None:
         return out
     return dq.reshape(q.shape), dk, dv
+
+
+def backward_chunked(do, q, sources, table, chunk_rows, q_positions, o, lse, scale, dq, dkv, dk_row_base, dv_row_base,
+                     causal=True):
+    """Backward of :func:`attention_native.forward_chunked`.  ``dq`` is a destination view with ``q``'s
+    geometry; ``dkv`` is ONE ``[rows, b, g, d]`` destination that receives dK and dV of the whole logical
+    key range, logical chunk ``c`` of dK starting at row ``dk_row_base[c]`` and of dV at ``dv_row_base[c]``."""
+    from .attention_native import _int_array, _ptr_array, check_chunked
+    sq, b, g, rep, d, qs = check_chunked(q, sources, table, chunk_rows, q_positions)
+    L = _lib()
+    if not getattr(L, "_chunked_bwd_declared", False):
+        P, I, LNG, F = c_void_p, c_int, c_long, c_float
+        L.kb_flash_attn_bwd_chunked.argtypes = ([P, LNG, LNG, LNG, LNG, P, P, I, I, LNG, LNG, LNG, LNG, LNG, LNG, P, P,
+                                                 I, I, I, P, P, P, P, P, LNG, LNG, LNG, LNG, P, LNG, LNG, LNG, P, P, P] +
+                                                [I] * 5 + [F, I, P, P])
+        L.kb_flash_attn_bwd_chunked.restype = c_int
+        L._chunked_bwd_declared = True
+    if not (_ok(dkv) and dkv.dim() == 4 and dkv.dtype == torch.bfloat16):
+        raise KC.KernelError("dkv must be a bf16 [rows, b, g, d] view with 16-byte aligned strides")
+    hq = g * rep
+    o4, do4 = o.reshape(sq, b, hq, d), do.reshape(sq, b, hq, d)
+    if not (o4.is_contiguous() and do4.is_contiguous()):
+        KC._no_recording("making attention outputs contiguous")
+        o4, do4 = o4.contiguous(), do4.contiguous()
+    k0, v0 = sources[0]
+    skv = len(table) * int(chunk_rows)
+    _, _, _, _, _, dqs = _geom5(dq, k0.shape[2])
+    work = torch.empty(L.kb_flash_attn_bwd_scratch_floats(sq, skv, b, g, rep, d), dtype=torch.float32, device=q.device)
+    st = KC.status_word(q.device)
+    rc = L.kb_flash_attn_bwd_chunked(
+        q.data_ptr(), *qs, _ptr_array([k for k, _ in sources]), _ptr_array([v for _, v in sources]), len(sources),
+        k0.shape[0], k0.stride(0), k0.stride(1), k0.stride(2), v0.stride(0), v0.stride(1), v0.stride(2),
+        _int_array([t[0] for t in table]), _int_array([t[1] for t in table]), len(table), int(chunk_rows),
+        sq // len(q_positions), _int_array(q_positions), o4.data_ptr(), do4.data_ptr(), lse.data_ptr(),
+        dq.data_ptr(), *dqs, dkv.data_ptr(), dkv.stride(0), dkv.stride(1), dkv.stride(2), _int_array(dk_row_base),
+        _int_array(dv_row_base), work.data_ptr(), sq, b, g, rep, d, float(scale), 1 if causal else 0, st.data_ptr(),
+        KC._stream())
+    KC._check(rc, "flash_attn_bwd_chunked")
+    KC._count(6)
+    return dq, dkv

@@ -80,6 +80,63 @@ def forward(q, k, v, scale, causal=True, q_offset=0, kv_len=None, strict=False):
     return out, lse
 
 
+def _ptr_array(tensors):
+    return (c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
+
+
+def _int_array(values):
+    return (c_int * len(values))(*[int(v) for v in values])
+
+
+def check_chunked(q, sources, table, chunk_rows, q_positions):
+    """Validate a chunked call (see ``ref.attention_fwd_chunked``); raises :class:`KernelError`.  These
+    calls may read other GPUs' memory, so there is no fallback of any kind."""
+    k0, v0 = sources[0]
+    kg = k0.shape[2]
+    sq, b, g, rep, d, qs = _q_geometry(q)
+    if q.dim() == 4:
+        rep, g = q.shape[2] // kg, kg
+        qs = (q.stride(0), q.stride(1), q.stride(2) * rep, q.stride(2))
+    why = unsupported_reason(d, g, kg, q, *[t for kv in sources for t in kv])
+    if why is None and q.dtype != torch.bfloat16:
+        why = f"dtype {q.dtype}"
+    if why is None and any(tuple(k.stride()) != tuple(k0.stride()) or tuple(v.stride()) != tuple(v0.stride())
+                           or k.shape != k0.shape for k, v in sources):
+        why = "K/V sources differ in shape or strides"
+    if why is None and (chunk_rows % 128 or sq % len(q_positions) or (sq // len(q_positions)) % 128):
+        why = "chunks must be multiples of 128 rows"
+    if why is not None:
+        raise KC.KernelError(f"chunked attention cannot run ({why}); its operands may be peer memory, so no "
+                             "library or PyTorch route exists")
+    return sq, b, g, rep, d, qs
+
+
+def forward_chunked(q, sources, table, chunk_rows, q_positions, scale, causal=True):
+    """One launch over K/V chunks that live in several buffers (other GPUs' heaps through their peer
+    mappings).  Returns ``(out [sq,b,h,d], lse [b,h,sq])``."""
+    sq, b, g, rep, d, qs = check_chunked(q, sources, table, chunk_rows, q_positions)
+    L = _lib()
+    if not getattr(L, "_chunked_declared", False):
+        P, I, LNG, F = c_void_p, c_int, c_long, c_float
+        L.kb_flash_attn_fwd_chunked.argtypes = [P, LNG, LNG, LNG, LNG, P, P, I, I, LNG, LNG, LNG, LNG, LNG, LNG, P, P, I,
+                                                I, I, P, P, P, I, I, I, I, I, F, I, P, P]
+        L.kb_flash_attn_fwd_chunked.restype = c_int
+        L._chunked_declared = True
+    k0, v0 = sources[0]
+    out = torch.empty(sq, b, g * rep, d, dtype=q.dtype, device=q.device)
+    lse = torch.empty(b, g * rep, sq, dtype=torch.float32, device=q.device)
+    st = KC.status_word(q.device)
+    rc = L.kb_flash_attn_fwd_chunked(
+        q.data_ptr(), *qs, _ptr_array([k for k, _ in sources]), _ptr_array([v for _, v in sources]), len(sources),
+        k0.shape[0], k0.stride(0), k0.stride(1), k0.stride(2), v0.stride(0), v0.stride(1), v0.stride(2),
+        _int_array([t[0] for t in table]), _int_array([t[1] for t in table]), len(table), int(chunk_rows),
+        sq // len(q_positions), _int_array(q_positions), out.data_ptr(), lse.data_ptr(), sq, b, g, rep, d,
+        float(scale), 1 if causal else 0, st.data_ptr(), KC._stream())
+    KC._check(rc, "flash_attn_fwd_chunked")
+    KC._count()
+    return out, lse
+
+
 def backward(do, q, k, v, o, lse, scale, causal=True, q_offset=0, kv_len=None, out=None, strict=False):
     from . import attention_bwd_native
     return attention_bwd_native.backward(do, q, k, v, o, lse, scale, causal, q_offset, kv_len, out, strict=strict)

@@ -13,11 +13,18 @@
 // are added to fp32 accumulators at the end (query heads of one KV group run in different CTAs).
 // A second kernel converts the fp32 accumulators into the packed bf16 gradient of the QKV GEMM.
 //
+// Chunked keys and queries (context parallelism, see attention_chunks.h): K/V tiles may come from
+// several source buffers (other GPUs' shards through their peer mappings, plain TMA loads), query
+// tiles carry per-chunk absolute positions, and the bf16 conversion can scatter dK/dV chunk by chunk
+// into the input buffer of a reduce-scatter.
+//
 // Replaces the FlashAttention-2 backward the reference calls through its wheel
 // (kareus/flash_attn/flash_attn_interface.py:147-199).
 #include "sm100.cuh"
 #include "launch.h"
 #include "host_utils.h"
+#include "attention_chunks.h"
+#include <string.h>
 
 namespace kb {
 
@@ -35,7 +42,15 @@ struct BwdParams {
   int sq, skv, b, hq, rep, q_offset, causal;
   float scale, scale_log2;
   int* status;
+  ChunkGeom geom;
 };
+
+// Can any query of tile `qt` see key tile starting at k0?  (Suffix rule per query chunk.)
+__device__ __forceinline__ bool q_tile_sees(const BwdParams& p, int qt, int k0) {
+  if (!p.causal) return true;
+  const int q0 = qt * FB_T;
+  return p.geom.q_offset_of(q0, p.q_offset) + q0 + FB_T - 1 >= k0;
+}
 
 struct FbSmem {
   static constexpr int K_OFF = 0, V_OFF = FB_TILE, Q_OFF = 2 * FB_TILE, DO_OFF = 3 * FB_TILE, P_OFF = 4 * FB_TILE,
@@ -52,9 +67,8 @@ __device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, 
 }
 
 __global__ void __launch_bounds__(FB_THREADS, 1)
-flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
-                      const BwdParams p) {
+flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ KvMaps kv,
+                      const __grid_constant__ CUtensorMap tmDO, const BwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FbSmem::BAR_OFF);
@@ -74,12 +88,8 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   const int g = head / p.rep, r = head % p.rep;
   const int k0 = kt * FB_T;
   const int n_q = (p.sq + FB_T - 1) / FB_T;
-  int m_start = 0;
-  if (p.causal) {
-    const int d0 = k0 - p.q_offset;
-    m_start = d0 > 0 ? d0 / FB_T : 0;
-  }
-  const int n_it = n_q > m_start ? n_q - m_start : 0;
+  int n_it = 0;                              // query tiles that see this key tile
+  for (int qt = 0; qt < n_q; ++qt) n_it += q_tile_sees(p, qt, k0) ? 1 : 0;
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
@@ -101,15 +111,20 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 
   if (warp == 0) {
     if (lane == 0 && n_it > 0) {
-      prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmDO);
+      int src, srow;
+      p.geom.locate(k0, src, srow);
+      prefetch_tmap(&tmQ); prefetch_tmap(&kv.k[src]); prefetch_tmap(&kv.v[src]); prefetch_tmap(&tmDO);
       mbar_expect_tx(kv_full, 2 * FB_TILE);
-      tma_load_4d(smem + FbSmem::K_OFF, &tmK, kv_full, 0, g, batch, k0);
-      tma_load_4d(smem + FbSmem::K_OFF + FB_CHUNK, &tmK, kv_full, 64, g, batch, k0);
-      tma_load_4d(smem + FbSmem::V_OFF, &tmV, kv_full, 0, g, batch, k0);
-      tma_load_4d(smem + FbSmem::V_OFF + FB_CHUNK, &tmV, kv_full, 64, g, batch, k0);
-      for (int it = 0; it < n_it; ++it) {
+      tma_load_4d(smem + FbSmem::K_OFF, &kv.k[src], kv_full, 0, g, batch, srow);
+      tma_load_4d(smem + FbSmem::K_OFF + FB_CHUNK, &kv.k[src], kv_full, 64, g, batch, srow);
+      tma_load_4d(smem + FbSmem::V_OFF, &kv.v[src], kv_full, 0, g, batch, srow);
+      tma_load_4d(smem + FbSmem::V_OFF + FB_CHUNK, &kv.v[src], kv_full, 64, g, batch, srow);
+      int it = 0;
+      for (int qt = 0; qt < n_q; ++qt) {
+        if (!q_tile_sees(p, qt, k0)) continue;
         if (!mbar_wait(qdo_empty, (it & 1u) ^ 1u, abort_flag, p.status, ST_TIMEOUT_EMPTY)) break;
-        const int q0 = (m_start + it) * FB_T;
+        ++it;
+        const int q0 = qt * FB_T;
         mbar_expect_tx(qdo_full, 2 * FB_TILE);
         tma_load_5d(smem + FbSmem::Q_OFF, &tmQ, qdo_full, 0, r, g, batch, q0);
         tma_load_5d(smem + FbSmem::Q_OFF + FB_CHUNK, &tmQ, qdo_full, 64, r, g, batch, q0);
@@ -165,18 +180,22 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const float lg2e = 1.4426950408889634f;
     bool ok = n_it > 0;
-    for (int it = 0; it < n_it && ok; ++it) {
+    int it = -1;
+    for (int qt = 0; qt < n_q && ok; ++qt) {
+      if (!q_tile_sees(p, qt, k0)) continue;
+      ++it;
       const uint32_t ph = it & 1u;
-      const int q0 = (m_start + it) * FB_T;
+      const int q0 = qt * FB_T;
+      const int q_off = p.geom.q_offset_of(q0, p.q_offset);
       const int qrow = q0 + row;
-      const int qpos = p.q_offset + qrow;
+      const int qpos = q_off + qrow;
       const bool valid = qrow < p.sq;
       const size_t stat = (static_cast<size_t>(batch) * p.hq + head) * p.sq + (valid ? qrow : 0);
       const float lse2 = valid ? p.lse[stat] * lg2e : 0.f;
       const float dlt = valid ? p.delta[stat] : 0.f;
       if (!mbar_wait(s_full, ph, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
-      const bool tile_mask = (p.causal && k0 + FB_T - 1 > p.q_offset + q0) || (k0 + FB_T > p.skv) || (q0 + FB_T > p.sq);
+      const bool tile_mask = (p.causal && k0 + FB_T - 1 > q_off + q0) || (k0 + FB_T > p.skv) || (q0 + FB_T > p.sq);
       uint8_t* p_row = smem + FbSmem::P_OFF + row * 128;
       uint8_t* ds_row = smem + FbSmem::DS_OFF + row * 128;
 #pragma unroll 1
@@ -340,15 +359,47 @@ extern "C" long kb_flash_attn_bwd_scratch_floats(int sq, int skv, int b, int g, 
   return (long)sq * b * g * rep * d + 2L * skv * b * g * d + (long)b * g * rep * sq;
 }
 
-// q: view [sq,b,g,rep,d]; k,v: views [skv,b,g,d]; o, dO: [sq,b,hq,d] contiguous; lse [b,hq,sq].
-// dq/dk/dv: destination views with the same geometry as q/k/v (strides in elements).
-extern "C" int kb_flash_attn_bwd(const void* q, long qs_s, long qs_b, long qs_g, long qs_r, const void* k, long ks_s,
-                                 long ks_b, long ks_g, const void* v, long vs_s, long vs_b, long vs_g, const void* o,
-                                 const void* dO, const float* lse, void* dq, long dqs_s, long dqs_b, long dqs_g,
-                                 long dqs_r, void* dk, long dks_s, long dks_b, long dks_g, void* dv, long dvs_s,
-                                 long dvs_b, long dvs_g, float* work, int sq, int skv, int b, int g, int rep, int d,
-                                 float scale, int causal, int q_offset, int* status, cudaStream_t stream) {
-  if (d != FB_T || sq <= 0 || skv <= 0) return ST_BAD_ARG;
+namespace kb {
+
+struct RowMap {
+  int chunk_rows;                    // 0: rows map to themselves
+  int base[MAX_KV_CHUNKS];
+};
+
+// fp32 accumulator [logical rows, b, g, d] → bf16 rows of a strided destination where logical chunk c
+// starts at destination row map.base[c] (dK/dV straight into the layout a reduce-scatter expects)
+__global__ void attn_convert_chunked_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ out, long n_vec,
+                                            int B, int G, long st_s, long st_b, long st_g, RowMap map) {
+  for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const int dv = static_cast<int>(i % (FB_T / 4));
+    long rest = i / (FB_T / 4);
+    const int gg = static_cast<int>(rest % G); rest /= G;
+    const int bb = static_cast<int>(rest % B);
+    long ss = rest / B;
+    if (map.chunk_rows > 0) {
+      const int c = static_cast<int>(ss / map.chunk_rows);
+      ss = map.base[c] + (ss - static_cast<long>(c) * map.chunk_rows);
+    }
+    const float4 v = reinterpret_cast<const float4*>(acc)[i];
+    __nv_bfloat16* o = out + ss * st_s + bb * st_b + gg * st_g + dv * 4;
+    uint2 w;
+    *reinterpret_cast<__nv_bfloat162*>(&w.x) = __floats2bfloat162_rn(v.x, v.y);
+    *reinterpret_cast<__nv_bfloat162*>(&w.y) = __floats2bfloat162_rn(v.z, v.w);
+    *reinterpret_cast<uint2*>(o) = w;
+  }
+}
+
+struct BwdOut {
+  void* dq; long dqs_s, dqs_b, dqs_g, dqs_r;
+  void* dk; long dks_s, dks_b, dks_g;
+  void* dv; long dvs_s, dvs_b, dvs_g;
+  RowMap dk_rows, dv_rows;
+};
+
+static int launch_bwd(const CUtensorMap& tmQ, const KvMaps& kv, const ChunkGeom& geom, const void* o, const void* dO,
+                      const float* lse, const BwdOut& out, float* work, int sq, int skv, int b, int g, int rep, int d,
+                      float scale, int causal, int q_offset, int last_key, int* status, cudaStream_t stream) {
   const int hq = g * rep;
   const long n_dq = (long)sq * b * hq * d, n_dkv = (long)skv * b * g * d;
   float* dq_acc = work;
@@ -363,19 +414,14 @@ extern "C" int kb_flash_attn_bwd(const void* q, long qs_s, long qs_b, long qs_g,
     if (blocks > 148 * 16) blocks = 148 * 16;
     KB_LAUNCH(attn_delta_kernel, (int)blocks, 256, 0, stream, (const __nv_bfloat16*)dO, (const __nv_bfloat16*)o, delta, sq, b, hq);
   }
-  CUtensorMap tmQ, tmK, tmV, tmDO;
-  int rc = make_qkv_map(&tmQ, q, d, rep, g, b, sq, qs_r, qs_g, qs_b, qs_s, 1);
-  if (rc) return rc;
-  rc = make_qkv_map(&tmK, k, d, 1, g, b, skv, 0, ks_g, ks_b, ks_s, 0);
-  if (rc) return rc;
-  rc = make_qkv_map(&tmV, v, d, 1, g, b, skv, 0, vs_g, vs_b, vs_s, 0);
-  if (rc) return rc;
-  rc = make_qkv_map(&tmDO, dO, d, 1, hq, b, sq, 0, d, (long)hq * d, (long)b * hq * d, 0);
+  CUtensorMap tmDO;
+  int rc = make_qkv_map(&tmDO, dO, d, 1, hq, b, sq, 0, d, (long)hq * d, (long)b * hq * d, 0);
   if (rc) return rc;
   BwdParams p;
   p.lse = lse; p.delta = delta; p.dq_acc = dq_acc; p.dk_acc = dk_acc; p.dv_acc = dv_acc;
   p.sq = sq; p.skv = skv; p.b = b; p.hq = hq; p.rep = rep; p.q_offset = q_offset; p.causal = causal;
   p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
+  p.geom = geom;
   static bool configured = false;
   if (!configured) {
     e = cudaFuncSetAttribute(flash_attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FbSmem::TOTAL);
@@ -384,23 +430,102 @@ extern "C" int kb_flash_attn_bwd(const void* q, long qs_s, long qs_b, long qs_g,
   }
   int n_kv = (skv + FB_T - 1) / FB_T;
   if (causal) {
-    const int last = q_offset + sq;               // keys >= last are seen by no query
-    const int lim = (last + FB_T - 1) / FB_T;
+    const int lim = (last_key + FB_T - 1) / FB_T;      // keys >= last_key are seen by no query
     if (lim < n_kv) n_kv = lim > 0 ? lim : 0;
   }
   if (n_kv > 0) {
     dim3 grid(n_kv, hq, b);
-    KB_LAUNCH(flash_attn_bwd_kernel, grid, FB_THREADS, FbSmem::TOTAL, stream, tmQ, tmK, tmV, tmDO, p);
+    KB_LAUNCH(flash_attn_bwd_kernel, grid, FB_THREADS, FbSmem::TOTAL, stream, tmQ, kv, tmDO, p);
   }
-  auto conv = [&](const float* acc, void* out, long n, int G, int R, long s_s, long s_b, long s_g, long s_r) {
-    long nvec = n / 4;
+  {
+    long nvec = n_dq / 4;
     long blocks = (nvec + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
-    KB_LAUNCH(attn_convert_kernel, (int)blocks, 256, 0, stream, acc, (__nv_bfloat16*)out, nvec, b, G, R, s_s, s_b, s_g, s_r);
-  };
-  conv(dq_acc, dq, n_dq, g, rep, dqs_s, dqs_b, dqs_g, dqs_r);
-  conv(dk_acc, dk, n_dkv, g, 1, dks_s, dks_b, dks_g, 0);
-  conv(dv_acc, dv, n_dkv, g, 1, dvs_s, dvs_b, dvs_g, 0);
+    KB_LAUNCH(attn_convert_kernel, (int)blocks, 256, 0, stream, (const float*)dq_acc, (__nv_bfloat16*)out.dq, nvec, b, g, rep,
+              out.dqs_s, out.dqs_b, out.dqs_g, out.dqs_r);
+    nvec = n_dkv / 4;
+    blocks = (nvec + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    KB_LAUNCH(attn_convert_chunked_kernel, (int)blocks, 256, 0, stream, (const float*)dk_acc, (__nv_bfloat16*)out.dk, nvec, b,
+              g, out.dks_s, out.dks_b, out.dks_g, out.dk_rows);
+    KB_LAUNCH(attn_convert_chunked_kernel, (int)blocks, 256, 0, stream, (const float*)dv_acc, (__nv_bfloat16*)out.dv, nvec, b,
+              g, out.dvs_s, out.dvs_b, out.dvs_g, out.dv_rows);
+  }
   e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 2000 + (int)e;
+}
+
+}  // namespace kb
+
+// q: view [sq,b,g,rep,d]; k,v: views [skv,b,g,d]; o, dO: [sq,b,hq,d] contiguous; lse [b,hq,sq].
+// dq/dk/dv: destination views with the same geometry as q/k/v (strides in elements).
+extern "C" int kb_flash_attn_bwd(const void* q, long qs_s, long qs_b, long qs_g, long qs_r, const void* k, long ks_s,
+                                 long ks_b, long ks_g, const void* v, long vs_s, long vs_b, long vs_g, const void* o,
+                                 const void* dO, const float* lse, void* dq, long dqs_s, long dqs_b, long dqs_g,
+                                 long dqs_r, void* dk, long dks_s, long dks_b, long dks_g, void* dv, long dvs_s,
+                                 long dvs_b, long dvs_g, float* work, int sq, int skv, int b, int g, int rep, int d,
+                                 float scale, int causal, int q_offset, int* status, cudaStream_t stream) {
+  if (d != FB_T || sq <= 0 || skv <= 0) return ST_BAD_ARG;
+  CUtensorMap tmQ;
+  KvMaps kv;
+  memset(&kv, 0, sizeof(kv));
+  int rc = make_qkv_map(&tmQ, q, d, rep, g, b, sq, qs_r, qs_g, qs_b, qs_s, 1);
+  if (rc) return rc;
+  rc = make_qkv_map(&kv.k[0], k, d, 1, g, b, skv, 0, ks_g, ks_b, ks_s, 0);
+  if (rc) return rc;
+  rc = make_qkv_map(&kv.v[0], v, d, 1, g, b, skv, 0, vs_g, vs_b, vs_s, 0);
+  if (rc) return rc;
+  ChunkGeom geom;
+  memset(&geom, 0, sizeof(geom));
+  BwdOut out;
+  memset(&out, 0, sizeof(out));
+  out.dq = dq; out.dqs_s = dqs_s; out.dqs_b = dqs_b; out.dqs_g = dqs_g; out.dqs_r = dqs_r;
+  out.dk = dk; out.dks_s = dks_s; out.dks_b = dks_b; out.dks_g = dks_g;
+  out.dv = dv; out.dvs_s = dvs_s; out.dvs_b = dvs_b; out.dvs_g = dvs_g;
+  return launch_bwd(tmQ, kv, geom, o, dO, lse, out, work, sq, skv, b, g, rep, d, scale, causal, q_offset,
+                    q_offset + sq, status, stream);
+}
+
+// Chunked variant (see kb_flash_attn_fwd_chunked for the key/query chunk description).  dK and dV of the
+// whole logical key range go to ONE destination `dkv` ([rows, b, g, d] with the strides given): logical
+// chunk c of dK starts at row dk_row_base[c], of dV at dv_row_base[c] — e.g. the rank-ordered input
+// buffer of a reduce-scatter, so that nothing is copied between this kernel and the collective.
+extern "C" int kb_flash_attn_bwd_chunked(const void* q, long qs_s, long qs_b, long qs_g, long qs_r,
+                                         const void* const* k_ptrs, const void* const* v_ptrs, int n_src, int src_rows,
+                                         long ks_s, long ks_b, long ks_g, long vs_s, long vs_b, long vs_g,
+                                         const int* kv_src, const int* kv_row_base, int n_chunks, int chunk_rows,
+                                         int q_chunk_rows, const int* q_pos, const void* o, const void* dO,
+                                         const float* lse, void* dq, long dqs_s, long dqs_b, long dqs_g, long dqs_r,
+                                         void* dkv, long dkvs_s, long dkvs_b, long dkvs_g, const int* dk_row_base,
+                                         const int* dv_row_base, float* work, int sq, int b, int g, int rep, int d,
+                                         float scale, int causal, int* status, cudaStream_t stream) {
+  ChunkGeom geom;
+  int rc = fill_chunk_geom(&geom, n_src, kv_src, kv_row_base, n_chunks, chunk_rows, src_rows, q_chunk_rows, q_pos, sq);
+  if (rc || d != FB_T) return ST_BAD_ARG;
+  const int skv = n_chunks * chunk_rows;
+  CUtensorMap tmQ;
+  KvMaps kv;
+  memset(&kv, 0, sizeof(kv));
+  rc = make_qkv_map(&tmQ, q, d, rep, g, b, sq, qs_r, qs_g, qs_b, qs_s, 1);
+  if (rc) return rc;
+  for (int i = 0; i < n_src; ++i) {
+    rc = make_qkv_map(&kv.k[i], k_ptrs[i], d, 1, g, b, src_rows, 0, ks_g, ks_b, ks_s, 0);
+    if (rc) return rc;
+    rc = make_qkv_map(&kv.v[i], v_ptrs[i], d, 1, g, b, src_rows, 0, vs_g, vs_b, vs_s, 0);
+    if (rc) return rc;
+  }
+  BwdOut out;
+  memset(&out, 0, sizeof(out));
+  out.dq = dq; out.dqs_s = dqs_s; out.dqs_b = dqs_b; out.dqs_g = dqs_g; out.dqs_r = dqs_r;
+  out.dk = dkv; out.dks_s = dkvs_s; out.dks_b = dkvs_b; out.dks_g = dkvs_g;
+  out.dv = dkv; out.dvs_s = dkvs_s; out.dvs_b = dkvs_b; out.dvs_g = dkvs_g;
+  out.dk_rows.chunk_rows = out.dv_rows.chunk_rows = chunk_rows;
+  int last_key = 0;
+  for (int i = 0; i < sq / q_chunk_rows; ++i) last_key = q_pos[i] + q_chunk_rows > last_key ? q_pos[i] + q_chunk_rows : last_key;
+  for (int c = 0; c < n_chunks; ++c) {
+    out.dk_rows.base[c] = dk_row_base[c];
+    out.dv_rows.base[c] = dv_row_base[c];
+  }
+  return launch_bwd(tmQ, kv, geom, o, dO, lse, out, work, sq, skv, b, g, rep, d, scale, causal, 0, last_key, status,
+                    stream);
 }

@@ -10,6 +10,15 @@
 // exponent units overlap.  O stays in TMEM for the whole row tile; it is rescaled only when the
 // running maximum moves by more than 2^8 ("lazy rescale"), which happens on the first tiles only.
 //
+// Chunked keys (context parallelism without a gathered copy): the logical key sequence may be cut
+// into equal chunks that live in different buffers — each context-parallel rank's K/V shard inside
+// its own heap, reached through its peer mapping.  The producer picks the tensor map and the row
+// inside it from a small chunk table (`ChunkGeom`), everything else works on logical key positions,
+// so one launch covers what a ring of per-chunk launches plus log-sum-exp merges would compute
+// (3rdparty/TransformerEngine/.../context_parallel.py:94-162,676-712).  Query rows may likewise be
+// two chunks with their own absolute positions (dual-chunk causal load balance).  Remote tiles are
+// fetched with plain (non-multicast) TMA loads.
+//
 // Q, K and V are read through TMA from strided views of the packed QKV projection
 // ([s, b, groups, (rep+2)·d]), so no transpose or copy precedes the kernel (the reference
 // transposes sbhd→bshd and calls the FlashAttention-2 wheel:
@@ -17,6 +26,7 @@
 #include "sm100.cuh"
 #include "launch.h"
 #include "host_utils.h"
+#include <string.h>
 
 namespace kb {
 
@@ -39,6 +49,10 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
   return d;
 }
 
+}  // namespace kb
+#include "attention_chunks.h"
+namespace kb {
+
 struct FwdParams {
   __nv_bfloat16* out;   // [sq, b, hq, d] contiguous
   float* lse;           // [b, hq, sq]
@@ -47,6 +61,7 @@ struct FwdParams {
   float scale_log2;     // softmax scale * log2(e)
   int causal;
   int* status;
+  ChunkGeom geom;       // chunk tables (all zero: one K/V buffer, one query chunk at q_offset)
 };
 
 constexpr int FA_KSTAGES = 2;   // K tiles are released as soon as their S MMA retires
@@ -62,8 +77,8 @@ struct FaSmem {
 };
 
 __global__ void __launch_bounds__(FA_THREADS, 1)
-flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                      const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
+flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ KvMaps kv,
+                      const FwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FaSmem::BAR_OFF);
@@ -89,10 +104,12 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   const int batch = blockIdx.z;
   const int g = head / p.rep, r = head % p.rep;
   const int q0 = qt * FA_BM;
+  // absolute position of local query row x of this tile is q_off + x
+  const int q_off = p.geom.q_offset_of(q0, p.q_offset);
   // keys visible to this tile: [0, kv_end)
   int kv_end = p.skv;
   if (p.causal) {
-    const int last_q = p.q_offset + min(q0 + FA_BM, p.sq) - 1;
+    const int last_q = q_off + min(q0 + FA_BM, p.sq) - 1;
     kv_end = min(p.skv, last_q + 1);
   }
   const int n_kv = kv_end > 0 ? (kv_end + FA_BN - 1) / FA_BN : 0;
@@ -128,8 +145,8 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     // ------------------------------------------------------------------ producer
     if (lane == 0 && n_kv > 0) {
       prefetch_tmap(&tmQ);
-      prefetch_tmap(&tmK);
-      prefetch_tmap(&tmV);
+      prefetch_tmap(&kv.k[0]);
+      prefetch_tmap(&kv.v[0]);
       mbar_expect_tx(q_full, FA_TILE_BYTES);
       tma_load_5d(smem + FaSmem::Q_OFF, &tmQ, q_full, 0, r, g, batch, q0);
       tma_load_5d(smem + FaSmem::Q_OFF + FA_CHUNK, &tmQ, q_full, 64, r, g, batch, q0);
@@ -140,8 +157,10 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         if (!mbar_wait(&k_empty[s], ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_EMPTY)) { okp = false; return; }
         uint8_t* kd = smem + FaSmem::K_OFF + s * FA_TILE_BYTES;
         mbar_expect_tx(&k_full[s], FA_TILE_BYTES);
-        tma_load_4d(kd, &tmK, &k_full[s], 0, g, batch, j * FA_BN);
-        tma_load_4d(kd + FA_CHUNK, &tmK, &k_full[s], 64, g, batch, j * FA_BN);
+        int src, srow;
+        p.geom.locate(j * FA_BN, src, srow);
+        tma_load_4d(kd, &kv.k[src], &k_full[s], 0, g, batch, srow);
+        tma_load_4d(kd + FA_CHUNK, &kv.k[src], &k_full[s], 64, g, batch, srow);
       };
       load_k(0);
       // K runs one tile ahead of V: K(j+1) is requested before V(j)
@@ -153,8 +172,10 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         if (!mbar_wait(&v_empty[s], ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_EMPTY)) break;
         uint8_t* vd = smem + FaSmem::V_OFF + s * FA_TILE_BYTES;
         mbar_expect_tx(&v_full[s], FA_TILE_BYTES);
-        tma_load_4d(vd, &tmV, &v_full[s], 0, g, batch, j * FA_BN);
-        tma_load_4d(vd + FA_CHUNK, &tmV, &v_full[s], 64, g, batch, j * FA_BN);
+        int src, srow;
+        p.geom.locate(j * FA_BN, src, srow);
+        tma_load_4d(vd, &kv.v[src], &v_full[s], 0, g, batch, srow);
+        tma_load_4d(vd + FA_CHUNK, &kv.v[src], &v_full[s], 64, g, batch, srow);
       }
       if (*abort_flag) {
         const uint64_t t0 = globaltimer_ns();
@@ -225,7 +246,7 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     // needs few registers; packed f32x2 FMA/ADD halve the ALU work next to the exponentials.
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;           // row inside the tile = TMEM lane
-    const int qpos = p.q_offset + q0 + row;        // absolute position of this query
+    const int qpos = q_off + q0 + row;             // absolute position of this query
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     float m_ref = -INFINITY;   // reference maximum (scaled, log2 domain) used for the exponentials
     float l_sum = 0.f;
@@ -236,7 +257,7 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       tc_fence_after();
       const int key0 = j * FA_BN;
       // warp-uniform: does any row of this tile need masking?
-      const bool tile_mask = (p.causal && key0 + FA_BN - 1 > p.q_offset + q0) || (key0 + FA_BN > p.skv);
+      const bool tile_mask = (p.causal && key0 + FA_BN - 1 > q_off + q0) || (key0 + FA_BN > p.skv);
       const uint32_t s_addr = tmem_s + s * FA_BN + lane_addr;
       // ---- pass 1: row maximum of the raw scores
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -390,38 +411,29 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 
 }  // namespace kb
 
-// q: view [sq, b, g, rep, d] (strides in elements, d contiguous); k, v: views [skv, b, g, d];
-// out: [sq, b, g*rep, d] contiguous; lse: [b, g*rep, sq] fp32.
-extern "C" int kb_flash_attn_fwd(const void* q, long qs_s, long qs_b, long qs_g, long qs_r, const void* k, long ks_s,
-                                 long ks_b, long ks_g, const void* v, long vs_s, long vs_b, long vs_g, void* out,
-                                 float* lse, int sq, int skv, int b, int g, int rep, int d, float scale, int causal,
-                                 int q_offset, int* status, cudaStream_t stream) {
-  using namespace kb;
-  if (d != FA_D || sq <= 0 || skv <= 0) return ST_BAD_ARG;
-  CUtensorMap tmQ, tmK, tmV;
-  {
-    uint64_t dims[5] = {(uint64_t)d, (uint64_t)rep, (uint64_t)g, (uint64_t)b, (uint64_t)sq};
-    uint64_t str[4] = {(uint64_t)qs_r * 2, (uint64_t)qs_g * 2, (uint64_t)qs_b * 2, (uint64_t)qs_s * 2};
-    uint32_t box[5] = {64, 1, 1, 1, FA_BM};
-    // a size-1 dimension may carry any stride; TMA still wants it to be a multiple of 16 bytes
-    for (int i = 0; i < 4; ++i) if (str[i] == 0 || (str[i] & 15)) str[i] = (uint64_t)d * 2;
-    int rc = make_tmap(&tmQ, q, 2, 5, dims, str, box, 3);
-    if (rc) return rc;
-  }
-  {
-    uint64_t dims[4] = {(uint64_t)d, (uint64_t)g, (uint64_t)b, (uint64_t)skv};
-    uint32_t box[4] = {64, 1, 1, FA_BN};
-    uint64_t strk[3] = {(uint64_t)ks_g * 2, (uint64_t)ks_b * 2, (uint64_t)ks_s * 2};
-    uint64_t strv[3] = {(uint64_t)vs_g * 2, (uint64_t)vs_b * 2, (uint64_t)vs_s * 2};
-    for (int i = 0; i < 3; ++i) {
-      if (strk[i] == 0 || (strk[i] & 15)) strk[i] = (uint64_t)d * 2;
-      if (strv[i] == 0 || (strv[i] & 15)) strv[i] = (uint64_t)d * 2;
-    }
-    int rc = make_tmap(&tmK, k, 2, 4, dims, strk, box, 3);
-    if (rc) return rc;
-    rc = make_tmap(&tmV, v, 2, 4, dims, strv, box, 3);
-    if (rc) return rc;
-  }
+namespace kb {
+
+static int make_q_map(CUtensorMap* m, const void* q, int d, int rep, int g, int b, int sq, long qs_s, long qs_b,
+                      long qs_g, long qs_r) {
+  uint64_t dims[5] = {(uint64_t)d, (uint64_t)rep, (uint64_t)g, (uint64_t)b, (uint64_t)sq};
+  uint64_t str[4] = {(uint64_t)qs_r * 2, (uint64_t)qs_g * 2, (uint64_t)qs_b * 2, (uint64_t)qs_s * 2};
+  uint32_t box[5] = {64, 1, 1, 1, FA_BM};
+  // a size-1 dimension may carry any stride; TMA still wants it to be a multiple of 16 bytes
+  for (int i = 0; i < 4; ++i) if (str[i] == 0 || (str[i] & 15)) str[i] = (uint64_t)d * 2;
+  return make_tmap(m, q, 2, 5, dims, str, box, 3);
+}
+
+static int make_kv_map(CUtensorMap* m, const void* ptr, int d, int g, int b, int rows, long s_s, long s_b, long s_g) {
+  uint64_t dims[4] = {(uint64_t)d, (uint64_t)g, (uint64_t)b, (uint64_t)rows};
+  uint32_t box[4] = {64, 1, 1, FA_BN};
+  uint64_t str[3] = {(uint64_t)s_g * 2, (uint64_t)s_b * 2, (uint64_t)s_s * 2};
+  for (int i = 0; i < 3; ++i) if (str[i] == 0 || (str[i] & 15)) str[i] = (uint64_t)d * 2;
+  return make_tmap(m, ptr, 2, 4, dims, str, box, 3);
+}
+
+static int launch_fwd(const CUtensorMap& tmQ, const KvMaps& kv, const ChunkGeom& geom, void* out, float* lse, int sq,
+                      int skv, int b, int g, int rep, float scale, int causal, int q_offset, int* status,
+                      cudaStream_t stream) {
   FwdParams p;
   p.out = reinterpret_cast<__nv_bfloat16*>(out);
   p.lse = lse;
@@ -430,6 +442,7 @@ extern "C" int kb_flash_attn_fwd(const void* q, long qs_s, long qs_b, long qs_g,
   p.scale_log2 = scale * 1.4426950408889634f;
   p.causal = causal;
   p.status = status;
+  p.geom = geom;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(flash_attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -438,7 +451,60 @@ extern "C" int kb_flash_attn_fwd(const void* q, long qs_s, long qs_b, long qs_g,
     configured = true;
   }
   dim3 grid((sq + FA_BM - 1) / FA_BM, g * rep, b);
-  KB_LAUNCH(flash_attn_fwd_kernel, grid, FA_THREADS, FaSmem::TOTAL, stream, tmQ, tmK, tmV, p);
+  KB_LAUNCH(flash_attn_fwd_kernel, grid, FA_THREADS, FaSmem::TOTAL, stream, tmQ, kv, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 2000 + (int)e;
+}
+
+}  // namespace kb
+
+// q: view [sq, b, g, rep, d] (strides in elements, d contiguous); k, v: views [skv, b, g, d];
+// out: [sq, b, g*rep, d] contiguous; lse: [b, g*rep, sq] fp32.
+extern "C" int kb_flash_attn_fwd(const void* q, long qs_s, long qs_b, long qs_g, long qs_r, const void* k, long ks_s,
+                                 long ks_b, long ks_g, const void* v, long vs_s, long vs_b, long vs_g, void* out,
+                                 float* lse, int sq, int skv, int b, int g, int rep, int d, float scale, int causal,
+                                 int q_offset, int* status, cudaStream_t stream) {
+  using namespace kb;
+  if (d != FA_D || sq <= 0 || skv <= 0) return ST_BAD_ARG;
+  CUtensorMap tmQ;
+  KvMaps kv;
+  memset(&kv, 0, sizeof(kv));
+  int rc = make_q_map(&tmQ, q, d, rep, g, b, sq, qs_s, qs_b, qs_g, qs_r);
+  if (rc) return rc;
+  rc = make_kv_map(&kv.k[0], k, d, g, b, skv, ks_s, ks_b, ks_g);
+  if (rc) return rc;
+  rc = make_kv_map(&kv.v[0], v, d, g, b, skv, vs_s, vs_b, vs_g);
+  if (rc) return rc;
+  ChunkGeom geom;
+  memset(&geom, 0, sizeof(geom));
+  return launch_fwd(tmQ, kv, geom, out, lse, sq, skv, b, g, rep, scale, causal, q_offset, status, stream);
+}
+
+// Chunked variant.  The logical key sequence is `n_chunks` chunks of `chunk_rows` keys (a multiple of
+// 128); chunk c lives in source buffer kv_src[c] (0..n_src-1) starting at row kv_row_base[c].  Every
+// source is a [src_rows, b, g, d] view with the strides given (the same for all sources); k_ptrs and
+// v_ptrs hold their base addresses, which may be peer mappings of other GPUs' memory.  The local
+// queries are `sq / q_chunk_rows` chunks whose first rows sit at absolute positions q_pos[i].
+extern "C" int kb_flash_attn_fwd_chunked(const void* q, long qs_s, long qs_b, long qs_g, long qs_r,
+                                         const void* const* k_ptrs, const void* const* v_ptrs, int n_src, int src_rows,
+                                         long ks_s, long ks_b, long ks_g, long vs_s, long vs_b, long vs_g,
+                                         const int* kv_src, const int* kv_row_base, int n_chunks, int chunk_rows,
+                                         int q_chunk_rows, const int* q_pos, void* out, float* lse, int sq, int b, int g,
+                                         int rep, int d, float scale, int causal, int* status, cudaStream_t stream) {
+  using namespace kb;
+  ChunkGeom geom;
+  int rc = fill_chunk_geom(&geom, n_src, kv_src, kv_row_base, n_chunks, chunk_rows, src_rows, q_chunk_rows, q_pos, sq);
+  if (rc || d != FA_D) return ST_BAD_ARG;
+  CUtensorMap tmQ;
+  KvMaps kv;
+  memset(&kv, 0, sizeof(kv));
+  rc = make_q_map(&tmQ, q, d, rep, g, b, sq, qs_s, qs_b, qs_g, qs_r);
+  if (rc) return rc;
+  for (int i = 0; i < n_src; ++i) {
+    rc = make_kv_map(&kv.k[i], k_ptrs[i], d, g, b, src_rows, ks_s, ks_b, ks_g);
+    if (rc) return rc;
+    rc = make_kv_map(&kv.v[i], v_ptrs[i], d, g, b, src_rows, vs_s, vs_b, vs_g);
+    if (rc) return rc;
+  }
+  return launch_fwd(tmQ, kv, geom, out, lse, sq, n_chunks * chunk_rows, b, g, rep, scale, causal, 0, status, stream);
 }

@@ -207,6 +207,50 @@ def merge_attention(o1, lse1, o2, lse2):
     return o, lse
 
 
+def _logical_kv(sources, table, chunk_rows):
+    k = torch.cat([sources[src][0][base:base + chunk_rows] for src, base in table], dim=0)
+    v = torch.cat([sources[src][1][base:base + chunk_rows] for src, base in table], dim=0)
+    return k, v
+
+
+def attention_fwd_chunked(q, sources, table, chunk_rows: int, q_positions, scale: float, causal: bool = True):
+    """Attention over a logical key sequence that is stored as chunks of ``chunk_rows`` keys in several
+    buffers (``sources[i] = (k_i, v_i)``; logical chunk ``c`` is rows ``base .. base+chunk_rows`` of source
+    ``src`` with ``table[c] = (src, base)``).  The local queries are ``len(q_positions)`` equal chunks whose
+    first rows sit at those absolute positions.  Returns ``(out [sq,b,h,d], lse [b,h,sq])``."""
+    k, v = _logical_kv(sources, table, chunk_rows)
+    qc = q.shape[0] // len(q_positions)
+    outs, lses = [], []
+    for i, pos in enumerate(q_positions):
+        o, l = attention_fwd(q[i * qc:(i + 1) * qc], k, v, scale, causal, q_offset=pos,
+                             kv_len=min(k.shape[0], pos + qc) if causal else None)
+        outs.append(o)
+        lses.append(l)
+    return torch.cat(outs, dim=0), torch.cat(lses, dim=-1)
+
+
+def attention_bwd_chunked(do, q, sources, table, chunk_rows: int, q_positions, o, lse, scale: float,
+                          causal: bool = True):
+    """Gradients of :func:`attention_fwd_chunked`: ``(dq, dk, dv)`` with dk/dv over the LOGICAL key
+    sequence (``len(table) * chunk_rows`` rows)."""
+    k, v = _logical_kv(sources, table, chunk_rows)
+    qc = q.shape[0] // len(q_positions)
+    h = o.shape[-2]
+    do4 = do.reshape(q.shape[0], q.shape[1], h, -1)
+    acc = _acc(q)
+    dk = torch.zeros(k.shape, dtype=acc, device=k.device)
+    dv = torch.zeros(v.shape, dtype=acc, device=v.device)
+    dqs = []
+    for i, pos in enumerate(q_positions):
+        sl = slice(i * qc, (i + 1) * qc)
+        dq_i, dk_i, dv_i = attention_bwd(do4[sl], q[sl], k, v, o[sl], lse[..., sl], scale, causal, q_offset=pos,
+                                         kv_len=min(k.shape[0], pos + qc) if causal else None)
+        dqs.append(dq_i)
+        dk += dk_i.to(acc)
+        dv += dv_i.to(acc)
+    return torch.cat(dqs, dim=0), dk.to(k.dtype), dv.to(v.dtype)
+
+
 # ----------------------------------------------------------------------------- cross entropy
 def cross_entropy_local_stats(logits, targets, vocab_start: int):
     """Per-row ``(max, sum exp(x - max), target logit or 0)`` over this rank's vocab shard."""

@@ -176,6 +176,25 @@ class ReduceScatterKV(CollectiveBase):
     """CP reduce-scatter of full-length, sequence-ordered dK and dV."""
 
     group_name = "cp"
+    staging_kind = "rs"
+
+    def reduce_rows(self, x, nb=0, sm_num=16, block_size=1024):
+        """Plain dim-0 reduce-scatter of a tensor that is already in rank order (the chunked attention
+        backward writes dK|dV per rank straight into :meth:`staging`)."""
+        self.calls += 1
+        if self.world == 1:
+            return x
+        if self._use_kernel(x, sm_num):
+            return self.heap.reduce_scatter(x, nb=nb, sm_num=sm_num, block_size=block_size, tag=self.tag)
+        x = x.contiguous()
+        out = torch.empty((x.shape[0] // self.world,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        if x.is_cuda:
+            dist.reduce_scatter_tensor(out, x, group=self.group)
+        else:
+            dist.all_reduce(x, group=self.group)
+            n = out.shape[0]
+            out.copy_(x[self.rank * n:(self.rank + 1) * n])
+        return out
 
     def run(self, tensors, sm_num=None, block_size=None, backward=False, nb=0, ctx=None):
         dk, dv = tensors

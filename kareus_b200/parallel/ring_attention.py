@@ -1,19 +1,25 @@
 """Context-parallel attention without a materialised K/V all-gather.
 
-Every CP rank publishes its post-RoPE K and V shards in the symmetric heap; the flash-attention
-kernels then read the K/V tiles of *other* ranks' chunks straight out of peer memory with their own
-TMA loads (no multicast), chunk by chunk, and the partial results are merged with log-sum-exp
-algebra.  With dual-chunk causal load balance (rank r owns sequence chunks r and 2cp−1−r) a query
-chunk ``c`` attends to key chunks ``0..c``: all of them unmasked except the diagonal one.  This is the
-arithmetic of ring attention (``3rdparty/TransformerEngine/.../context_parallel.py:94-162,676-712``,
-unreachable in the reference, which all-gathers K/V instead: ``context_parallel.py:247-506``) with
-pulls over NVSwitch in place of a rotating ring.
+Every CP rank publishes its post-RoPE K and V shards in the symmetric heap; ONE flash-attention
+launch per direction then walks the whole visible key range and fetches the tiles of *other* ranks'
+chunks straight out of peer memory with its own TMA loads (no multicast), picking the buffer per
+chunk from a table (``csrc/attention_chunks.h``).  With dual-chunk causal load balance (rank r owns
+sequence chunks r and 2cp−1−r) the local queries are two chunks with their own absolute positions;
+the kernel carries the running maximum and sum across chunks, so nothing is merged afterwards.  This
+is the arithmetic of ring attention (``3rdparty/TransformerEngine/.../context_parallel.py:94-162,
+676-712``, unreachable in the reference, which all-gathers K/V instead:
+``context_parallel.py:247-506``) with pulls over NVSwitch in place of a rotating ring.
 
-Backward re-reads the peers' K/V the same way, accumulates dK/dV for every key chunk it touched and
-reduce-scatters them to their owners.
+Backward is again one launch: it re-reads the peers' K/V the same way, keeps dK/dV of every key chunk
+it touched in fp32 and converts them straight into the rank-ordered input buffer of a reduce-scatter
+(one all-pairs kernel over the heap) that returns each rank the sums for its own two chunks.
 
-Without a heap (CPU / gloo) the K/V shards are exchanged with ``all_gather`` and the same chunk
-schedule and merge run on the PyTorch statements, which is how the math is tested without GPUs.
+Per layer and direction: two peer barriers and two copies to publish K/V, one attention launch, and in
+backward one reduce-scatter — instead of one launch per (query chunk, key chunk) pair with eager
+merges in between.
+
+Without a heap (CPU / gloo) the K/V shards are exchanged with ``all_gather`` and the same chunk tables
+drive the PyTorch statement of the math, which is how the logic is tested without GPUs.
 """
 from __future__ import annotations
 
@@ -24,7 +30,6 @@ import torch
 import torch.distributed as dist
 
 from .. import kernels as K
-from ..kernels import ref
 from ..kernels.cuda import KernelError
 from .collectives import ReduceScatterKV, dual_chunk_ids
 
@@ -32,6 +37,11 @@ from .collectives import ReduceScatterKV, dual_chunk_ids
 def chunk_owner(j: int, cp: int) -> Tuple[int, int]:
     """(rank, half) holding sequence chunk ``j``."""
     return (j, 0) if j < cp else (2 * cp - 1 - j, 1)
+
+
+def chunk_table(cp: int, c: int) -> List[Tuple[int, int]]:
+    """Logical chunk → (source rank, first row in that rank's ``[2c, ...]`` shard)."""
+    return [(r, half * c) for r, half in (chunk_owner(j, cp) for j in range(2 * cp))]
 
 
 class RingAttention:
@@ -72,55 +82,40 @@ class RingAttention:
         be announced as such (``peer=True``), which pins it to this package's own kernels."""
         return self.heap is not None and k.is_cuda
 
-    def _kv_chunk(self, kv, j: int, c: int):
-        r, half = chunk_owner(j, self.cp)
-        return kv[r][0][half * c:(half + 1) * c], kv[r][1][half * c:(half + 1) * c]
+    def _q_positions(self, c: int) -> List[int]:
+        return [cid * c for cid in dual_chunk_ids(self.cp, self.rank)]
 
     # ------------------------------------------------------------------ forward / backward
     def forward(self, q, k, v, scale: float, nb: int = 0):
-        s = q.shape[0]
-        c = s // 2
+        """``q`` ``[2c, b, ...]`` (this rank's two chunks), ``k``/``v`` ``[2c, b, g, d]``.  Returns
+        ``(out [2c,b,h,d], lse [b,h,2c])``."""
+        c = q.shape[0] // 2
         kv = self._publish(k, v, nb, "fwd")
-        peer = self._peer(k)
-        outs, lses = [], []
-        for half, cid in enumerate(dual_chunk_ids(self.cp, self.rank)):
-            qc = q[half * c:(half + 1) * c]
-            o = lse = None
-            for j in range(cid + 1):
-                kj, vj = self._kv_chunk(kv, j, c)
-                oj, lj = K.attention_fwd(qc, kj, vj, scale, causal=(j == cid), peer=peer)
-                if o is None:
-                    o, lse = oj, lj
-                else:
-                    o, lse = ref.merge_attention(o, lse, oj, lj)
-            outs.append(o)
-            lses.append(lse)
-        return torch.cat(outs, dim=0), torch.stack(lses, dim=0)       # lse: [2, b, h, c]
+        return K.attention_fwd_chunked(q, kv, chunk_table(self.cp, c), c, self._q_positions(c), scale, causal=True,
+                                       peer=self._peer(k))
 
     def backward(self, do, q, k, v, out, lse, scale: float, out_grads=None, nb: int = 0):
-        s = q.shape[0]
-        c = s // 2
+        c = q.shape[0] // 2
+        cp = self.cp
         kv = self._publish(k, v, nb, "bwd")
-        peer = self._peer(k)
-        acc = torch.float64 if q.dtype == torch.float64 else torch.float32
-        dk_full = torch.zeros((2 * self.cp * c,) + tuple(k.shape[1:]), dtype=acc, device=k.device)
-        dv_full = torch.zeros_like(dk_full)
-        dqs = []
-        for half, cid in enumerate(dual_chunk_ids(self.cp, self.rank)):
-            sl = slice(half * c, (half + 1) * c)
-            dq = None
-            for j in range(cid + 1):
-                kj, vj = self._kv_chunk(kv, j, c)
-                dqj, dkj, dvj = K.attention_bwd(do[sl], q[sl], kj, vj, out[sl], lse[half], scale, causal=(j == cid),
-                                                peer=peer)
-                dq = dqj.to(acc) if dq is None else dq + dqj.to(acc)
-                dk_full[j * c:(j + 1) * c] += dkj.to(acc)
-                dv_full[j * c:(j + 1) * c] += dvj.to(acc)
-            dqs.append(dq.to(q.dtype))
-        dk, dv = self.rs.run((dk_full.to(k.dtype), dv_full.to(v.dtype)), sm_num=16, nb=nb)
-        dq = torch.cat(dqs, dim=0)
+        table = chunk_table(cp, c)
+        # dK and dV of all 2cp chunks in the layout the reduce-scatter shards by rank: rank r's block is
+        # [dK chunk r | dK chunk 2cp-1-r | dV chunk r | dV chunk 2cp-1-r]
+        rows = cp * 4 * c
+        shape = (rows,) + tuple(k.shape[1:])
+        dkv = None
+        if self._peer(k):
+            dkv = self.rs.staging(shape, k.dtype, nb, k.device)     # the collective's own input buffer
+        if dkv is None:
+            dkv = torch.empty(shape, dtype=k.dtype, device=k.device)
+        dk_base = [r * 4 * c + half * c for r, half in (chunk_owner(j, cp) for j in range(2 * cp))]
+        dv_base = [b + 2 * c for b in dk_base]
+        dq = out_grads[0] if out_grads is not None else torch.empty_like(q)
+        K.attention_bwd_chunked(do, q, kv, table, c, self._q_positions(c), out, lse, scale, dq, dkv, dk_base, dv_base,
+                                causal=True, peer=self._peer(k))
+        mine = self.rs.reduce_rows(dkv, nb=nb)                      # [4c, b, g, d]: this rank's dK | dV
+        dk, dv = mine[:2 * c], mine[2 * c:]
         if out_grads is not None:
-            out_grads[0].copy_(dq.reshape(out_grads[0].shape))
             out_grads[1].copy_(dk)
             out_grads[2].copy_(dv)
             return out_grads

@@ -291,3 +291,46 @@ def test_layernorm_and_bias_kernels():
         assert _rel(z, x.float() + 0.75) < 5e-3
         b.backward(OpContext(), g)
         assert _rel(b.bias.main_grad, g.float().sum(0)) < 1e-2
+
+
+@pytest.mark.parametrize("cp,c", [(2, 128), (2, 256), (4, 128)])
+def test_chunked_attention_matches_reference(cp, c):
+    """Context-parallel attention in one launch: K/V chunks in several buffers (here: local tensors that
+    stand for the ranks' shards), two query chunks with their own positions, dK/dV scattered per chunk
+    into a rank-ordered buffer.  Every rank's view is checked against the fp32 statement of the math."""
+    from kareus_b200.kernels import attention_bwd_native, attention_native, ref
+    from kareus_b200.parallel.ring_attention import chunk_owner, chunk_table
+    KC = _K()
+    b, g, rep, d = 2, 2, 3, 128
+    gen = torch.Generator(device="cuda").manual_seed(11 * cp + c)
+    packed = [torch.randn(2 * c, b, g, (rep + 2) * d, device="cuda", generator=gen).bfloat16() for _ in range(cp)]
+    qs = [p[..., : rep * d].unflatten(-1, (rep, d)) for p in packed]
+    sources = [(p[..., rep * d:(rep + 1) * d], p[..., (rep + 1) * d:]) for p in packed]
+    table = chunk_table(cp, c)
+    dk_base = [r * 4 * c + half * c for r, half in (chunk_owner(j, cp) for j in range(2 * cp))]
+    dv_base = [x + 2 * c for x in dk_base]
+    f32 = [(k.float(), v.float()) for k, v in sources]
+    for rank in range(cp):
+        q = qs[rank]
+        qpos = [rank * c, (2 * cp - 1 - rank) * c]
+        out, lse = attention_native.forward_chunked(q, sources, table, c, qpos, d ** -0.5)
+        KC.check_status()
+        want, lse_w = ref.attention_fwd_chunked(q.float(), f32, table, c, qpos, d ** -0.5)
+        assert _rel(out, want.reshape(out.shape)) < 2e-2, ("fwd", rank)
+        torch.testing.assert_close(lse, lse_w.reshape(lse.shape), rtol=1e-2, atol=2e-2)
+        do = torch.randn(out.shape, device="cuda", generator=gen).bfloat16()
+        dq = torch.empty_like(q)
+        dkv = torch.full((cp * 4 * c, b, g, d), float("nan"), device="cuda", dtype=torch.bfloat16)
+        attention_bwd_native.backward_chunked(do, q, sources, table, c, qpos, out, lse, d ** -0.5, dq, dkv, dk_base,
+                                              dv_base)
+        KC.check_status()
+        wq, wk, wv = ref.attention_bwd_chunked(do.float(), q.float(), f32, table, c, qpos, want, lse_w, d ** -0.5)
+        assert _rel(dq, wq.reshape(dq.shape)) < 3e-2, ("dq", rank)
+        assert not torch.isnan(dkv.float()).any()            # every row of the collective's input was written
+        for j in range(2 * cp):
+            assert _rel(dkv[dk_base[j]:dk_base[j] + c], wk[j * c:(j + 1) * c]) < 3e-2 or \
+                wk[j * c:(j + 1) * c].abs().max() == 0, ("dk", rank, j)
+            assert _rel(dkv[dv_base[j]:dv_base[j] + c], wv[j * c:(j + 1) * c]) < 3e-2 or \
+                wv[j * c:(j + 1) * c].abs().max() == 0, ("dv", rank, j)
+            if wk[j * c:(j + 1) * c].abs().max() == 0:      # chunk no local query can see: exact zeros
+                assert dkv[dk_base[j]:dk_base[j] + c].abs().max() == 0

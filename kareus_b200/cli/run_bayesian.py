@@ -48,7 +48,7 @@ def main(argv=None) -> int:
     from ..profile.bo import run_bo_search
     from ..profile.hardware import HardwareEvaluator
     from ..profile.partition_executor import PartitionExecutor
-    from ..profile.space import PARTITION_SPACES
+    from ..profile.space import partition_space
     from ..compose.composer import run_dir
 
     rank, world, local = init_distributed()
@@ -80,7 +80,9 @@ def main(argv=None) -> int:
         ctl.close()
         return 0
 
-    kind, space = PARTITION_SPACES[a.partition]
+    import copy
+    kind, space = partition_space(a.partition, a.tp_comm)
+    space = copy.deepcopy(space)
     space.nano_values = list(a.nano)
 
     def make_executor(nano: int):

@@ -280,7 +280,8 @@ class PartitionProgram:
 
         for st in steps:
             cfg = schedule.get(st.key) if schedule is not None else None
-            if cfg is not None:
+            planned = cfg is not None
+            if planned:
                 start = resolve_slot(st.slots, cfg.start) if st.compute else -1
                 shape = cfg.resource_shape
             else:
@@ -288,18 +289,18 @@ class PartitionProgram:
             launched = st.comm is None
             if self.n == 1 and st.comm is not None:
                 # a single nanobatch has nothing to hide the collective behind
-                self._launch_comm(st, ctxs, streams, shape, pending)
+                self._launch_comm(st, ctxs, streams, shape, pending, planned)
                 self._wait_all(pending, ctxs, streams)
                 launched = True
             for i, node in enumerate(st.compute):
                 if not launched and i == start:
-                    self._launch_comm(st, ctxs, streams, shape, pending)
+                    self._launch_comm(st, ctxs, streams, shape, pending, planned)
                     launched = True
                 self._run_compute(node, ctxs[st.nb], streams, grad_enabled, release_saved)
             if st.compute:
                 ctxs[st.nb].ready_event[st.segment] = streams.record(streams.compute())
             if not launched:
-                self._launch_comm(st, ctxs, streams, shape, pending)
+                self._launch_comm(st, ctxs, streams, shape, pending, planned)
             if self.sync == "partition_end":
                 self._wait_all(pending, ctxs, streams)
         self._wait_all(pending, ctxs, streams)
@@ -344,7 +345,7 @@ class PartitionProgram:
                 store.pop(tid)
 
     # -- collectives
-    def _launch_comm(self, st: Step, ctxs, streams: StreamSet, shape, pending) -> None:
+    def _launch_comm(self, st: Step, ctxs, streams: StreamSet, shape, pending, planned: bool = False) -> None:
         node, nb = st.comm, st.comm_nb
         nbctx = ctxs[nb]
         store = nbctx.store
@@ -362,16 +363,18 @@ class PartitionProgram:
                     wait_event(side, ev)
         sm_num, block = shape if shape is not None else (None, None)
         ctx = nbctx.ctx_for(node.op_id) if getattr(node.operator, "needs_ctx", False) else None
+        # operators whose sm_num has a second meaning when it comes from a plan entry are told so
+        kw = {"planned": planned} if getattr(node.operator, "takes_planned", False) else {}
         if streams.cuda:
             with torch.cuda.stream(side):
                 outs = node.operator.run(ins, sm_num=sm_num, block_size=block, backward=self.backward,
-                                         nb=nb, ctx=ctx)
+                                         nb=nb, ctx=ctx, **kw)
             done = streams.record(side)
             for t in ins:
                 record_stream(t, side)
         else:
             outs = node.operator.run(ins, sm_num=sm_num, block_size=block, backward=self.backward,
-                                     nb=nb, ctx=ctx)
+                                     nb=nb, ctx=ctx, **kw)
             done = None
         if not isinstance(outs, (tuple, list)):
             outs = (outs,)

@@ -19,8 +19,14 @@
 //   One extra CTA runs the start barrier (peers must have entered the call before their staging is
 //   written).
 //
-// `n_comm` (copy-driver CTAs of ag_gemm) is the plan's "SMs given to the collective" knob.  Every
-// wait is bounded (status word + return).  Role of the reference's separate cuBLASLt GEMM followed
+// The plan's `sm_num` knob ("SMs given to the collective") reaches both kernels as `n_comm`:
+// * ag_gemm: the number of copy-driver CTAs (more drivers pull the peers' shards faster and take SMs
+//   from the GEMM role);
+// * gemm_rs: the number of SMs the kernel leaves ALONE — its GEMM CTAs number num_sms − 1 − n_comm —
+//   so that the other nanobatch's kernels on the compute stream keep that many SMs while this
+//   link-bound kernel runs (0: use the whole budget).  There are no separate reducer CTAs: the sums
+//   are finished in the own-row epilogues.
+// Every wait is bounded (status word + return).  Role of the reference's separate cuBLASLt GEMM followed
 // or preceded by an all-reduce kernel (kareus/megatron/core/extensions/ops/te_linear.py:303-445,
 // 3rdparty/mscclpp/python/mscclpp_benchmark/allreduce.cu:155-246).
 #include "sm100.cuh"
@@ -504,19 +510,19 @@ extern "C" int kb_ag_gemm_bf16(void* const* bases, int rank, int world, uint64_t
 
 // out[M/world, N] = rows owned by this rank of sum over ranks of (A[M,K] · op(W)); W as above.
 // stage_off: staging [world][M/world][N] bf16; cnt_off: uint32 counters [world][M/world/128][tiles_n];
-// go: local uint32 flag.  n_comm reducer CTAs run next to the GEMM CTAs.
+// go: local uint32 flag.  n_comm: SMs of the num_sms budget that the kernel does not occupy.
 extern "C" int kb_gemm_rs_bf16(void* const* bases, int rank, int world, uint64_t flag_off, uint64_t stage_off,
                                uint64_t cnt_off, const void* A, int lda, const void* W, int ldw, int b_mn, void* out,
                                int M, int N, int K, uint32_t* go, uint32_t epoch, int n_comm, int num_sms, int* status,
                                cudaStream_t stream) {
   if (world < 2 || world > MAX_PEERS || M % (world * FG_BM) || (K & 7) || (N & 7) || (lda & 7)) return ST_BAD_ARG;
   if (num_sms <= 0) num_sms = device_sm_count();
-  if (n_comm < 1) n_comm = 1;
+  if (n_comm < 0) n_comm = 0;
   FusedParams p{};
   p.peer = fused_ctx(bases, rank, world, flag_off, status);
   p.mode = MODE_RS;
   p.n_first = 0;
-  p.n_last = n_comm;
+  p.n_last = 1;
   p.rows_per_rank = M / world;
   p.epoch = epoch;
   p.stage_off = stage_off;
@@ -526,9 +532,10 @@ extern "C" int kb_gemm_rs_bf16(void* const* bases, int rank, int world, uint64_t
   const bool narrow = (N <= 128) || (N % 256 != 0 && N % 256 <= 128);
   const int bn = narrow ? 128 : 256;
   const int tiles = (M / FG_BM) * ((N + bn - 1) / bn);
-  n_comm = 1;     // one CTA for the start barrier; the sums are finished in the GEMM epilogues
-  p.n_last = n_comm;
-  p.n_gemm = num_sms - n_comm < tiles ? num_sms - n_comm : tiles;   // reducers get SMs of their own
+  // one CTA runs the start barrier; n_comm SMs stay free for the other stream's kernels
+  int budget = num_sms - 1 - n_comm;
+  if (budget < 8) budget = 8;
+  p.n_gemm = budget < tiles ? budget : tiles;
   if (narrow) return b_mn ? launch_fused<128, true>(A, W, p, M, N, K, lda, ldw, stream)
                           : launch_fused<128, false>(A, W, p, M, N, K, lda, ldw, stream);
   return b_mn ? launch_fused<256, true>(A, W, p, M, N, K, lda, ldw, stream)

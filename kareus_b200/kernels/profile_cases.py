@@ -157,7 +157,7 @@ def fused_table() -> None:
                 ctx.requires_grad = False
                 op.run((x,), sm_num=sm, nb=0, ctx=ctx)
             elif cls is FusedDgradRS:
-                op._gemm_rs(x.reshape(-1, red), w, out, True, sm, 0)
+                op._gemm_rs(x.reshape(-1, red), w, out, True, 0, 0)      # whole SM budget, none left free
             else:
                 op._ag_gemm(x.reshape(-1, red), w, out, True, sm, 0)
 

@@ -6,8 +6,10 @@ the local wgrad) and ``FusedAGDgrad`` (all-gather of dY → row-parallel dgrad, 
 gathered dY).  All four wrap the kernels of ``csrc/fused_gemm_comm.cu``.
 
 To the partition engine they are collective nodes: they run on the side stream, take the plan
-entry's ``sm_num`` (copy-driver / reducer CTAs) and overlap with the other nanobatch's compute, but
-they also produce the GEMM results, so the graph has no separate compute node for the linear layer.
+entry's ``sm_num`` and overlap with the other nanobatch's compute.  ``sm_num`` means copy-driver CTAs
+for the all-gather kernels; for the reduce-scatter kernels it is the number of SMs the kernel leaves
+to the other nanobatch, honoured only when a plan names it (``planned=True``) — without a plan they
+use their whole SM budget.  They also produce the GEMM results, so the graph has no separate compute node for the linear layer.
 State kept between forward and backward (the gathered input, or the row-parallel input) lives in the
 linear operator's own context: these nodes share its graph uid.
 """
@@ -75,6 +77,7 @@ def _wgrad(dy2, x, weight) -> None:
 
 class _FusedBase:
     needs_ctx = True
+    takes_planned = True      # run() wants to know whether sm_num comes from a plan entry
     group = "linear"
 
     def __init__(self, linear, heap, default_sm: int):
@@ -119,7 +122,7 @@ class _FusedBase:
         return y, xg
 
     def _gemm_rs(self, a2, w, n_out, b_mn: bool, sm_num, nb: int):
-        """``reduce_scatter_rows(a2 · op(w))`` → ``[M/world, n_out]``."""
+        """``reduce_scatter_rows(a2 · op(w))`` → ``[M/world, n_out]``.  ``sm_num``: SMs left free."""
         heap = self.heap
         world, rank = heap.world, heap.rank
         if not KC._rowmajor_ok(a2):
@@ -140,7 +143,7 @@ class _FusedBase:
         st = KC.status_word(a2.device)
         rc = L.kb_gemm_rs_bf16(heap._bases_arr, rank, world, ch.flag_off, stage_off, cnt_off, a2.data_ptr(),
                                a2.stride(0), w.data_ptr(), w.stride(0), 1 if b_mn else 0, out.data_ptr(), m, n_out, k,
-                               go.data_ptr(), ch.epoch, int(sm_num or self.default_sm), _fused_sms(), st.data_ptr(),
+                               go.data_ptr(), ch.epoch, int(sm_num or 0), _fused_sms(), st.data_ptr(),
                                KC._stream())
         KC._check(rc, f"gemm_rs {self.name}")
         KC._count()
@@ -150,7 +153,7 @@ class _FusedBase:
 class FusedAGGemm(_FusedBase):
     """forward of a column-parallel layer: ``Y = AllGather(x)·Wᵀ``."""
 
-    def run(self, tensors, sm_num=None, block_size=None, backward=False, nb=0, ctx=None):
+    def run(self, tensors, sm_num=None, block_size=None, backward=False, nb=0, ctx=None, planned=False):
         (x,) = tensors
         lin = self.linear
         lead = x.shape[:-1]
@@ -163,11 +166,12 @@ class FusedAGGemm(_FusedBase):
 class FusedGemmRS(_FusedBase):
     """forward of a row-parallel layer: ``Y_shard = ReduceScatter(a·Wᵀ)``."""
 
-    def run(self, tensors, sm_num=None, block_size=None, backward=False, nb=0, ctx=None):
+    def run(self, tensors, sm_num=None, block_size=None, backward=False, nb=0, ctx=None, planned=False):
         (a,) = tensors
         lin = self.linear
         lead = a.shape[:-1]
-        out, a2 = self._gemm_rs(a.reshape(-1, a.shape[-1]), lin.weight, lin.out_features, False, sm_num, nb)
+        out, a2 = self._gemm_rs(a.reshape(-1, a.shape[-1]), lin.weight, lin.out_features, False,
+                                sm_num if planned else 0, nb)
         if ctx is not None and ctx.requires_grad:
             ctx.save_for_backward(a2)
         return (out.reshape((lead[0] // self.heap.world,) + tuple(lead[1:]) + (lin.out_features,)),)
@@ -176,12 +180,13 @@ class FusedGemmRS(_FusedBase):
 class FusedDgradRS(_FusedBase):
     """backward of a column-parallel layer: ``dX_shard = ReduceScatter(dY·W)`` and ``dW += dYᵀ·X``."""
 
-    def run(self, tensors, sm_num=None, block_size=None, backward=True, nb=0, ctx=None):
+    def run(self, tensors, sm_num=None, block_size=None, backward=True, nb=0, ctx=None, planned=False):
         (dy,) = tensors
         lin = self.linear
         (x_full,) = ctx.saved_tensors
         lead = dy.shape[:-1]
-        dx, dy2 = self._gemm_rs(dy.reshape(-1, dy.shape[-1]), lin.weight, lin.in_features, True, sm_num, nb)
+        dx, dy2 = self._gemm_rs(dy.reshape(-1, dy.shape[-1]), lin.weight, lin.in_features, True,
+                                sm_num if planned else 0, nb)
         _wgrad(dy2, x_full, lin.weight)
         ctx.clear()
         return (dx.reshape((lead[0] // self.heap.world,) + tuple(lead[1:]) + (lin.in_features,)),)
@@ -190,7 +195,7 @@ class FusedDgradRS(_FusedBase):
 class FusedAGDgrad(_FusedBase):
     """backward of a row-parallel layer: ``dX = AllGather(dY)·W`` and ``dW += AllGather(dY)ᵀ·A``."""
 
-    def run(self, tensors, sm_num=None, block_size=None, backward=True, nb=0, ctx=None):
+    def run(self, tensors, sm_num=None, block_size=None, backward=True, nb=0, ctx=None, planned=False):
         (dy,) = tensors
         lin = self.linear
         (a2,) = ctx.saved_tensors

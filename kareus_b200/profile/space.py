@@ -88,5 +88,34 @@ PARTITION_SPACES: Dict[str, Tuple[str, SearchSpace]] = {
     "bwd_o_ag": ("all_gather_kv", SearchSpace(_ow("norm_0", "linear_0"), _AG_SM, 36, 3, 16)),
     "bwd_o_ar": ("all_reduce", SearchSpace(_ow("norm_0"), _AR_SM, 36, 3, 16)),
 }
+# Partitions of the fused sequence-parallel path (``tp_comm="sp_fused"``): eight per layer, each the
+# compute of one segment beside the fused GEMM+collective kernel of the other nanobatch.  ``sm``
+# is the fused kernel's knob: copy-driver CTAs for all-gather→GEMM kernels, SMs the kernel leaves to
+# the other nanobatch's compute for GEMM→reduce-scatter kernels (``csrc/fused_gemm_comm.cu``).  The
+# reference has no such partitions (its TP collectives are all-reduces: ``tests/bayesian/partitions``).
+_FUSED_AG_SM = [4, 8, 12, 16, 24, 32]
+_FUSED_RS_SM = [0, 8, 16, 24, 32, 48]
+SP_FUSED_SPACES: Dict[str, Tuple[str, SearchSpace]] = {
+    "fwd_attn_ag": ("fused_ag_gemm", SearchSpace(_ow("norm_0"), _FUSED_AG_SM, 12, 2, 6)),
+    "fwd_attn": ("fused_gemm_rs", SearchSpace(_ow("rope_0", "attn_0"), _FUSED_RS_SM, 16, 2, 8)),
+    "fwd_mlp_ag": ("fused_ag_gemm", SearchSpace(_ow("norm_0"), _FUSED_AG_SM, 12, 2, 6)),
+    "fwd_mlp": ("fused_gemm_rs", SearchSpace(_ow("activation_0"), _FUSED_RS_SM, 12, 2, 6)),
+    "bwd_mlp_ag": ("fused_ag_dgrad", SearchSpace(_ow("norm_0"), _FUSED_AG_SM, 12, 2, 6)),
+    "bwd_mlp": ("fused_dgrad_rs", SearchSpace(_ow("activation_0"), _FUSED_RS_SM, 12, 2, 6)),
+    "bwd_attn_ag": ("fused_ag_dgrad", SearchSpace(_ow("norm_0"), _FUSED_AG_SM, 12, 2, 6)),
+    "bwd_attn": ("fused_dgrad_rs", SearchSpace(_ow("attn_0", "rope_0"), _FUSED_RS_SM, 16, 2, 8)),
+}
+SP_FUSED_PARTITIONS = tuple(SP_FUSED_SPACES)
+
+
+def partition_space(key: str, tp_comm: str = "allreduce") -> Tuple[str, SearchSpace]:
+    """``(collective kind, search space)`` of a partition key for a tensor-parallel flavour."""
+    if tp_comm in ("sp", "sp_fused") and key in SP_FUSED_SPACES:
+        return SP_FUSED_SPACES[key]
+    if key not in PARTITION_SPACES:
+        raise KeyError(f"unknown partition {key!r}; known: {sorted(PARTITION_SPACES) + sorted(SP_FUSED_SPACES)}")
+    return PARTITION_SPACES[key]
+
+
 TP_PARTITIONS = ("fwd_attn", "fwd_mlp", "bwd_attn", "bwd_mlp")
 CP_PARTITIONS = tuple(k for k in PARTITION_SPACES if k not in TP_PARTITIONS or k in ("fwd_mlp", "bwd_mlp"))

@@ -49,3 +49,35 @@ def test_evaluator_and_nonpartition(tmp_path):
                          sleep_fn=lambda s: None)
     txt = (tmp_path / "nonpartition" / "1500" / "loss_energy.csv").read_text().splitlines()
     assert txt[0] == "time (s),total_energy (J),per_rank_energy (J)" and len(txt[1].split(",")) == 3
+
+
+def test_fused_sequence_parallel_partitions_name_real_slots():
+    """Every partition of the fused sequence-parallel path exists as a step key and offers the launch
+    slots its search space lists (checked on the unfused "sp" program, which has the same segments)."""
+    from kareus_b200.config import ParallelConfig, get_model_config
+    from kareus_b200.engine.block import _Chunk
+    from kareus_b200.models.llama import TransformerLayer
+    from kareus_b200.profile.space import SP_FUSED_SPACES, partition_space
+
+    class Comm:
+        heap = None
+
+        def _args(self, axis):
+            return (None, 2, 0) if axis == "tp" else (None, 1, 0)
+
+        def make(self, cls, axis, name):
+            g, w, r = self._args(axis)
+            return cls(g, w, r, name=name)
+
+    cfg = get_model_config("tiny")
+    layer = TransformerLayer(cfg, ParallelConfig(tp=2, tp_comm="sp"), Comm(), 0, torch.float32, "cpu", seed=0)
+    chunk = _Chunk(layer.operators(), 2, "partition_end")
+    assert len(SP_FUSED_SPACES) == 8
+    for key, (kind, space) in SP_FUSED_SPACES.items():
+        prog = chunk.bwd if key.startswith("bwd_") else chunk.fwd
+        steps = [s for s in prog.steps if s.key == key and s.compute and s.comm is not None]
+        assert steps, key
+        for slot, _ in space.overlap_windows:
+            assert slot in steps[-1].slots, (key, slot, steps[-1].slots)
+        assert partition_space(key, "sp_fused")[0] == kind
+    assert partition_space("fwd_attn", "allreduce")[0] == "all_reduce"

@@ -109,13 +109,16 @@ def add(a, b):
 
 
 # ----------------------------------------------------------------------------- GEMM
-def gemm(a, b, trans_a=False, trans_b=True, out_dtype=None, accumulate=None, out=None):
-    """``op(a) @ op(b)``.  ``accumulate`` is an fp32 tensor that receives ``+=``."""
+def gemm(a, b, trans_a=False, trans_b=True, out_dtype=None, accumulate=None, out=None, bias=None, activation=None):
+    """``op(a) @ op(b)``.  ``accumulate`` is an fp32 tensor that receives ``+=``.  ``bias`` (per output
+    feature) and ``activation`` (``"gelu"``) run in the GEMM's epilogue."""
     if is_cuda(a):
         if library_baseline():
-            return _cuda().gemm_library(a, b, trans_a, trans_b, out_dtype, accumulate, out)
-        return _cuda().gemm(a, b, trans_a, trans_b, out_dtype, accumulate, out)
+            return _cuda().gemm_library(a, b, trans_a, trans_b, out_dtype, accumulate, out, bias, activation)
+        return _cuda().gemm(a, b, trans_a, trans_b, out_dtype, accumulate, out, bias=bias, activation=activation)
     r = ref.gemm(a, b, trans_a, trans_b, out_dtype, accumulate)
+    if bias is not None or activation:
+        r = ref.bias_act(r, bias, activation)
     if out is not None:
         out.copy_(r)
         return out

@@ -49,10 +49,30 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
   tn = r / gsz;
 }
 
+// Optional epilogue on the fp32 accumulator before it is stored: + bias[col] (bf16, per output
+// feature) and then an activation (1: GELU, tanh approximation).  This is the fused forward of
+// Linear + Bias (+ activation) of the reference's operator set
+// (kareus/transformer_engine/pytorch/ops/basic/basic_linear_bias.py:34-315,
+// ops/fused/forward_linear_bias_activation.py:37-213); Llama layers have no bias and pass null.
+struct Epilogue {
+  const __nv_bfloat16* bias;
+  int act;
+};
+__device__ __forceinline__ void apply_epilogue(uint32_t (&v)[32], const Epilogue& ep, int col0, int N) {
+  if (ep.bias == nullptr && ep.act == 0) return;
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    float x = __uint_as_float(v[j]);
+    if (ep.bias != nullptr && col0 + j < N) x += __bfloat162float(ep.bias[col0 + j]);
+    if (ep.act == 1) x = 0.5f * x * (1.f + tanhf(0.7978845608028654f * x * (1.f + 0.044715f * x * x)));
+    v[j] = __float_as_uint(x);
+  }
+}
+
 template <int BN, bool A_MN, bool B_MN, bool OUT_F32, bool ACCUM>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 void* __restrict__ Cout, int M, int N, int K, int ldc, int group_m, int* status) {
+                 void* __restrict__ Cout, int M, int N, int K, int ldc, int group_m, int* status, Epilogue ep) {
   using S = GemmSmem<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -193,6 +213,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               uint32_t v[32];
               tmem_ld_32x32(taddr + (cp * 2 + half) * 32, v);
               tmem_ld_wait();
+              apply_epilogue(v, ep, n0 + cp * 64 + half * 32, N);
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
                 uint4 o;
@@ -228,6 +249,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         tmem_ld_32x32(taddr + c * 32, v);
         tmem_ld_wait();
         const int col = n0 + c * 32;
+        if constexpr (!ACCUM) apply_epilogue(v, ep, col, N);
         if (row < M && col < N) {
           if constexpr (OUT_F32) {
             float* crow = reinterpret_cast<float*>(Cout) + static_cast<size_t>(row) * ldc + col;
@@ -285,7 +307,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 // ----------------------------------------------------------------------------- host side
 template <int BN, bool A_MN, bool B_MN, bool OUT_F32, bool ACCUM>
 static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
-                       int num_sms, int* status, cudaStream_t stream) {
+                       int num_sms, int* status, cudaStream_t stream, Epilogue ep) {
   CUtensorMap tmA, tmB;
   int rc;
   // K-major operand: dims (K, rows), box (64, tile rows).  MN-major: dims (rows, K), box (64, 64).
@@ -312,20 +334,20 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
   int group_m = (int)((40L << 20) / (panel > 0 ? panel : 1));
   if (group_m < 4) group_m = 4;
   if (group_m > tiles_m) group_m = tiles_m;
-  KB_LAUNCH(kern, grid, GEMM_THREADS, smem, stream, tmA, tmB, C, M, N, K, ldc, group_m, status);
+  KB_LAUNCH(kern, grid, GEMM_THREADS, smem, stream, tmA, tmB, C, M, N, K, ldc, group_m, status, ep);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 2000 + static_cast<int>(e);
 }
 
 template <int BN, bool A_MN, bool B_MN>
 static int dispatch_out(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
-                        int out_f32, int accumulate, int num_sms, int* status, cudaStream_t stream) {
+                        int out_f32, int accumulate, int num_sms, int* status, cudaStream_t stream, Epilogue ep) {
   if (out_f32 && accumulate)
-    return launch_gemm<BN, A_MN, B_MN, true, true>(A, B, C, M, N, K, lda, ldb, ldc, num_sms, status, stream);
+    return launch_gemm<BN, A_MN, B_MN, true, true>(A, B, C, M, N, K, lda, ldb, ldc, num_sms, status, stream, ep);
   if (out_f32)
-    return launch_gemm<BN, A_MN, B_MN, true, false>(A, B, C, M, N, K, lda, ldb, ldc, num_sms, status, stream);
+    return launch_gemm<BN, A_MN, B_MN, true, false>(A, B, C, M, N, K, lda, ldb, ldc, num_sms, status, stream, ep);
   if (accumulate) return ST_BAD_ARG;
-  return launch_gemm<BN, A_MN, B_MN, false, false>(A, B, C, M, N, K, lda, ldb, ldc, num_sms, status, stream);
+  return launch_gemm<BN, A_MN, B_MN, false, false>(A, B, C, M, N, K, lda, ldb, ldc, num_sms, status, stream, ep);
 }
 
 }  // namespace kb
@@ -335,11 +357,17 @@ static int dispatch_out(const void* A, const void* B, void* C, int M, int N, int
 //   b_mn = 0: B is [N, K] row-major;                                b_mn = 1: B is stored [K, N].
 //   out_f32: C is fp32 (else bf16); accumulate: C += (fp32 only).  num_sms limits the grid.
 // Strides must be multiples of 8 elements and base pointers 16-byte aligned (TMA rules).
-extern "C" int kb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int a_mn, int lda,
-                            int b_mn, int ldb, int ldc, int out_f32, int accumulate, int num_sms, int* status,
-                            cudaStream_t stream) {
+// kb_gemm_bias_act_bf16 adds the epilogue: bias (bf16 [N], may be null) and act (0 none, 1 GELU); it is not
+// available together with accumulate.
+extern "C" int kb_gemm_bias_act_bf16(const void* A, const void* B, void* C, int M, int N, int K, int a_mn, int lda,
+                                     int b_mn, int ldb, int ldc, int out_f32, int accumulate, int num_sms,
+                                     const void* bias, int act, int* status, cudaStream_t stream) {
   using namespace kb;
   if (M <= 0 || N <= 0 || K <= 0) return ST_BAD_ARG;
+  if ((bias != nullptr || act != 0) && accumulate) return ST_BAD_ARG;
+  if (act < 0 || act > 1) return ST_BAD_ARG;
+  const Epilogue ep{reinterpret_cast<const __nv_bfloat16*>(bias), act};
+  const bool plain = bias == nullptr && act == 0;
   if ((lda & 7) || (ldb & 7) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
     return ST_BAD_ARG;
   if (num_sms <= 0) num_sms = device_sm_count();
@@ -348,7 +376,7 @@ extern "C" int kb_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
     // epilogue is not overlapped, which only pays off when the main loop is long), see gemm256_sm100.cu
     static const bool allow256 = [] { const char* e = getenv("KB_GEMM256"); return !(e && e[0] == '0'); }();
     const long tiles256 = (long)((M + 255) / 256) * ((N + 255) / 256);
-    if (allow256 && M >= 512 && N >= 512 && K >= 2048 && (N % 256 == 0 || N >= 4096) && tiles256 >= num_sms)
+    if (plain && allow256 && M >= 512 && N >= 512 && K >= 2048 && (N % 256 == 0 || N >= 4096) && tiles256 >= num_sms)
       return gemm256_dispatch(A, B, C, M, N, K, a_mn, lda, b_mn, ldb, ldc, out_f32, accumulate, num_sms, status,
                               stream);
   }
@@ -356,12 +384,19 @@ extern "C" int kb_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
   const bool narrow = (N <= 128) || (N % 256 != 0 && N % 256 <= 128);
 #define KB_GO(BN_)                                                                                         \
   do {                                                                                                     \
-    if (!a_mn && !b_mn) return dispatch_out<BN_, false, false>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, accumulate, num_sms, status, stream); \
-    if (!a_mn && b_mn) return dispatch_out<BN_, false, true>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, accumulate, num_sms, status, stream);   \
-    if (a_mn && !b_mn) return dispatch_out<BN_, true, false>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, accumulate, num_sms, status, stream);   \
-    return dispatch_out<BN_, true, true>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, accumulate, num_sms, status, stream);                       \
+    if (!a_mn && !b_mn) return dispatch_out<BN_, false, false>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, accumulate, num_sms, status, stream, ep); \
+    if (!a_mn && b_mn) return dispatch_out<BN_, false, true>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, accumulate, num_sms, status, stream, ep);   \
+    if (a_mn && !b_mn) return dispatch_out<BN_, true, false>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, accumulate, num_sms, status, stream, ep);   \
+    return dispatch_out<BN_, true, true>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, accumulate, num_sms, status, stream, ep);                       \
   } while (0)
   if (narrow) KB_GO(128);
   KB_GO(256);
 #undef KB_GO
+}
+
+extern "C" int kb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int a_mn, int lda,
+                            int b_mn, int ldb, int ldc, int out_f32, int accumulate, int num_sms, int* status,
+                            cudaStream_t stream) {
+  return kb_gemm_bias_act_bf16(A, B, C, M, N, K, a_mn, lda, b_mn, ldb, ldc, out_f32, accumulate, num_sms, nullptr, 0,
+                               status, stream);
 }

@@ -51,6 +51,7 @@ def _declare(L) -> None:
     P, I, LNG, F, U = c_void_p, c_int, c_long, c_float, c_uint
     sig = {
         "kb_gemm_bf16": [P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, P],
+        "kb_gemm_bias_act_bf16": [P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, I, P, P],
         "kb_rmsnorm_fwd": [P, P, P, P, I, I, F, P],
         "kb_rmsnorm_bwd": [P, P, P, P, P, P, P, I, I, P],
         "kb_rmsnorm_bwd_acc": [P, P, P, P, P, P, P, I, I, I, P],
@@ -309,10 +310,24 @@ def _rowmajor_ok(t: torch.Tensor) -> bool:
         and t.stride(0) >= t.shape[1]
 
 
-def gemm(a, b, trans_a=False, trans_b=True, out_dtype=None, accumulate=None, out=None, num_sms=None):
+ACTIVATIONS = {None: 0, "none": 0, "gelu": 1}
+
+
+def gemm(a, b, trans_a=False, trans_b=True, out_dtype=None, accumulate=None, out=None, num_sms=None, bias=None,
+         activation=None):
     """``op(a) @ op(b)`` on the tcgen05 kernel.  ``a``: [M,K] (or [K,M] if ``trans_a``); ``b``: [N,K]
-    when ``trans_b`` (the nn.Linear weight layout) else [K,N]."""
+    when ``trans_b`` (the nn.Linear weight layout) else [K,N].  ``bias`` ([N]) and ``activation``
+    (``"gelu"``) are applied to the accumulator in the kernel's epilogue."""
     if not _bf16(a):
+        if bias is not None or activation:
+            r = ref.gemm(a, b, trans_a, trans_b, None, None)
+            r = ref.bias_act(r, bias, activation)
+            if out_dtype is not None:
+                r = r.to(out_dtype)
+            if out is not None:
+                out.copy_(r)
+                return out
+            return r
         r = ref.gemm(a, b, trans_a, trans_b, out_dtype, accumulate)
         if out is not None:
             out.copy_(r)
@@ -342,6 +357,25 @@ def gemm(a, b, trans_a=False, trans_b=True, out_dtype=None, accumulate=None, out
             raise KernelError("gemm out must have a contiguous last dim")
         c, f32, acc = out, 1 if out.dtype == torch.float32 else 0, 0
     st = status_word(a.device)
+    if bias is not None or activation:
+        if accumulate is not None:
+            raise KernelError("a bias/activation epilogue cannot be combined with accumulation")
+        if activation not in ACTIVATIONS:
+            raise KernelError(f"unknown epilogue activation {activation!r}")
+        bp = 0
+        if bias is not None:
+            if bias.numel() != N:
+                raise KernelError(f"bias has {bias.numel()} elements for {N} output features")
+            bias = bias if (_bf16(bias) and bias.is_contiguous()) else bias.to(torch.bfloat16).contiguous()
+            bp = bias.data_ptr()
+        rc = lib().kb_gemm_bias_act_bf16(a.data_ptr(), b.data_ptr(), c.data_ptr(), M, N, K, 1 if trans_a else 0,
+                                         a.stride(0), 0 if trans_b else 1, b.stride(0), c.stride(0), f32, 0,
+                                         int(num_sms) if num_sms else 0, bp, ACTIVATIONS[activation], st.data_ptr(),
+                                         _stream())
+        if rc != 0:
+            _check(rc, f"gemm+epilogue M={M} N={N} K={K}")
+        _count()
+        return c
     rc = lib().kb_gemm_bf16(a.data_ptr(), b.data_ptr(), c.data_ptr(), M, N, K, 1 if trans_a else 0, a.stride(0),
                             0 if trans_b else 1, b.stride(0), c.stride(0), f32, acc,
                             int(num_sms) if num_sms else 0, st.data_ptr(), _stream())
@@ -351,11 +385,18 @@ def gemm(a, b, trans_a=False, trans_b=True, out_dtype=None, accumulate=None, out
     return c
 
 
-def gemm_library(a, b, trans_a=False, trans_b=True, out_dtype=None, accumulate=None, out=None):
+def gemm_library(a, b, trans_a=False, trans_b=True, out_dtype=None, accumulate=None, out=None, bias=None,
+                 activation=None):
     """cuBLAS through torch: the A/B baseline, never the default."""
     _no_recording("a cuBLAS GEMM")
     A = a.t() if trans_a else a
     B = b.t() if trans_b else b
+    if bias is not None or activation:
+        r = ref.bias_act(torch.matmul(A, B), bias, activation)
+        if out is not None:
+            out.copy_(r)
+            return out
+        return r
     if accumulate is not None:
         accumulate.add_(torch.matmul(A, B).to(accumulate.dtype))
         return accumulate

@@ -122,6 +122,23 @@ def gemm(a, b, trans_a: bool = False, trans_b: bool = True, out_dtype=None, accu
 
 
 # ----------------------------------------------------------------------------- attention
+def gelu(x):
+    """tanh approximation (the one Megatron's fused bias-GELU uses)."""
+    xf = x.to(_acc(x))
+    return (0.5 * xf * (1.0 + torch.tanh(0.7978845608028654 * xf * (1.0 + 0.044715 * xf * xf)))).to(x.dtype)
+
+
+def bias_act(y, bias=None, activation=None):
+    """Epilogue of a linear layer: ``act(y + bias)``."""
+    if bias is not None:
+        y = (y.to(_acc(y)) + bias.to(_acc(y))).to(y.dtype)
+    if activation in (None, "none"):
+        return y
+    if activation == "gelu":
+        return gelu(y)
+    raise ValueError(f"unknown activation {activation!r}")
+
+
 def _heads4(t):
     """``[s,b,g,rep,d]`` → ``[s,b,g*rep,d]`` (copy if the strides need it)."""
     if t.dim() == 5:

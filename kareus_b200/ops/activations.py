@@ -81,3 +81,27 @@ class GeluOp(_GeluBase):
 
 class GegluOp(_GeluBase):
     gated = True
+
+
+def gelu_forward(x2: torch.Tensor) -> torch.Tensor:
+    """GELU of a 2-D tensor (kernel on bf16 CUDA tensors, PyTorch statement otherwise)."""
+    if x2.is_cuda and x2.dtype == torch.bfloat16:
+        x2 = x2.contiguous()
+        y = torch.empty_like(x2)
+        _launch("kb_gelu_fwd", [c_void_p(x2.data_ptr()), c_void_p(y.data_ptr()), c_long(x2.shape[0]), c_int(x2.shape[1]),
+                                c_int(0), c_void_p(KC._stream())])
+        return y
+    acc = torch.float64 if x2.dtype == torch.float64 else torch.float32
+    return gelu_ref(x2.to(acc)).to(x2.dtype)
+
+
+def gelu_backward(dy2: torch.Tensor, x2: torch.Tensor) -> torch.Tensor:
+    """``dy * gelu'(x)`` for 2-D tensors."""
+    if x2.is_cuda and x2.dtype == torch.bfloat16:
+        dy2 = dy2.contiguous()
+        dx = torch.empty_like(x2)
+        _launch("kb_gelu_bwd", [c_void_p(dy2.data_ptr()), c_void_p(x2.data_ptr()), c_void_p(dx.data_ptr()),
+                                c_long(x2.shape[0]), c_int(x2.shape[1]), c_int(0), c_void_p(KC._stream())])
+        return dx
+    acc = torch.float64 if x2.dtype == torch.float64 else torch.float32
+    return (dy2.to(acc) * gelu_grad_ref(x2.to(acc))).to(x2.dtype)

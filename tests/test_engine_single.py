@@ -141,3 +141,34 @@ def test_layernorm_and_bias_ops_match_autograd():
     b.backward(OpContext(), g)
     torch.testing.assert_close(b.bias.main_grad, g.reshape(-1, 32).sum(0))
     assert type(make_norm("RMSNorm", 32, 1e-5, "n")).__name__ == "RMSNormOp"
+
+
+@pytest.mark.parametrize("activation,skip", [(None, False), ("gelu", False), (None, True)])
+def test_linear_bias_operator_matches_autograd(activation, skip):
+    """Linear + bias (+ GELU): forward with and without gradients, all three gradients."""
+    import torch.nn.functional as F
+    from kareus_b200.engine.context import OpContext
+    from kareus_b200.ops.extras import LinearBiasOp
+    torch.manual_seed(0)
+    op = LinearBiasOp(48, 40, activation=activation, skip_bias_add=skip, dtype=torch.float64, seed=3)
+    op.bias.data.normal_()
+    x = torch.randn(6, 2, 48, dtype=torch.float64, requires_grad=True)
+    w = op.weight.detach().clone().requires_grad_(True)
+    b = op.bias.detach().clone().requires_grad_(True)
+    z = F.linear(x, w, None if skip else b)
+    want = F.gelu(z, approximate="tanh") if activation else z
+    ctx = OpContext()
+    (y,) = op.forward(ctx, x.detach())
+    torch.testing.assert_close(y, want.detach())
+    nog = OpContext()
+    nog.requires_grad = False
+    torch.testing.assert_close(op.forward(nog, x.detach())[0], want.detach())     # the single-launch path
+    dy = torch.randn_like(want)
+    want.backward(dy)
+    (dx,) = op.backward(ctx, dy)
+    torch.testing.assert_close(dx, x.grad)
+    torch.testing.assert_close(op.weight.main_grad, w.grad)
+    if skip:
+        assert getattr(op.bias, "main_grad", None) is None
+    else:
+        torch.testing.assert_close(op.bias.main_grad, b.grad)

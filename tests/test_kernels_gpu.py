@@ -334,3 +334,21 @@ def test_chunked_attention_matches_reference(cp, c):
                 wv[j * c:(j + 1) * c].abs().max() == 0, ("dv", rank, j)
             if wk[j * c:(j + 1) * c].abs().max() == 0:      # chunk no local query can see: exact zeros
                 assert dkv[dk_base[j]:dk_base[j] + c].abs().max() == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 384, 512), (1000, 328, 200), (4096, 4096, 2048)])
+@pytest.mark.parametrize("activation", [None, "gelu"])
+def test_gemm_bias_activation_epilogue(M, N, K, activation):
+    """Bias and GELU applied to the accumulator inside the GEMM kernel."""
+    KC = _K()
+    from kareus_b200.kernels import ref
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    a = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.05).bfloat16()
+    bias = torch.randn(N, device="cuda", generator=g).bfloat16()
+    got = KC.gemm(a, w, bias=bias, activation=activation)
+    KC.check_status()
+    want = ref.bias_act(a.float() @ w.float().t(), bias.float(), activation)
+    assert _rel(got, want) < 1e-2
+    only_act = KC.gemm(a, w, activation=activation)
+    assert _rel(only_act, ref.bias_act(a.float() @ w.float().t(), None, activation)) < 1e-2

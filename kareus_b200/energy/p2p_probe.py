@@ -33,3 +33,36 @@ def probe_p2p_power(duration_s: float = 60.0, monitor: Optional[EnergyMonitor] =
         sleep_fn(duration_s)
         dist.send(buf, dst=0)
     return 0.0
+
+
+def main(argv=None) -> int:
+    """``torchrun --nproc-per-node 2 -m kareus_b200.energy.p2p_probe --duration 20`` prints one JSON line
+    with the measured watts (rank 0's GPU, blocked in an NCCL receive)."""
+    import argparse
+    import json
+    import torch
+    import torch.distributed as dist
+    from ..parallel.mesh import init_distributed
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--duration", type=float, default=20.0)
+    a = ap.parse_args(argv)
+    rank, world, local = init_distributed()
+    if world < 2:
+        raise SystemExit("the probe needs two ranks")
+    if torch.cuda.is_available():
+        torch.cuda.set_device(local)
+        # make sure the communicator exists before the measured wait
+        t = torch.zeros(1, device="cuda")
+        dist.all_reduce(t)
+        torch.cuda.synchronize()
+    watts = probe_p2p_power(a.duration)
+    if rank == 0:
+        print(json.dumps({"p2p_wait_power_w": watts, "duration_s": a.duration,
+                          "gpu": torch.cuda.get_device_name(local) if torch.cuda.is_available() else "cpu"}), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

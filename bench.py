@@ -148,6 +148,9 @@ def main() -> int:
     if args.comm_backend is None:
         args.comm_backend = "kernel"
     tp = args.tp or max(1, world // (args.pp * args.cp))
+    if world > 1:
+        # a peer's matching kernel can sit behind a full-GPU GEMM of the other nanobatch: allow for it
+        os.environ.setdefault("KAREUS_PEER_WAIT_MS", "8000")
     if tp > 1 and args.tp_comm == "sp_fused":
         os.environ.setdefault("KAREUS_SYNC", "lazy")
         if tp >= 4:
@@ -205,6 +208,9 @@ def main() -> int:
         trainer.optimizer.step()
     sync_all()
     KC.check_status()
+    if args.pp > 1 and trainer.p2p is not None:
+        from kareus_b200.parallel.pipeline import P2PStats
+        trainer.p2p.stats = P2PStats()
     sampler = ClockSampler(local)
     sampler.start()
     e0 = sampler.energy_mj()
@@ -234,6 +240,18 @@ def main() -> int:
     ms = float(t.item())
     value = tokens_per_step * args.steps / (ms / 1000.0)
     final_loss = trainer.reduce_loss(loss)
+    p2p = None
+    if args.pp > 1 and trainer.p2p is not None and trainer.p2p.stats is not None:
+        st = trainer.p2p.stats.summary()
+        trainer.p2p.stats = None
+        v = torch.tensor([st["stall_ms"], float(st["received_bytes"]), float(st["receives"])], device=device,
+                         dtype=torch.float64)
+        dist.all_reduce(v, op=dist.ReduceOp.MAX)
+        # per step, worst stage: time the compute stream waited for a neighbour's activations or gradients
+        # (unhidden transfer + pipeline bubble), next to the time the bytes need at the measured peer-copy rate
+        p2p = {"recv_stall_ms_per_step": float(v[0]) / args.steps, "recv_bytes_per_step": float(v[1]) / args.steps,
+               "receives_per_step": float(v[2]) / args.steps,
+               "transfer_ms_at_770GBs_per_step": float(v[1]) / args.steps / 770e9 * 1e3}
 
     # ------------------------------------------------------------- end-to-end region
     e2e = None
@@ -332,7 +350,7 @@ def main() -> int:
             "host_enqueue_ms_per_step": host_ms / args.steps,
             "host_us_per_launch": host_ms * 1000.0 / max(1, launches),
             "launch_list_regions_replayed": replayed,
-            "nccl_cublas_baseline": baseline,
+            "nccl_cublas_baseline": baseline, "pipeline_p2p": p2p,
             "impl": "ours",
         }
         print(json.dumps(out))

@@ -10,6 +10,7 @@
 // Also here: the host side of the heap (allocation, CUDA IPC handle exchange is done by the caller).
 #include <cuda_bf16.h>
 #include "launch.h"
+#include <stdlib.h>
 #include <string.h>
 #include "peer.cuh"
 
@@ -145,12 +146,33 @@ static PeerCtx make_ctx(void* const* bases, int rank, int world, uint64_t flag_o
   c.world = world;
   c.flag_off = flag_off;
   c.status = status;
+  c.wait_ns = peer_wait_limit_ns();
   return c;
 }
 
 }  // namespace kb
 
+namespace kb {
+static uint64_t g_peer_wait_ns = 0;
+uint64_t peer_wait_limit_ns() {
+  if (g_peer_wait_ns == 0) {
+    const char* e = getenv("KAREUS_PEER_WAIT_MS");
+    long ms = e ? atol(e) : 0;
+    if (ms <= 0) ms = 2000;
+    g_peer_wait_ns = static_cast<uint64_t>(ms) * 1000000ull;
+  }
+  return g_peer_wait_ns;
+}
+}  // namespace kb
+
 using namespace kb;
+
+// Bound (ms) of every later wait for another GPU; see peer.cuh.
+extern "C" int kb_set_peer_wait_ms(long ms) {
+  if (ms <= 0) return 7;
+  kb::g_peer_wait_ns = static_cast<uint64_t>(ms) * 1000000ull;
+  return 0;
+}
 
 static int clamp_grid(int sm_num) { return sm_num < 1 ? 1 : (sm_num > MAX_SIGNAL_CTAS ? MAX_SIGNAL_CTAS : sm_num); }
 static int clamp_block(int b) { return b < 32 ? 32 : (b > 1024 ? 1024 : (b / 32) * 32); }

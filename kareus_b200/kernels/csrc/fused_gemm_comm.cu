@@ -234,7 +234,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         coords(t, tm, tn);
         if (p.mode == MODE_AG && tm / tiles_per_rank != c.rank) {
           // remote rows: wait until the copy drivers have landed this tile in local memory
-          if (!wait_u32_ge(&p.ready[tm], p.epoch, false, status, ST_TIMEOUT_PEER, abort_flag)) { ok = false; break; }
+          if (!wait_u32_ge(&p.ready[tm], p.epoch, false, status, ST_TIMEOUT_PEER, abort_flag, c.wait_ns)) { ok = false; break; }
           fence_proxy_async_all();
         }
         const int m0 = tm * FG_BM, n0 = tn * BN;
@@ -304,7 +304,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       bool own = false;            // reduce-scatter: tile of this rank's own rows
       if (p.mode == MODE_RS) {
         if (!go_seen) {
-          if (!wait_u32_ge(p.go, p.epoch, false, status, ST_TIMEOUT_PEER, abort_flag)) { ok = false; break; }
+          if (!wait_u32_ge(p.go, p.epoch, false, status, ST_TIMEOUT_PEER, abort_flag, c.wait_ns)) { ok = false; break; }
           go_seen = true;
         }
         const int owner = tm / tiles_per_rank;
@@ -321,7 +321,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           if (lane < c.world && lane != c.rank) {
             const uint32_t* cnt = reinterpret_cast<const uint32_t*>(c.base[c.rank] + p.cnt_off) +
                                   (static_cast<long>(lane) * tiles_per_rank + (tm - owner * tiles_per_rank)) * tiles_n + tn;
-            got = wait_u32_ge(cnt, p.epoch * 4u, true, status, ST_TIMEOUT_PEER, abort_flag);
+            got = wait_u32_ge(cnt, p.epoch * 4u, true, status, ST_TIMEOUT_PEER, abort_flag, c.wait_ns);
           }
           if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
         }
@@ -469,6 +469,7 @@ static PeerCtx fused_ctx(void* const* bases, int rank, int world, uint64_t flag_
   PeerCtx c;
   for (int i = 0; i < MAX_PEERS; ++i) c.base[i] = i < world ? reinterpret_cast<uint8_t*>(bases[i]) : nullptr;
   c.rank = rank; c.world = world; c.flag_off = flag_off; c.status = status;
+  c.wait_ns = peer_wait_limit_ns();
   return c;
 }
 

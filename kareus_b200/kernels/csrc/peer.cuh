@@ -26,7 +26,13 @@ struct PeerCtx {
   uint64_t flag_off;          // byte offset (inside each heap) of this channel's flag block:
                               // uint64 flags[MAX_PEERS][MAX_SIGNAL_CTAS]
   int* status;
+  uint64_t wait_ns;           // bound of every wait on another GPU (host: peer_wait_limit_ns())
 };
+
+// Bound of a wait for a peer, in ns.  A peer may legitimately be late by as much as the kernels that
+// are queued in front of its matching launch need (another nanobatch's GEMM can hold every SM), so the
+// limit is a run-time setting: KAREUS_PEER_WAIT_MS (default 2000) or kb_set_peer_wait_ms().
+uint64_t peer_wait_limit_ns();
 
 __device__ __forceinline__ void st_release_sys(uint64_t* p, uint64_t v) {
   asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
@@ -55,14 +61,14 @@ __device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
 
 // Bounded polls.  `abort_flag` may be null (kernels without a CTA-wide abort flag).
 __device__ __forceinline__ bool wait_u64_ge(const uint64_t* p, uint64_t want, int* status, int code,
-                                            volatile int* abort_flag = nullptr) {
+                                            volatile int* abort_flag = nullptr, uint64_t limit_ns = KB_WAIT_NS) {
   if (ld_acquire_sys(p) >= want) return true;
   const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
   while (ld_acquire_sys(p) < want) {
     if ((++spins & 31u) == 0u) {
       if (abort_flag && *abort_flag) return false;
-      if (globaltimer_ns() - t0 > KB_WAIT_NS) {
+      if (globaltimer_ns() - t0 > limit_ns) {
         if (abort_flag) *abort_flag = 1;
         if (status) atomicCAS(status, 0, code);
         return false;
@@ -72,7 +78,7 @@ __device__ __forceinline__ bool wait_u64_ge(const uint64_t* p, uint64_t want, in
   return true;
 }
 __device__ __forceinline__ bool wait_u32_ge(const uint32_t* p, uint32_t want, bool sys_scope, int* status, int code,
-                                            volatile int* abort_flag = nullptr) {
+                                            volatile int* abort_flag = nullptr, uint64_t limit_ns = KB_WAIT_NS) {
   auto ld = [&]() { return sys_scope ? ld_acquire_sys_u32(p) : ld_acquire_gpu_u32(p); };
   if (static_cast<int32_t>(ld() - want) >= 0) return true;
   const uint64_t t0 = globaltimer_ns();
@@ -80,7 +86,7 @@ __device__ __forceinline__ bool wait_u32_ge(const uint32_t* p, uint32_t want, bo
   while (static_cast<int32_t>(ld() - want) < 0) {
     if ((++spins & 31u) == 0u) {
       if (abort_flag && *abort_flag) return false;
-      if (globaltimer_ns() - t0 > KB_WAIT_NS) {
+      if (globaltimer_ns() - t0 > limit_ns) {
         if (abort_flag) *abort_flag = 1;
         if (status) atomicCAS(status, 0, code);
         return false;
@@ -103,7 +109,7 @@ __device__ __forceinline__ bool peer_barrier(const PeerCtx& c, int cta, uint64_t
     uint64_t* remote = reinterpret_cast<uint64_t*>(c.base[peer] + c.flag_off) + c.rank * MAX_SIGNAL_CTAS + cta;
     st_release_sys(remote, value);
     const uint64_t* mine = reinterpret_cast<const uint64_t*>(c.base[c.rank] + c.flag_off) + peer * MAX_SIGNAL_CTAS + cta;
-    if (!wait_u64_ge(mine, value, c.status, ST_TIMEOUT_PEER)) *smem_ok = 0;
+    if (!wait_u64_ge(mine, value, c.status, ST_TIMEOUT_PEER, nullptr, c.wait_ns)) *smem_ok = 0;
   }
   __syncthreads();
   return *smem_ok != 0;

@@ -37,13 +37,51 @@ def one_f_one_b_order(pp: int, pp_rank: int, num_microbatches: int) -> List[Tupl
     return out
 
 
+class P2PStats:
+    """How long the compute stream stood still for pipeline receives.
+
+    A pair of CUDA events brackets every receive wait on the compute stream; their distance is the
+    time the stream could not run because the data (or the neighbour stage that produces it) was not
+    there yet — transfer time that compute did not hide plus pipeline bubble.  ``summary()``
+    synchronises and returns totals; the engine never reads it on its own."""
+
+    def __init__(self):
+        self.pairs = []
+        self.bytes = 0
+
+    def bracket(self, reqs, tensors):
+        if not reqs or not tensors or not tensors[0].is_cuda:
+            for r in reqs:
+                r.wait()
+            return
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for r in reqs:
+            r.wait()
+        b.record()
+        self.pairs.append((a, b))
+        self.bytes += sum(t.numel() * t.element_size() for t in tensors)
+
+    def summary(self, reset: bool = True) -> dict:
+        if self.pairs:
+            torch.cuda.synchronize()
+        out = {"receives": len(self.pairs), "stall_ms": sum(a.elapsed_time(b) for a, b in self.pairs),
+               "received_bytes": self.bytes}
+        if reset:
+            self.pairs, self.bytes = [], 0
+        return out
+
+
 class _Pending:
-    def __init__(self, tensors, reqs):
-        self.tensors, self.reqs = tensors, reqs
+    def __init__(self, tensors, reqs, stats: Optional[P2PStats] = None):
+        self.tensors, self.reqs, self.stats = tensors, reqs, stats
 
     def wait(self):
-        for r in self.reqs:
-            r.wait()
+        if self.stats is not None and self.tensors is not None:
+            self.stats.bracket(self.reqs, self.tensors)
+        else:
+            for r in self.reqs:
+                r.wait()
         self.reqs = []
         return self.tensors
 
@@ -58,6 +96,7 @@ class P2P:
         self.next = mesh.pp_neighbor(+1) if not mesh.is_last_stage else None
         self.group = mesh.group("pp")
         self._sends: List[_Pending] = []
+        self.stats: Optional[P2PStats] = None          # set to a P2PStats() to measure receive stalls
 
     def _bufs(self):
         return [torch.empty(s, dtype=self.dtype, device=self.device) for s in self.shapes]
@@ -82,7 +121,7 @@ class P2P:
         reqs = self._post(ops)
         if keep is not None:
             self._sends.append(_Pending(keep, reqs if bufs is None else []))
-        return _Pending(bufs, reqs) if bufs is not None else None
+        return _Pending(bufs, reqs, self.stats) if bufs is not None else None
 
     def finish_sends(self) -> None:
         for p in self._sends:

@@ -15,14 +15,14 @@ from typing import Dict, Optional, Tuple
 
 # --------------------------------------------------------------------------- GPUs
 # ``p2p_power_w`` is the static ("blocked in a p2p wait") board power that the planner
-# subtracts to get effective energy.  A100/A40 values are the reference's; the B200 value is a
-# placeholder until `kareus_b200.energy.p2p_probe` has measured it on the box in use.
+# subtracts to get effective energy.  A100/A40 values are the reference's; the B200 value was measured
+# with `kareus_b200.energy.p2p_probe` (20 s blocked in an NCCL receive, HGX B200, 1000 W limit: 251 W).
 GPU_CONFIGS: Dict[str, dict] = {
     "A40": {"p2p_power_w": 70.0, "freq_range": (900, 1740, 30)},
     "A100": {"p2p_power_w": 85.0, "freq_range": (900, 1410, 30)},
     # B200: 1965 MHz max SM clock; under dense GEMM the part is power limited near 1.3 GHz,
     # so the useful search range ends well below the maximum.
-    "B200": {"p2p_power_w": 190.0, "freq_range": (900, 1965, 75)},
+    "B200": {"p2p_power_w": 251.0, "freq_range": (900, 1965, 75)},
 }
 DEFAULT_GPU = "B200"
 

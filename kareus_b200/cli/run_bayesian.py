@@ -17,7 +17,8 @@ import torch
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--partition", default="fwd_attn")
+    ap.add_argument("--partition", default="fwd_attn",
+                    help="partition key, or 'all': every partition of the chosen --tp-comm flavour in one process")
     ap.add_argument("--nonpartition", action="store_true")
     ap.add_argument("-m", "--model_name", default="llama3.2_3b")
     ap.add_argument("-w", "--world_size", type=int, default=None)
@@ -81,29 +82,37 @@ def main(argv=None) -> int:
         return 0
 
     import copy
-    kind, space = partition_space(a.partition, a.tp_comm)
-    space = copy.deepcopy(space)
-    space.nano_values = list(a.nano)
+    from ..profile.space import CP_PARTITIONS, SP_FUSED_PARTITIONS, TP_PARTITIONS
+    if a.partition == "all":
+        parts = CP_PARTITIONS if cp > 1 else (SP_FUSED_PARTITIONS if a.tp_comm in ("sp", "sp_fused") else TP_PARTITIONS)
+    else:
+        parts = (a.partition,)
+    for part in parts:
+        kind, space = partition_space(part, a.tp_comm)
+        space = copy.deepcopy(space)
+        space.nano_values = list(a.nano)
 
-    def make_executor(nano: int):
-        par = ParallelConfig(tp=tp, cp=cp, num_nanobatches=nano, tp_comm=a.tp_comm, comm_backend=a.comm_backend,
-                             recompute=False)
-        return PartitionExecutor(cfg, par, a.partition, a.batch_size, a.seq_len, mesh=mesh,
-                                 comm=CommFactory(mesh, a.comm_backend, heap), device=device)
+        def make_executor(nano: int, part=part):
+            par = ParallelConfig(tp=tp, cp=cp, num_nanobatches=nano, tp_comm=a.tp_comm, comm_backend=a.comm_backend,
+                                 recompute=False)
+            return PartitionExecutor(cfg, par, part, a.batch_size, a.seq_len, mesh=mesh,
+                                     comm=CommFactory(mesh, a.comm_backend, heap), device=device)
 
-    ev = HardwareEvaluator(make_executor, monitor, ctl, world_size=world, measurement_duration=a.measure_s,
-                           cooldown_duration=a.cooldown_s)
-    logs = base / a.partition
-    if rank == 0:
-        print(f"[{a.partition}] {kind}; grid {len(space.grid(freqs))} configurations → {logs}")
-    # every rank runs the search with the same seed so all ranks measure the same configurations;
-    # only rank 0's files are kept
-    res = run_bo_search(space, freqs, ev, logs if rank == 0 else logs / f".rank{rank}", get_p2p_power(a.gpu_type),
-                        n_init=a.n_init, batches=a.batches, acq_batch=a.acq_batch,
-                        log=(print if rank == 0 else (lambda s: None)))
-    ev.close()
-    if rank == 0:
-        print(f"[{a.partition}] {len(res.records)} measurements, {len(res.pareto_effective)} on the effective frontier")
+        ev = HardwareEvaluator(make_executor, monitor, ctl, world_size=world, measurement_duration=a.measure_s,
+                               cooldown_duration=a.cooldown_s)
+        logs = base / part
+        if rank == 0:
+            print(f"[{part}] {kind}; grid {len(space.grid(freqs))} configurations → {logs}", flush=True)
+        # every rank runs the search with the same seed so all ranks measure the same configurations;
+        # only rank 0's files are kept
+        res = run_bo_search(space, freqs, ev, logs if rank == 0 else logs / f".rank{rank}", get_p2p_power(a.gpu_type),
+                            n_init=a.n_init, batches=a.batches, acq_batch=a.acq_batch,
+                            log=(print if rank == 0 else (lambda s: None)))
+        ev.close()
+        if rank == 0:
+            print(f"[{part}] {len(res.records)} measurements, {len(res.pareto_effective)} on the effective frontier",
+                  flush=True)
+    ctl.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -77,6 +77,33 @@ def read_prepost(base_dir, freqs: Sequence[int]) -> Dict[int, Dict[str, Tuple[fl
     return out
 
 
+# Fused sequence-parallel path: every reference key has a second partition (the all-gather→GEMM segment
+# in front of it) that a plan does not name; at run time it inherits the key's sm with the launch slot
+# "first" (plan/schedule.py).  Its measured cost therefore belongs to the key's point with the same sm.
+FUSED_CHILD = {"fwd_attn": "fwd_attn_ag", "fwd_mlp": "fwd_mlp_ag", "bwd_attn": "bwd_attn_ag", "bwd_mlp": "bwd_mlp_ag"}
+
+
+def merge_fused_partitions(maps: Dict[str, Dict[int, List[Point]]]) -> Dict[str, Dict[int, List[Point]]]:
+    """Fold the ``*_ag`` partitions of the fused path into their reference keys: for every clock and every
+    point of the key, add the child's point measured with the same sm (its fastest one if several launch
+    slots were tried); points whose sm the child was never measured at are dropped."""
+    out = {k: v for k, v in maps.items() if k not in FUSED_CHILD.values()}
+    for parent, child in FUSED_CHILD.items():
+        if child not in maps or parent not in maps:
+            continue
+        merged: Dict[int, List[Point]] = {}
+        for f, pts in maps[parent].items():
+            by_sm: Dict[int, Tuple[float, float]] = {}
+            for cfg, (t, e) in maps[child].get(f, []):
+                if cfg[2] not in by_sm or t < by_sm[cfg[2]][0]:
+                    by_sm[cfg[2]] = (t, e)
+            rows = [(cfg, (t + by_sm[cfg[2]][0], e + by_sm[cfg[2]][1])) for cfg, (t, e) in pts if cfg[2] in by_sm]
+            if rows:
+                merged[f] = rows
+        out[parent] = merged
+    return out
+
+
 def pareto_optimal(points: Sequence[Point], p2p_power: float, tol: float = 1e-4) -> List[Point]:
     best = float("inf")
     keep: List[Point] = []
@@ -219,6 +246,11 @@ def generate_profile_csv(model_name: str, tp: int, cp: int, pp: int, batch_size:
     context_parallel = cp > 1
     keys = (FWD_KEYS_CP + BWD_KEYS_CP) if context_parallel else (FWD_KEYS_TP + BWD_KEYS_TP)
     maps = {k: read_bo_jsonl(base / k / "eval_results.jsonl") for k in keys}
+    if not context_parallel:
+        for child in FUSED_CHILD.values():          # logs of the fused sequence-parallel path, if profiled
+            if (base / child / "eval_results.jsonl").exists():
+                maps[child] = read_bo_jsonl(base / child / "eval_results.jsonl")
+        maps = merge_fused_partitions(maps)
     freqs = set.intersection(*(set(m) for m in maps.values()))
     prepost = read_prepost(pre_base, sorted(freqs))
     first = cfg.num_layers_in_first_pipeline_stage

@@ -93,8 +93,10 @@ PARTITION_SPACES: Dict[str, Tuple[str, SearchSpace]] = {
 # is the fused kernel's knob: copy-driver CTAs for all-gather→GEMM kernels, SMs the kernel leaves to
 # the other nanobatch's compute for GEMM→reduce-scatter kernels (``csrc/fused_gemm_comm.cu``).  The
 # reference has no such partitions (its TP collectives are all-reduces: ``tests/bayesian/partitions``).
+# Both kinds sweep the same values: a plan file names ONE config per reference key (fwd_attn, ...), the
+# "_ag" segment of that key inherits its sm, so the composer pairs the two partitions' points by sm.
 _FUSED_AG_SM = [4, 8, 12, 16, 24, 32]
-_FUSED_RS_SM = [0, 8, 16, 24, 32, 48]
+_FUSED_RS_SM = [4, 8, 12, 16, 24, 32]
 SP_FUSED_SPACES: Dict[str, Tuple[str, SearchSpace]] = {
     "fwd_attn_ag": ("fused_ag_gemm", SearchSpace(_ow("norm_0"), _FUSED_AG_SM, 12, 2, 6)),
     "fwd_attn": ("fused_gemm_rs", SearchSpace(_ow("rope_0", "attn_0"), _FUSED_RS_SM, 16, 2, 8)),

@@ -219,3 +219,23 @@ def test_frequency_profile_from_timer_and_poller_files(tmp_path):
     t, e = got[(1, "backward", 1200)]
     assert abs(t - 2 * 0.23 * 1500 / 1200) < 1e-9
     assert abs(e - (420.0 * 2 * 0.22 + 430.0 * 2 * 0.23) * 1500 / 1200 / 2) < 1e-6
+
+
+def test_fused_path_partitions_fold_into_the_reference_keys():
+    """The all-gather→GEMM partition in front of a key is not named by a plan: it inherits the key's sm,
+    so its measured point with that sm is added to the key's point; other sm values drop out."""
+    from kareus_b200.compose.composer import merge_fused_partitions
+    maps = {
+        "fwd_attn": {1500: [(("rope_0", "none", 8, 1024), (1.0, 10.0)), (("attn_0", "none", 16, 1024), (0.9, 11.0)),
+                            (("attn_0", "none", 32, 1024), (0.8, 12.0))]},
+        "fwd_attn_ag": {1500: [(("norm_0", "none", 8, 1024), (0.5, 5.0)), (("norm_0", "none", 16, 1024), (0.4, 6.0)),
+                               (("first", "none", 16, 1024), (0.45, 5.5))]},
+        "fwd_mlp": {1500: [(("activation_0", "none", 8, 1024), (2.0, 20.0))]},
+    }
+    out = merge_fused_partitions(maps)
+    assert set(out) == {"fwd_attn", "fwd_mlp"}
+    got = dict(out["fwd_attn"][1500])
+    assert got[("rope_0", "none", 8, 1024)] == (1.5, 15.0)
+    assert got[("attn_0", "none", 16, 1024)] == (0.9 + 0.4, 11.0 + 6.0)          # child's faster point at sm 16
+    assert ("attn_0", "none", 32, 1024) not in got                                # child never measured at 32
+    assert out["fwd_mlp"] == maps["fwd_mlp"]                                      # no child logs: unchanged

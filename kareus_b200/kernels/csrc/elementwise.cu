@@ -69,12 +69,17 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
 
 // ----------------------------------------------------------------------------- RMSNorm
 // One CTA per row; H multiple of 8; each thread keeps up to VPT vectors of the row in registers.
-constexpr int NORM_THREADS = 256;
-constexpr int NORM_VPT = 4;  // rows up to 256*4*8 = 8192 wide stay in registers
+constexpr int NORM_MAX_H = 256 * 4 * 8;   // widest row the register-resident kernels take (8192)
 
-__global__ void __launch_bounds__(NORM_THREADS)
+// THREADS x VPT vectors of 8 elements are kept in registers; the launcher picks the smallest variant that
+// covers the row, so that narrow rows (3072: 384 threads x 1 vector) neither idle half of a 256-thread
+// block nor carry register arrays sized for 8192-wide rows (which capped occupancy at 25 %).
+template <int THREADS, int VPT>
+__global__ void __launch_bounds__(THREADS)
 rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                    __nv_bfloat16* __restrict__ y, float* __restrict__ rstd, int rows, int H, float eps) {
+  constexpr int NORM_THREADS = THREADS;
+  constexpr int NORM_VPT = VPT;
   __shared__ float red[32];
   const int nvec = H >> 3;
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
@@ -149,10 +154,13 @@ __global__ void rmsnorm_fwd_warp_kernel(const __nv_bfloat16* __restrict__ x, con
 
 // Backward: dx per row; dw partial sums per CTA into `partial[gridDim.x][H]` (scratch), reduced by
 // rmsnorm_dw_reduce_kernel.  The grid is persistent (a few CTAs per SM) so `partial` stays small.
-__global__ void __launch_bounds__(NORM_THREADS)
+template <int THREADS, int VPT>
+__global__ void __launch_bounds__(THREADS)
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                    const float* __restrict__ rstd, const __nv_bfloat16* __restrict__ w,
                    __nv_bfloat16* __restrict__ dx, float* __restrict__ partial, int rows, int H) {
+  constexpr int NORM_THREADS = THREADS;
+  constexpr int NORM_VPT = VPT;
   __shared__ float red[32];
   const int nvec = H >> 3;
   float dwacc[NORM_VPT][8];
@@ -279,6 +287,57 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ q, long qs_s, long qs_b,
       *reinterpret_cast<__nv_bfloat162*>(p + i) = __floats2bfloat162_rn(af.x * c0 - cf.x * s0, af.y * c1 - cf.y * s1);
       *reinterpret_cast<__nv_bfloat162*>(p + half + i) =
           __floats2bfloat162_rn(cf.x * c0 + af.x * s0, cf.y * c1 + af.y * s1);
+    }
+  }
+}
+
+// Vectorised variant for head dims that are multiples of 16 (all models here: 128).  One warp owns one
+// token (s, b): D/16 lanes form a group that rotates one head vector, 16 bytes from each half per lane,
+// and the groups of the warp walk the token's heads.  The lane's 8 cos and 8 sin values are loaded once
+// per token and stay in registers for all heads, so table traffic is amortised over the heads and every
+// global access is a 16-byte vector.
+__global__ void __launch_bounds__(256)
+rope_vec_kernel(__nv_bfloat16* __restrict__ q, long qs_s, long qs_b, long qs_g, long qs_r, int G, int R,
+                __nv_bfloat16* __restrict__ k, long ks_s, long ks_b, long ks_g, int KG,
+                const float* __restrict__ cosb, const float* __restrict__ sinb, int S, int B, int D, float sign) {
+  const int lanes_per_head = D >> 4;                 // 8 for D = 128
+  const int groups = 32 / lanes_per_head;
+  const int lane = threadIdx.x & 31;
+  const int grp = lane / lanes_per_head;
+  const int l = lane - grp * lanes_per_head;
+  const int half = D >> 1;
+  const int qh = G * R, heads = qh + KG;
+  const long tokens = static_cast<long>(S) * B;
+  for (long tok = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; tok < tokens;
+       tok += (static_cast<long>(gridDim.x) * blockDim.x) >> 5) {
+    const int b = static_cast<int>(tok % B);
+    const int s = static_cast<int>(tok / B);
+    float c[8], sn[8];
+    {
+      const float4* cr = reinterpret_cast<const float4*>(cosb + static_cast<long>(s) * half + l * 8);
+      const float4* sr = reinterpret_cast<const float4*>(sinb + static_cast<long>(s) * half + l * 8);
+      const float4 c0 = cr[0], c1 = cr[1], s0 = sr[0], s1 = sr[1];
+      c[0] = c0.x; c[1] = c0.y; c[2] = c0.z; c[3] = c0.w; c[4] = c1.x; c[5] = c1.y; c[6] = c1.z; c[7] = c1.w;
+      sn[0] = s0.x * sign; sn[1] = s0.y * sign; sn[2] = s0.z * sign; sn[3] = s0.w * sign;
+      sn[4] = s1.x * sign; sn[5] = s1.y * sign; sn[6] = s1.z * sign; sn[7] = s1.w * sign;
+    }
+    __nv_bfloat16* qrow = q + s * qs_s + b * qs_b;
+    __nv_bfloat16* krow = k + s * ks_s + b * ks_b;
+#pragma unroll 2
+    for (int h = grp; h < heads; h += groups) {
+      __nv_bfloat16* p = h < qh ? qrow + (h / R) * qs_g + (h % R) * qs_r : krow + (h - qh) * ks_g;
+      uint4* lo = reinterpret_cast<uint4*>(p + l * 8);
+      uint4* hi = reinterpret_cast<uint4*>(p + half + l * 8);
+      float a[8], d[8], o1[8], o2[8];
+      unpack8(*lo, a);
+      unpack8(*hi, d);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        o1[i] = a[i] * c[i] - d[i] * sn[i];
+        o2[i] = d[i] * c[i] + a[i] * sn[i];
+      }
+      *lo = pack8(o1);
+      *hi = pack8(o2);
     }
   }
 }
@@ -548,6 +607,26 @@ __global__ void sumsq_bf16_kernel(const __nv_bfloat16* __restrict__ x, long n, f
   if (threadIdx.x == 0) atomicAdd(out, tot);
 }
 
+// Variant of the RMSNorm kernels for a row of H elements: threads per CTA, vectors per thread and how
+// many CTAs of it fit an SM (register budget of the backward kernel).
+struct NormVariant { int id, threads, vpt, ctas_per_sm; };
+static inline NormVariant norm_variant(int H) {
+  const int nvec = H >> 3;
+  if (nvec <= 128) return {0, 128, 1, 8};
+  if (nvec <= 256) return {1, 256, 1, 4};
+  if (nvec <= 384) return {2, 384, 1, 3};
+  if (nvec <= 512) return {3, 256, 2, 3};
+  return {4, 256, 4, 2};
+}
+#define KB_NORM_DISPATCH(variant, CALL)           \
+  switch ((variant).id) {                         \
+    case 0: { CALL(128, 1); break; }              \
+    case 1: { CALL(256, 1); break; }              \
+    case 2: { CALL(384, 1); break; }              \
+    case 3: { CALL(256, 2); break; }              \
+    default: { CALL(256, 4); break; }             \
+  }
+
 static inline int grid_for(long work, int threads, int max_blocks) {
   long b = (work + threads - 1) / threads;
   if (b < 1) b = 1;
@@ -563,8 +642,13 @@ using namespace kb;
 extern "C" int kb_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int rows, int H, float eps,
                               cudaStream_t st) {
   if (H % 8 == 0 && H >= 512) {
-    KB_LAUNCH(rmsnorm_fwd_kernel, grid_for(rows, 1, 148 * 8), NORM_THREADS, 0, st, 
-        (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, rstd, rows, H, eps);
+    const NormVariant nv = norm_variant(H);
+    const int grid = grid_for(rows, 1, 148 * 2 * nv.ctas_per_sm);
+#define KB_FWD(T_, V_)                                                                                            \
+    KB_LAUNCH((rmsnorm_fwd_kernel<T_, V_>), grid, T_, 0, st, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w,      \
+              (__nv_bfloat16*)y, rstd, rows, H, eps)
+    KB_NORM_DISPATCH(nv, KB_FWD)
+#undef KB_FWD
   } else {
     KB_LAUNCH(rmsnorm_fwd_warp_kernel, grid_for(rows, 8, 148 * 8), 256, 0, st, 
         (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, rstd, rows, H, eps);
@@ -574,7 +658,7 @@ extern "C" int kb_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd
 
 // Number of fp32 elements of scratch that kb_rmsnorm_bwd needs for a given H (0 for narrow rows).
 extern "C" long kb_rmsnorm_bwd_scratch_elems(int rows, int H) {
-  if (H % 8 == 0 && H >= 512 && H <= NORM_THREADS * NORM_VPT * 8) return (long)grid_for(rows, 1, 148 * 2) * H;
+  if (H % 8 == 0 && H >= 512 && H <= NORM_MAX_H) return (long)grid_for(rows, 1, 148 * norm_variant(H).ctas_per_sm) * H;
   return 0;
 }
 
@@ -582,11 +666,15 @@ extern "C" long kb_rmsnorm_bwd_scratch_elems(int rows, int H) {
 // added to dw (callers pass the weight's fp32 main gradient and save a separate add).
 extern "C" int kb_rmsnorm_bwd_acc(const void* dy, const void* x, const float* rstd, const void* w, void* dx, float* dw,
                                   float* scratch, int rows, int H, int accumulate, cudaStream_t st) {
-  if (H % 8 == 0 && H >= 512 && H <= NORM_THREADS * NORM_VPT * 8) {
-    const int grid = grid_for(rows, 1, 148 * 2);
+  if (H % 8 == 0 && H >= 512 && H <= NORM_MAX_H) {
+    const NormVariant nv = norm_variant(H);
+    const int grid = grid_for(rows, 1, 148 * nv.ctas_per_sm);      // must match kb_rmsnorm_bwd_scratch_elems
     if (!scratch) return 7;
-    KB_LAUNCH(rmsnorm_bwd_kernel, grid, NORM_THREADS, 0, st, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, rstd,
-                                                      (const __nv_bfloat16*)w, (__nv_bfloat16*)dx, scratch, rows, H);
+#define KB_BWD(T_, V_)                                                                                              \
+    KB_LAUNCH((rmsnorm_bwd_kernel<T_, V_>), grid, T_, 0, st, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, rstd, \
+              (const __nv_bfloat16*)w, (__nv_bfloat16*)dx, scratch, rows, H)
+    KB_NORM_DISPATCH(nv, KB_BWD)
+#undef KB_BWD
     KB_LAUNCH(rmsnorm_dw_reduce_kernel, (H + 255) / 256, 256, 0, st, scratch, dw, grid, H, accumulate);
   } else {
     if (!accumulate) kb::memset_async(dw, 0, sizeof(float) * H, st);    // the kernel adds with atomics
@@ -606,6 +694,18 @@ extern "C" int kb_rope(void* q, long qs_s, long qs_b, long qs_g, long qs_r, int 
                        long ks_b, long ks_g, int KG, const float* cosb, const float* sinb, int S, int B, int D,
                        int inverse, cudaStream_t st) {
   if (D % 4) return 7;
+  {
+    // 16-byte vectors need 16-byte aligned head rows: every stride a multiple of 8 elements
+    const bool al = ((qs_s | qs_b | qs_g | qs_r | ks_s | ks_b | ks_g) & 7) == 0 &&
+                    (reinterpret_cast<uintptr_t>(q) & 15) == 0 && (k == nullptr || (reinterpret_cast<uintptr_t>(k) & 15) == 0);
+    if (al && D % 16 == 0 && D >= 16 && D <= 512 && (32 % (D / 16)) == 0) {
+      const long tokens = (long)S * B;
+      KB_LAUNCH(rope_vec_kernel, grid_for(tokens * 32, 256, 148 * 8), 256, 0, st,
+          (__nv_bfloat16*)q, qs_s, qs_b, qs_g, qs_r, G, R, (__nv_bfloat16*)k, ks_s, ks_b, ks_g, KG, cosb, sinb, S, B, D,
+          inverse ? -1.f : 1.f);
+      KB_CHECK_LAUNCH();
+    }
+  }
   const long warps = (long)S * B * (G * R + KG);
   KB_LAUNCH(rope_kernel, grid_for(warps * 32, 256, 148 * 16), 256, 0, st, 
       (__nv_bfloat16*)q, qs_s, qs_b, qs_g, qs_r, G, R, (__nv_bfloat16*)k, ks_s, ks_b, ks_g, KG, cosb, sinb, S, B, D,
@@ -707,7 +807,7 @@ extern "C" int kb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const float
   }
   float* partial = g_rmsnorm_bwd_partial_addr[dev];
   const int grid = rows < NOALLOC_MAX_CTAS ? rows : NOALLOC_MAX_CTAS;
-  KB_LAUNCH(rmsnorm_bwd_kernel, grid, NORM_THREADS, 0, st, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, rstd,
+  KB_LAUNCH((rmsnorm_bwd_kernel<256, 4>), grid, 256, 0, st, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, rstd,
                                                     (const __nv_bfloat16*)w, (__nv_bfloat16*)dx, partial, rows, H);
   KB_LAUNCH(rmsnorm_dw_reduce_kernel, (H + 255) / 256, 256, 0, st, partial, dw, grid, H, 0);
   KB_CHECK_LAUNCH();

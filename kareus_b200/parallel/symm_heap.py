@@ -126,7 +126,8 @@ class SymmetricHeap:
         self.guards = GuardMap()
         self.channels: Dict[str, Channel] = {}
         self._views: Dict[tuple, torch.Tensor] = {}
-        self.closed = False
+        self.nvls = None               # NvlsBuffer once enable_nvls() has run: all-reduce / reduce-scatter go
+        self.closed = False            # through the NVLink switch (multimem) instead of peer loads
         if world > 1:
             dist.barrier(group=group)
 
@@ -155,6 +156,20 @@ class SymmetricHeap:
         for n in ("kb_heap_alloc", "kb_ipc_get_handle", "kb_ipc_open", "kb_ipc_close", "kb_heap_free", "kb_allreduce",
                   "kb_allgather", "kb_reducescatter", "kb_wait_flag"):
             getattr(L, n).restype = c_int
+
+    def enable_nvls(self, nbytes: int = 1 << 30) -> bool:
+        """Collective.  Bind ``nbytes`` per rank to an NVLink-switch multicast object and route all-reduce
+        and reduce-scatter through it (see :mod:`kareus_b200.parallel.nvls`).  Returns False (and changes
+        nothing) when a device of the group lacks multicast support."""
+        from .nvls import NvlsBuffer
+        if self.world < 2 or self.nvls is not None:
+            return self.nvls is not None
+        ok = torch.tensor([1 if NvlsBuffer.supported(self.device) else 0], device=self.device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
+        if int(ok.item()) != 1:
+            return False
+        self.nvls = NvlsBuffer.create(self, nbytes)
+        return True
 
     # ------------------------------------------------------------------ allocation
     def channel(self, name: str, flag_bytes: int = FLAG_BLOCK) -> Channel:
@@ -241,6 +256,9 @@ class SymmetricHeap:
 
     def all_reduce(self, x: torch.Tensor, nb: int = 0, sm_num=None, block_size=None, tag: str = "ar") -> torch.Tensor:
         self._require_bf16(x, "all_reduce")
+        if self.nvls is not None and x.numel() % 8 == 0:
+            sm, blk = self._launch_shape(sm_num, block_size)
+            return self.nvls.all_reduce(x, tag=f"{tag}/{nb}", sm_num=sm, block_size=blk)
         ch = self.channel(f"{tag}/{nb}")
         n = x.numel()
         off, _ = self.buffer(ch, "x", n * x.element_size())
@@ -258,10 +276,12 @@ class SymmetricHeap:
     def staging(self, kind: str, tag: str, nb: int, shape, dtype) -> torch.Tensor:
         """The heap buffer a collective would copy its input into; a producer that writes its result
         there (``gemm(..., out=...)``) saves the copy.  ``kind``: ``"ar"`` or ``"rs"``."""
-        ch = self.channel(f"{tag}/{nb}")
         n = 1
         for s_ in shape:
             n *= s_
+        if self.nvls is not None and dtype == torch.bfloat16 and n % (8 * self.world) == 0:
+            return self.nvls.staging(f"{tag}/{nb}", shape, dtype)
+        ch = self.channel(f"{tag}/{nb}")
         off, _ = self.buffer(ch, "x", n * torch.empty((), dtype=dtype).element_size())
         return self.view(off, shape, dtype)
 
@@ -284,6 +304,9 @@ class SymmetricHeap:
 
     def reduce_scatter(self, x: torch.Tensor, nb: int = 0, sm_num=None, block_size=None, tag: str = "rs") -> torch.Tensor:
         self._require_bf16(x, "reduce_scatter")
+        if self.nvls is not None and (x.numel() // self.world) % 8 == 0 and x.shape[0] % self.world == 0:
+            sm, blk = self._launch_shape(sm_num, block_size)
+            return self.nvls.reduce_scatter(x, tag=f"{tag}/{nb}", sm_num=sm, block_size=blk)
         ch = self.channel(f"{tag}/{nb}")
         n = x.numel()
         off, _ = self.buffer(ch, "x", n * x.element_size())
@@ -347,6 +370,9 @@ class SymmetricHeap:
         if self.closed:
             return
         self.closed = True
+        if self.nvls is not None:
+            self.nvls.close()
+            self.nvls = None
         torch.cuda.synchronize(self.device)
         for r, b in enumerate(self.bases):
             if r != self.rank:

@@ -98,6 +98,42 @@ def test_fused_gemm_collectives(heap, rank, world, dev):
         assert rel(w.main_grad, dyg.float().reshape(-1, n).t() @ a.float().reshape(-1, k)) < 2e-2
 
 
+def test_nvls_collectives(heap, rank, world, dev):
+    """All-reduce and reduce-scatter through the NVLink switch (multimem) vs NCCL.  The multicast binding is
+    always undone before the process ends."""
+    from kareus_b200.kernels import cuda as KC
+    if not heap.enable_nvls(256 << 20):
+        if rank == 0:
+            print("switch multicast not supported here: skipped", flush=True)
+        return
+    try:
+        g = torch.Generator(device=dev).manual_seed(7 + rank)
+        for shape in [(1024, 2, 512), (4096, 1, 3072), (world * 64, 8)]:
+            x = torch.randn(shape, device=dev, generator=g).bfloat16()
+            want = x.clone()
+            dist.all_reduce(want)
+            for rep in range(3):
+                got = heap.all_reduce(x.clone(), nb=0, sm_num=8, block_size=512, tag=f"n_ar{shape[0]}")
+                torch.cuda.synchronize()
+                KC.check_status()
+                assert rel(got, want) < 2e-2, ("nvls all_reduce", shape, rep, rel(got, want))
+            ws = torch.empty((shape[0] // world,) + shape[1:], device=dev, dtype=torch.bfloat16)
+            dist.reduce_scatter_tensor(ws, x.clone())
+            gs = heap.reduce_scatter(x, nb=1, sm_num=6, block_size=1024, tag=f"n_rs{shape[0]}")
+            torch.cuda.synchronize()
+            KC.check_status()
+            assert rel(gs, ws) < 2e-2, ("nvls reduce_scatter", shape, rel(gs, ws))
+        # a producer writes straight into the collective's bound input buffer
+        st = heap.staging("ar", "n_stage", 0, (2048, 8), torch.bfloat16)
+        st.fill_(float(rank + 1))
+        y = heap.all_reduce(st, nb=0, sm_num=4, tag="n_stage")
+        torch.cuda.synchronize()
+        assert torch.all(y == world * (world + 1) / 2)
+    finally:
+        heap.nvls.close()
+        heap.nvls = None
+
+
 def test_bounded_wait(heap, dev):
     from kareus_b200.kernels import cuda as KC
     heap.wait_flag_probe(limit_ns=100_000_000)
@@ -192,6 +228,8 @@ def main():
         test_fused_gemm_collectives(heap, rank, world, dev)
     if which in ("all", "ring"):
         test_ring_attention(heap, rank, world, dev)
+    if which == "nvls":
+        test_nvls_collectives(heap, rank, world, dev)
     if which in ("all", "wait"):
         test_bounded_wait(heap, dev)
     if which in ("all", "model"):

@@ -20,7 +20,7 @@ def _run(which, n):
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
-@pytest.mark.parametrize("which", ["collectives", "fused", "ring", "wait", "model"])
+@pytest.mark.parametrize("which", ["collectives", "fused", "ring", "wait", "model", "nvls"])
 def test_multi_gpu(which, world):
     """Every case at 2, 4 and 8 ranks (own-row epilogue with up to 7 peers, rank-rotated tile order,
     half-GPU co-residency of the fused kernels); a box with fewer GPUs skips the larger worlds."""
@@ -28,4 +28,6 @@ def test_multi_gpu(which, world):
         pytest.skip(f"needs {world} GPUs")
     if which == "wait" and world > 2:
         pytest.skip("the bounded-wait probe involves no peer; covered at 2 ranks")
+    if which == "nvls" and world not in (2, 8):
+        pytest.skip("switch multicast is checked at 2 ranks and on the whole box")
     _run(which, world)

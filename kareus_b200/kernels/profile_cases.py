@@ -125,19 +125,22 @@ def fused_table() -> None:
     if pk.exists():
         peak = float(json.loads(pk.read_text()).get("bf16_tflops", 1669.2)) * 1e12
     sm = int(os.environ.get("KAREUS_COMM_SM", "12" if world >= 4 else "16"))
+    # per-rank shapes of tensor-parallel degree `tp` (default: the number of ranks; KAREUS_TABLE_TP runs
+    # another degree's shapes on this many ranks, e.g. the TP8 shapes on two GPUs)
+    tp = int(os.environ.get("KAREUS_TABLE_TP", str(world)))
     M, H, F, HEADS, KV, D = 16384, 3072, 8192, 24, 8, 128
-    q_out, f_out = (HEADS + 2 * KV) * D // world, 2 * F // world
+    q_out, f_out = (HEADS + 2 * KV) * D // tp, 2 * F // tp
     # name -> (in_features, out_features, class, kind of collective, is backward)
     cases = [("qkv fwd: AG->GEMM", H, q_out, FusedAGGemm, "ag"), ("fc1 fwd: AG->GEMM", H, f_out, FusedAGGemm, "ag"),
-             ("proj fwd: GEMM->RS", HEADS * D // world, H, FusedGemmRS, "rs"),
-             ("fc2 fwd: GEMM->RS", F // world, H, FusedGemmRS, "rs"),
+             ("proj fwd: GEMM->RS", HEADS * D // tp, H, FusedGemmRS, "rs"),
+             ("fc2 fwd: GEMM->RS", F // tp, H, FusedGemmRS, "rs"),
              ("qkv bwd: dgrad->RS", H, q_out, FusedDgradRS, "rs"), ("fc1 bwd: dgrad->RS", H, f_out, FusedDgradRS, "rs"),
-             ("proj bwd: AG->dgrad", HEADS * D // world, H, FusedAGDgrad, "ag"),
-             ("fc2 bwd: AG->dgrad", F // world, H, FusedAGDgrad, "ag")]
+             ("proj bwd: AG->dgrad", HEADS * D // tp, H, FusedAGDgrad, "ag"),
+             ("fc2 bwd: AG->dgrad", F // tp, H, FusedAGDgrad, "ag")]
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     if rank == 0:
-        print(f"| kernel (TP{world}, M={M}, {sm} comm CTAs) | N | K | us | GEMM TFLOP/s | NVLink GB/s/dir | roofline us "
-              "(gemm, link) | fraction |\n|---|---|---|---|---|---|---|---|")
+        print(f"| kernel (TP{tp} shapes on {world} ranks, M={M}, {sm} comm CTAs) | N | K | us | GEMM TFLOP/s | "
+              "NVLink GB/s/dir | roofline us (gemm, link) | fraction | plain GEMM us |\n|---|---|---|---|---|---|---|---|---|")
     for name, k_in, n_out, cls, kind in cases:
         w = (torch.randn(n_out, k_in, device=dev) * 0.02).bfloat16()
         w.main_grad = torch.zeros(n_out, k_in, device=dev)
@@ -178,12 +181,16 @@ def fused_table() -> None:
                 times.append(t.item())
         times.sort()
         ms = times[len(times) // 2]
+        # the same GEMM without any collective (whole GPU), for the cost of the communication inside the kernel
+        xa = torch.randn(M, red, device=dev).bfloat16()
+        plain = _timed(lambda: KC.gemm(xa, w, trans_b=not bwd), flush) * 1e3
+        del xa
         flops = 2.0 * M * out * red
         link = (world - 1) / world * M * (red if kind == "ag" else out) * 2
         t_gemm, t_link = flops / peak * 1e6, link / 770e9 * 1e6
         if rank == 0:
             print(f"| {name} | {out} | {red} | {ms * 1e3:.0f} | {flops / 1e9 / ms:.0f} | {link / 1e6 / ms:.0f} | "
-                  f"{t_gemm:.0f}, {t_link:.0f} | {max(t_gemm, t_link) / (ms * 1e3):.2f} |", flush=True)
+                  f"{t_gemm:.0f}, {t_link:.0f} | {max(t_gemm, t_link) / (ms * 1e3):.2f} | {plain:.0f} |", flush=True)
         del w, x
     KC.check_status()
     dist.barrier()

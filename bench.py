@@ -169,9 +169,24 @@ def main() -> int:
     if tp > 1 and (args.comm_backend == "kernel" or args.tp_comm == "sp_fused"):
         from kareus_b200.parallel.symm_heap import SymmetricHeap
         heap = SymmetricHeap.create(mesh.group("tp"), device)
+        if os.environ.get("KAREUS_NVLS", "0") == "1":
+            # fused kernels and heap collectives go through the NVLink switch (multimem) where supported
+            heap.enable_nvls(int(os.environ.get("KAREUS_NVLS_BYTES", str(3 << 30))))
     if args.cp > 1 and args.cp_comm == "ring":
         from kareus_b200.parallel.symm_heap import SymmetricHeap
         heap_cp = SymmetricHeap.create(mesh.group("cp"), device, size_bytes=2 << 30)
+
+    import atexit
+
+    def _release_heaps():
+        # a rank that leaves on an error must still unbind its switch-multicast memory (no barriers here)
+        for h in (heap, heap_cp):
+            if h is not None and not h.closed:
+                try:
+                    h.close(collective=False)
+                except Exception:
+                    pass
+    atexit.register(_release_heaps)
 
     def make_trainer(tp_comm, comm_backend):
         par = ParallelConfig(tp=tp, cp=args.cp, dp=dp, pp=args.pp, num_nanobatches=args.nano,
@@ -354,6 +369,9 @@ def main() -> int:
             "impl": "ours",
         }
         print(json.dumps(out))
+    for h in (heap, heap_cp):
+        if h is not None:
+            h.close()          # collective: unbinds switch multicast memory before any rank leaves
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -26,6 +26,15 @@
 //   so that the other nanobatch's kernels on the compute stream keep that many SMs while this
 //   link-bound kernel runs (0: use the whole budget).  There are no separate reducer CTAs: the sums
 //   are finished in the own-row epilogues.
+//
+// Switch-multicast variants (kb_ag_gemm_mc_bf16 / kb_gemm_rs_mc_bf16; buffers inside an NVLS buffer,
+// parallel/nvls.py).  The SMs then touch NVLink far less:
+// * ag_gemm: the drivers PUSH this rank's own shard once with multimem.st; the switch replicates it
+//   into all ranks' gathered buffers (posted writes, 1/7 of the bytes per sending SM) and a
+//   multimem.red bumps the tile's ready flag everywhere.
+// * gemm_rs: every partial tile is stored to LOCAL staging (the epilogue runs at plain-GEMM speed, the
+//   release that precedes the tile counter covers local writes only), and the owner fetches each of
+//   its tiles already summed over all ranks with multimem.ld_reduce.
 // Every wait is bounded (status word + return).  Role of the reference's separate cuBLASLt GEMM followed
 // or preceded by an all-reduce kernel (kareus/megatron/core/extensions/ops/te_linear.py:303-445,
 // 3rdparty/mscclpp/python/mscclpp_benchmark/allreduce.cu:155-246).
@@ -62,6 +71,11 @@ struct FusedParams {
   uint64_t cnt_off;       // counters [world][Ms/128][tiles_n] (uint32) in every heap
   uint32_t* go;           // local flag: peers have entered this call
   __nv_bfloat16* out;     // [Ms, N]
+  // switch-multicast variants: local and multicast view of the NVLS buffer (null: peer loads/stores);
+  // xg_off / stage_off / ready_off are then offsets inside that buffer
+  uint8_t* uc;
+  uint8_t* mc;
+  uint64_t ready_off;     // AG: uint32 per 128-row tile, bumped on every rank by the tile's sender
 };
 
 template <int BN>
@@ -139,6 +153,36 @@ __device__ void ag_copy_role(const FusedParams& p, int K, uint8_t* smem, uint64_
   peer_barrier(c, cta, static_cast<uint64_t>(p.epoch) * 4 + 2, ok_slot);
 }
 
+// ----------------------------------------------------------------------------- push driver (AG, multicast)
+// This rank's own shard, tile by tile, to every rank's gathered buffer through the switch.
+__device__ void ag_push_role(const FusedParams& p, int K, int* ok_slot) {
+  const PeerCtx& c = p.peer;
+  const int cta = blockIdx.x;
+  // every rank has entered this call: the previous contents of all gathered buffers have been consumed
+  if (!peer_barrier(c, cta, static_cast<uint64_t>(p.epoch) * 4 + 1, ok_slot)) return;
+  const long tile_vecs = static_cast<long>(FG_BM) * K * 2 / 16;
+  const int tiles_per_rank = p.rows_per_rank / FG_BM;
+  for (int lt = cta; lt < tiles_per_rank; lt += p.n_first) {
+    const int tile = c.rank * tiles_per_rank + lt;
+    const uint4* src = reinterpret_cast<const uint4*>(p.uc + p.xg_off) + tile * tile_vecs;
+    uint4* dst = reinterpret_cast<uint4*>(p.mc + p.xg_off) + tile * tile_vecs;
+    long i = threadIdx.x;
+    for (; i + 3 * FG_THREADS < tile_vecs; i += 4 * FG_THREADS) {
+      const uint4 a = src[i], b = src[i + FG_THREADS], d = src[i + 2 * FG_THREADS], e = src[i + 3 * FG_THREADS];
+      mm_st_bf16x8(dst + i, a);
+      mm_st_bf16x8(dst + i + FG_THREADS, b);
+      mm_st_bf16x8(dst + i + 2 * FG_THREADS, d);
+      mm_st_bf16x8(dst + i + 3 * FG_THREADS, e);
+    }
+    for (; i < tile_vecs; i += FG_THREADS) mm_st_bf16x8(dst + i, src[i]);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      fence_sys();      // the tile's stores (cumulative over the CTA through the barrier) before its flag
+      mm_red_add_u32(p.mc + p.ready_off + static_cast<uint64_t>(tile) * 4, 1u);
+    }
+  }
+}
+
 // ----------------------------------------------------------------------------- kernel
 // B_MN: the weight operand is stored [K rows][N contiguous] (dgrad: dY·W with W as [N_red, K_out]).
 template <int BN, bool B_MN>
@@ -177,7 +221,8 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       mbar_fence_init();
     }
     __syncthreads();
-    ag_copy_role(p, K, smem, ring_bars, ring_abort, ring_ok);
+    if (p.mc != nullptr) ag_push_role(p, K, ring_ok);
+    else ag_copy_role(p, K, smem, ring_bars, ring_abort, ring_ok);
     return;
   }
   if (static_cast<int>(blockIdx.x) >= p.n_first + p.n_gemm) {
@@ -234,7 +279,11 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         coords(t, tm, tn);
         if (p.mode == MODE_AG && tm / tiles_per_rank != c.rank) {
           // remote rows: wait until the copy drivers have landed this tile in local memory
-          if (!wait_u32_ge(&p.ready[tm], p.epoch, false, status, ST_TIMEOUT_PEER, abort_flag, c.wait_ns)) { ok = false; break; }
+          // (multicast: the flag was bumped by the sending rank, so the poll is system scope)
+          if (!wait_u32_ge(&p.ready[tm], p.epoch, p.mc != nullptr, status, ST_TIMEOUT_PEER, abort_flag, c.wait_ns)) {
+            ok = false;
+            break;
+          }
           fence_proxy_async_all();
         }
         const int m0 = tm * FG_BM, n0 = tn * BN;
@@ -302,6 +351,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       const uint32_t taddr = tmem_base + buf * BN + (static_cast<uint32_t>(q * 32) << 16);
       __nv_bfloat16* cbase;        // row 0 of this warp's 32 rows in the destination
       bool own = false;            // reduce-scatter: tile of this rank's own rows
+      bool own_mc = false;         // ... in the multicast variant (summed fetch after the local store)
       if (p.mode == MODE_RS) {
         if (!go_seen) {
           if (!wait_u32_ge(p.go, p.epoch, false, status, ST_TIMEOUT_PEER, abort_flag, c.wait_ns)) { ok = false; break; }
@@ -309,7 +359,12 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         }
         const int owner = tm / tiles_per_rank;
         own = owner == c.rank;
-        if (!own) {
+        if (p.mc != nullptr) {
+          // multicast: every partial tile goes to LOCAL staging [M, N]; own tiles are fetched summed below
+          cbase = reinterpret_cast<__nv_bfloat16*>(p.uc + p.stage_off) + static_cast<long>(m0 + q * 32) * N;
+          own_mc = own;
+          own = false;
+        } else if (!own) {
           __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(c.base[owner] + p.stage_off) +
                                  static_cast<long>(c.rank) * p.rows_per_rank * N;
           cbase = stage + static_cast<long>(m0 + q * 32 - owner * p.rows_per_rank) * N;
@@ -418,7 +473,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[buf]);
-      if (p.mode == MODE_RS && !own) {
+      if (p.mode == MODE_RS && !own && !own_mc) {
         // publish this warp's 32 rows of the tile to the owner: the lanes' stores are ordered before
         // lane 0 by the warp barrier, and lane 0's system-scope release is cumulative over them
         __syncwarp();
@@ -429,6 +484,40 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           red_release_sys_add_u32(cnt, 1u);
         }
         __syncwarp();
+      }
+      if (own_mc) {
+        // own rows, multicast variant: this rank's partial is in local staging; once the peers have
+        // published theirs, one multimem.ld_reduce per 16 bytes returns the sum over all ranks
+        __syncwarp();
+        fence_sys();
+        bool got = true;
+        if (lane < c.world && lane != c.rank) {
+          const uint32_t* cnt = reinterpret_cast<const uint32_t*>(c.base[c.rank] + p.cnt_off) +
+                                (static_cast<long>(lane) * tiles_per_rank + (tm - c.rank * tiles_per_rank)) * tiles_n + tn;
+          got = wait_u32_ge(cnt, p.epoch * 4u, true, status, ST_TIMEOUT_PEER, abort_flag, c.wait_ns);
+        }
+        if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
+        const __nv_bfloat16* mrow = reinterpret_cast<const __nv_bfloat16*>(p.mc + p.stage_off) +
+                                    static_cast<long>(m0 + q * 32) * N;
+        __nv_bfloat16* orow = p.out + static_cast<long>(m0 + q * 32 - c.rank * p.rows_per_rank) * N;
+        const int u = lane & 7;
+#pragma unroll 1
+        for (int cp = 0; cp < BN / 64; ++cp) {
+          const int col = n0 + cp * 64 + u * 8;
+          if (col + 8 > N) continue;
+          uint4 sv[8];
+#pragma unroll
+          for (int it4 = 0; it4 < 8; ++it4) {
+            const int r = it4 * 4 + (lane >> 3);
+            sv[it4] = (m0 + q * 32 + r < M) ? mm_ld_reduce_bf16x8(mrow + static_cast<long>(r) * N + col)
+                                            : make_uint4(0, 0, 0, 0);
+          }
+#pragma unroll
+          for (int it4 = 0; it4 < 8; ++it4) {
+            const int r = it4 * 4 + (lane >> 3);
+            if (m0 + q * 32 + r < M) *reinterpret_cast<uint4*>(orow + static_cast<long>(r) * N + col) = sv[it4];
+          }
+        }
       }
     }
   }
@@ -480,9 +569,9 @@ using namespace kb;
 // Y[M,N] = gathered(X)[M,K] · op(W) with W stored [N,K] (b_mn = 0) or [K,N] (b_mn = 1), where this rank's shard already sits at rows
 // [rank*Ms, (rank+1)*Ms) of the gathered buffer at heap offset xg_off (same offset on all ranks).
 // ready: local uint32[M/128] flags (persist across calls, epoch-valued).  n_comm copy-driver CTAs.
-extern "C" int kb_ag_gemm_bf16(void* const* bases, int rank, int world, uint64_t flag_off, uint64_t xg_off,
-                               const void* W, void* Y, int M, int N, int K, int ldw, int b_mn, uint32_t* ready,
-                               uint32_t epoch, int n_comm, int num_sms, int* status, cudaStream_t stream) {
+static int ag_gemm_impl(void* const* bases, int rank, int world, uint64_t flag_off, uint64_t xg_off, const void* W,
+                       void* Y, int M, int N, int K, int ldw, int b_mn, uint32_t* ready, uint32_t epoch, int n_comm,
+                       int num_sms, int* status, cudaStream_t stream, uint8_t* uc, uint8_t* mc, uint64_t ready_off) {
   if (world < 2 || world > MAX_PEERS || M % (world * FG_BM) || (K & 7) || (xg_off & 1023)) return ST_BAD_ARG;
   if (num_sms <= 0) num_sms = device_sm_count();
   if (n_comm < 1) n_comm = 1;
@@ -496,9 +585,10 @@ extern "C" int kb_ag_gemm_bf16(void* const* bases, int rank, int world, uint64_t
   p.rows_per_rank = M / world;
   p.epoch = epoch;
   p.xg_off = xg_off;
-  p.ready = ready;
+  p.ready = mc ? reinterpret_cast<uint32_t*>(uc + ready_off) : ready;
   p.out = reinterpret_cast<__nv_bfloat16*>(Y);
-  const void* A = reinterpret_cast<const uint8_t*>(bases[rank]) + xg_off;
+  p.uc = uc; p.mc = mc; p.ready_off = ready_off;
+  const void* A = mc ? uc + xg_off : reinterpret_cast<const uint8_t*>(bases[rank]) + xg_off;
   const bool narrow = (N <= 128) || (N % 256 != 0 && N % 256 <= 128);
   const int bn = narrow ? 128 : 256;
   const int tiles = (M / FG_BM) * ((N + bn - 1) / bn);
@@ -509,13 +599,33 @@ extern "C" int kb_ag_gemm_bf16(void* const* bases, int rank, int world, uint64_t
               : launch_fused<256, false>(A, W, p, M, N, K, K, ldw, stream);
 }
 
+extern "C" int kb_ag_gemm_bf16(void* const* bases, int rank, int world, uint64_t flag_off, uint64_t xg_off,
+                               const void* W, void* Y, int M, int N, int K, int ldw, int b_mn, uint32_t* ready,
+                               uint32_t epoch, int n_comm, int num_sms, int* status, cudaStream_t stream) {
+  return ag_gemm_impl(bases, rank, world, flag_off, xg_off, W, Y, M, N, K, ldw, b_mn, ready, epoch, n_comm, num_sms,
+                      status, stream, nullptr, nullptr, 0);
+}
+
+// Switch-multicast variant: the gathered buffer (xg_off) and the per-tile ready flags (ready_off, uint32 per
+// 128 rows, zero before the channel's first call) live inside an NVLS buffer whose local view is `uc` and whose
+// multicast view is `mc`; this rank's shard already sits in its rows of the local gathered buffer.  `epoch`
+// must be the number of calls made on this channel (flags count calls).
+extern "C" int kb_ag_gemm_mc_bf16(void* const* bases, int rank, int world, uint64_t flag_off, void* uc, void* mc,
+                                  uint64_t xg_off, uint64_t ready_off, const void* W, void* Y, int M, int N, int K,
+                                  int ldw, int b_mn, uint32_t epoch, int n_comm, int num_sms, int* status,
+                                  cudaStream_t stream) {
+  if (!uc || !mc || (ready_off & 3)) return ST_BAD_ARG;
+  return ag_gemm_impl(bases, rank, world, flag_off, xg_off, W, Y, M, N, K, ldw, b_mn, nullptr, epoch, n_comm, num_sms,
+                      status, stream, reinterpret_cast<uint8_t*>(uc), reinterpret_cast<uint8_t*>(mc), ready_off);
+}
+
 // out[M/world, N] = rows owned by this rank of sum over ranks of (A[M,K] · op(W)); W as above.
 // stage_off: staging [world][M/world][N] bf16; cnt_off: uint32 counters [world][M/world/128][tiles_n];
 // go: local uint32 flag.  n_comm: SMs of the num_sms budget that the kernel does not occupy.
-extern "C" int kb_gemm_rs_bf16(void* const* bases, int rank, int world, uint64_t flag_off, uint64_t stage_off,
-                               uint64_t cnt_off, const void* A, int lda, const void* W, int ldw, int b_mn, void* out,
-                               int M, int N, int K, uint32_t* go, uint32_t epoch, int n_comm, int num_sms, int* status,
-                               cudaStream_t stream) {
+static int gemm_rs_impl(void* const* bases, int rank, int world, uint64_t flag_off, uint64_t stage_off,
+                       uint64_t cnt_off, const void* A, int lda, const void* W, int ldw, int b_mn, void* out, int M,
+                       int N, int K, uint32_t* go, uint32_t epoch, int n_comm, int num_sms, int* status,
+                       cudaStream_t stream, uint8_t* uc, uint8_t* mc) {
   if (world < 2 || world > MAX_PEERS || M % (world * FG_BM) || (K & 7) || (N & 7) || (lda & 7)) return ST_BAD_ARG;
   if (num_sms <= 0) num_sms = device_sm_count();
   if (n_comm < 0) n_comm = 0;
@@ -530,6 +640,7 @@ extern "C" int kb_gemm_rs_bf16(void* const* bases, int rank, int world, uint64_t
   p.cnt_off = cnt_off;
   p.go = go;
   p.out = reinterpret_cast<__nv_bfloat16*>(out);
+  p.uc = uc; p.mc = mc;
   const bool narrow = (N <= 128) || (N % 256 != 0 && N % 256 <= 128);
   const int bn = narrow ? 128 : 256;
   const int tiles = (M / FG_BM) * ((N + bn - 1) / bn);
@@ -541,6 +652,25 @@ extern "C" int kb_gemm_rs_bf16(void* const* bases, int rank, int world, uint64_t
                           : launch_fused<128, false>(A, W, p, M, N, K, lda, ldw, stream);
   return b_mn ? launch_fused<256, true>(A, W, p, M, N, K, lda, ldw, stream)
               : launch_fused<256, false>(A, W, p, M, N, K, lda, ldw, stream);
+}
+
+extern "C" int kb_gemm_rs_bf16(void* const* bases, int rank, int world, uint64_t flag_off, uint64_t stage_off,
+                               uint64_t cnt_off, const void* A, int lda, const void* W, int ldw, int b_mn, void* out,
+                               int M, int N, int K, uint32_t* go, uint32_t epoch, int n_comm, int num_sms, int* status,
+                               cudaStream_t stream) {
+  return gemm_rs_impl(bases, rank, world, flag_off, stage_off, cnt_off, A, lda, W, ldw, b_mn, out, M, N, K, go, epoch,
+                      n_comm, num_sms, status, stream, nullptr, nullptr);
+}
+
+// Switch-multicast variant: stage_off names a [M, N] bf16 staging area inside an NVLS buffer (local view
+// `uc`, multicast view `mc`); the tile counters (cnt_off) stay in the peer-mapped heap.
+extern "C" int kb_gemm_rs_mc_bf16(void* const* bases, int rank, int world, uint64_t flag_off, void* uc, void* mc,
+                                  uint64_t stage_off, uint64_t cnt_off, const void* A, int lda, const void* W, int ldw,
+                                  int b_mn, void* out, int M, int N, int K, uint32_t* go, uint32_t epoch, int n_comm,
+                                  int num_sms, int* status, cudaStream_t stream) {
+  if (!uc || !mc || (stage_off & 15)) return ST_BAD_ARG;
+  return gemm_rs_impl(bases, rank, world, flag_off, stage_off, cnt_off, A, lda, W, ldw, b_mn, out, M, N, K, go, epoch,
+                      n_comm, num_sms, status, stream, reinterpret_cast<uint8_t*>(uc), reinterpret_cast<uint8_t*>(mc));
 }
 
 // Number of column tiles the fused kernels use for a given N (sizes the counter array).

@@ -60,20 +60,6 @@ static CUmulticastObjectProp mc_prop(int world, size_t size) {
 }
 
 // ----------------------------------------------------------------------------- kernels
-__device__ __forceinline__ uint4 mm_ld_reduce_bf16x8(const void* mc) {
-  uint4 v;
-  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(mc)
-               : "memory");
-  return v;
-}
-__device__ __forceinline__ void mm_st_bf16x8(void* mc, const uint4& v) {
-  asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(mc), "r"(v.x), "r"(v.y),
-               "r"(v.z), "r"(v.w)
-               : "memory");
-}
-
 // In-place sum of `n_vec` 16-byte vectors at byte offset `off` of every rank's bound buffer.
 __global__ void __launch_bounds__(1024, 1)
 nvls_allreduce_kernel(PeerCtx c, uint8_t* mc, uint64_t off, long n_vec, uint64_t epoch) {

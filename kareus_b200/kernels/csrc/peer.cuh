@@ -59,6 +59,28 @@ __device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
   return v;
 }
 
+// ----------------------------------------------------------------------------- NVLink-switch multicast
+// `mc` addresses are views of a multicast object that every rank of the group has bound memory to
+// (parallel/nvls.py).  ld_reduce returns the element-wise sum of all ranks' copies, computed in the
+// switch; st writes all copies; red adds to all copies.
+__device__ __forceinline__ uint4 mm_ld_reduce_bf16x8(const void* mc) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void mm_st_bf16x8(void* mc, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(mc), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
+}
+__device__ __forceinline__ void mm_red_add_u32(void* mc, uint32_t v) {
+  asm volatile("multimem.red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(mc), "r"(v) : "memory");
+}
+__device__ __forceinline__ void fence_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
+
 // Bounded polls.  `abort_flag` may be null (kernels without a CTA-wide abort flag).
 __device__ __forceinline__ bool wait_u64_ge(const uint64_t* p, uint64_t want, int* status, int code,
                                             volatile int* abort_flag = nullptr, uint64_t limit_ns = KB_WAIT_NS) {

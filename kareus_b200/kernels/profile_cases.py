@@ -120,6 +120,10 @@ def fused_table() -> None:
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
     heap = SymmetricHeap.create(dist.group.WORLD, dev, size_bytes=3 << 30)
+    if os.environ.get("KAREUS_NVLS", "0") == "1":      # multicast variants of the kernels
+        mc_on = heap.enable_nvls(3 << 30)
+        if rank == 0:
+            print(f"NVLink-switch multicast: {'on' if mc_on else 'not supported, peer loads/stores'}")
     peak = 1669.2e12
     pk = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
     if pk.exists():

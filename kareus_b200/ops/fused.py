@@ -38,7 +38,9 @@ def _lib():
         L.kb_ag_gemm_bf16.argtypes = [P, I, I, U64, U64, P, P, I, I, I, I, I, P, U32, I, I, P, P]
         L.kb_gemm_rs_bf16.argtypes = [P, I, I, U64, U64, U64, P, I, P, I, I, P, I, I, I, P, U32, I, I, P, P]
         L.kb_fused_tiles_n.argtypes = [I]
-        for n in ("kb_ag_gemm_bf16", "kb_gemm_rs_bf16", "kb_fused_tiles_n"):
+        L.kb_ag_gemm_mc_bf16.argtypes = [P, I, I, U64, P, P, U64, U64, P, P, I, I, I, I, I, U32, I, I, P, P]
+        L.kb_gemm_rs_mc_bf16.argtypes = [P, I, I, U64, P, P, U64, U64, P, I, P, I, I, P, I, I, I, P, U32, I, I, P, P]
+        for n in ("kb_ag_gemm_bf16", "kb_gemm_rs_bf16", "kb_fused_tiles_n", "kb_ag_gemm_mc_bf16", "kb_gemm_rs_mc_bf16"):
             getattr(L, n).restype = c_int
         _DECLARED = True
     return L
@@ -89,6 +91,28 @@ class _FusedBase:
         self._graph_uid = operator_uid(linear)
         self._local = {}
 
+    def _nvls(self):
+        """The heap's NVLink-switch buffer when the multicast variants of the kernels are to be used
+        (``SymmetricHeap.enable_nvls`` has run and ``KAREUS_FUSED_NVLS`` is not 0)."""
+        nv = getattr(self.heap, "nvls", None)
+        if nv is not None and os.environ.get("KAREUS_FUSED_NVLS", "1") != "0":
+            return nv
+        return None
+
+    def _nvls_region(self, ch, name: str, nbytes: int) -> int:
+        """Persistent region of this call site inside the NVLS buffer (same offset on every rank)."""
+        cur = ch.buffers.get("nvls:" + name)
+        if cur is None or cur[1] < nbytes:
+            if cur is None and ch.epoch != 0 and not any(k.startswith("nvls:") for k in ch.buffers):
+                # the ready flags of the multicast kernels count calls: they must start with the channel
+                raise KC.KernelError(f"{self.name}: this call site already ran without multicast; enable the "
+                                     "NVLS buffer before the first call")
+            if cur is not None and name == "ready":
+                raise KC.KernelError(f"{self.name}: the number of row tiles of a call site must not grow")
+            cur = (self._nvls().region(nbytes), nbytes)
+            ch.buffers["nvls:" + name] = cur
+        return cur[0]
+
     def _local_flags(self, key, n):
         t = self._local.get(key)
         if t is None or t.numel() < n:
@@ -107,6 +131,24 @@ class _FusedBase:
         if ms % 128 or x2.dtype != torch.bfloat16:
             raise KC.KernelError(f"fused all-gather GEMM needs bf16 and a multiple of 128 rows per rank, got {ms}")
         ch = heap.channel(f"{self.tag}/{nb}")
+        nv = self._nvls()
+        if nv is not None:
+            # multicast variant: the drivers push this rank's shard through the switch into every rank's
+            # gathered buffer; flags and data live in the NVLS buffer
+            off = self._nvls_region(ch, "xg", m * k * 2)
+            roff = self._nvls_region(ch, "ready", (m // 128) * 4)
+            xg = nv.view(off, (m, k), torch.bfloat16)
+            _replay.copy_(xg[rank * ms:(rank + 1) * ms], x2 if x2.is_contiguous() else x2.contiguous())
+            ch.bump()
+            y = torch.empty(m, n_out, dtype=torch.bfloat16, device=x2.device)
+            st = KC.status_word(x2.device)
+            rc = _lib().kb_ag_gemm_mc_bf16(heap._bases_arr, rank, world, ch.flag_off, c_void_p(nv.uc_ptr),
+                                           c_void_p(nv.mc_ptr), off, roff, w.data_ptr(), y.data_ptr(), m, n_out, k,
+                                           w.stride(0), 1 if b_mn else 0, ch.epoch, int(sm_num or self.default_sm),
+                                           _fused_sms(), st.data_ptr(), KC._stream())
+            KC._check(rc, f"ag_gemm (multicast) {self.name}")
+            KC._count()
+            return y, xg
         off, _ = heap.buffer(ch, "xg", m * k * 2)
         xg = heap.view(off, (m, k), torch.bfloat16)
         _replay.copy_(xg[rank * ms:(rank + 1) * ms], x2 if x2.is_contiguous() else x2.contiguous())
@@ -135,6 +177,23 @@ class _FusedBase:
         L = _lib()
         tiles_n = L.kb_fused_tiles_n(n_out)
         ch = heap.channel(f"{self.tag}/{nb}")
+        nv = self._nvls()
+        if nv is not None:
+            # multicast variant: partial tiles stay in local staging; each rank fetches its own rows summed
+            # over all ranks by the switch
+            stage_off = self._nvls_region(ch, "stage", m * n_out * 2)
+            cnt_off, _ = heap.buffer(ch, "cnt", world * (ms // 128) * tiles_n * 4)
+            go = self._local_flags(("go", nb), 1)
+            ch.bump()
+            out = torch.empty(ms, n_out, dtype=torch.bfloat16, device=a2.device)
+            st = KC.status_word(a2.device)
+            rc = L.kb_gemm_rs_mc_bf16(heap._bases_arr, rank, world, ch.flag_off, c_void_p(nv.uc_ptr), c_void_p(nv.mc_ptr),
+                                      stage_off, cnt_off, a2.data_ptr(), a2.stride(0), w.data_ptr(), w.stride(0),
+                                      1 if b_mn else 0, out.data_ptr(), m, n_out, k, go.data_ptr(), ch.epoch,
+                                      int(sm_num or 0), _fused_sms(), st.data_ptr(), KC._stream())
+            KC._check(rc, f"gemm_rs (multicast) {self.name}")
+            KC._count()
+            return out, a2
         stage_off, _ = heap.buffer(ch, "stage", m * n_out * 2)
         cnt_off, _ = heap.buffer(ch, "cnt", world * (ms // 128) * tiles_n * 4)
         go = self._local_flags(("go", nb), 1)

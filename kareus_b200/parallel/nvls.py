@@ -212,15 +212,18 @@ class NvlsBuffer:
         return out
 
     # ------------------------------------------------------------------ teardown
-    def close(self) -> None:
-        """Collective: everyone stops using the object, then unmaps, unbinds and releases its part."""
+    def close(self, collective: bool = True) -> None:
+        """Everyone stops using the object, then unmaps, unbinds and releases its part.  ``collective=False``
+        skips the barriers: the way out for a rank that leaves on an error (its kernels have drained; the
+        peers' waits on it are bounded)."""
         if self.closed:
             return
         self.closed = True
         torch.cuda.synchronize(self.heap.device)
-        if self.heap.world > 1 and dist.is_initialized():
+        sync = collective and self.heap.world > 1 and dist.is_initialized()
+        if sync:
             dist.barrier(group=self.heap.group)
         self.local = None
         KC._check(KC.lib().kb_nvls_destroy(c_void_p(self._state)), "multicast destroy")
-        if self.heap.world > 1 and dist.is_initialized():
+        if sync:
             dist.barrier(group=self.heap.group)

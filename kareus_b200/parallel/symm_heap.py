@@ -366,12 +366,12 @@ class SymmetricHeap:
         slot = self.local_ptr + ch.flag_off
         KC._check(self.lib.kb_wait_flag(c_void_p(slot), 1 << 62, limit_ns, st.data_ptr(), KC._stream()), "wait_flag")
 
-    def close(self) -> None:
+    def close(self, collective: bool = True) -> None:
         if self.closed:
             return
         self.closed = True
         if self.nvls is not None:
-            self.nvls.close()
+            self.nvls.close(collective)
             self.nvls = None
         torch.cuda.synchronize(self.device)
         for r, b in enumerate(self.bases):

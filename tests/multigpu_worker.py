@@ -40,7 +40,7 @@ def test_heap_collectives(heap, rank, world, dev):
     assert torch.all(y == world)
 
 
-def test_fused_gemm_collectives(heap, rank, world, dev):
+def test_fused_gemm_collectives(heap, rank, world, dev, prefix=""):
     """all-gather→GEMM and GEMM→reduce-scatter kernels vs NCCL + fp32 matmul."""
     from types import SimpleNamespace
     from kareus_b200.engine.context import OpContext
@@ -49,7 +49,7 @@ def test_fused_gemm_collectives(heap, rank, world, dev):
     g = torch.Generator(device=dev).manual_seed(5 + rank)
     for (ms, k, n, sm) in [(256, 512, 384, 4), (1024, 3072, 640, 12), (512, 1024, 3072, 8)]:
         w = (torch.randn(n, k, device=dev, generator=g) * 0.05).bfloat16()
-        lin = SimpleNamespace(name=f"lin{ms}_{n}", out_features=n, in_features=k, weight=w)
+        lin = SimpleNamespace(name=f"{prefix}lin{ms}_{n}", out_features=n, in_features=k, weight=w)
         x = torch.randn(ms, 1, k, device=dev, generator=g).bfloat16()
         xs = torch.empty(ms * world, 1, k, device=dev, dtype=torch.bfloat16)
         dist.all_gather_into_tensor(xs, x)
@@ -102,7 +102,7 @@ def test_nvls_collectives(heap, rank, world, dev):
     """All-reduce and reduce-scatter through the NVLink switch (multimem) vs NCCL.  The multicast binding is
     always undone before the process ends."""
     from kareus_b200.kernels import cuda as KC
-    if not heap.enable_nvls(256 << 20):
+    if not heap.enable_nvls(512 << 20):
         if rank == 0:
             print("switch multicast not supported here: skipped", flush=True)
         return
@@ -129,6 +129,8 @@ def test_nvls_collectives(heap, rank, world, dev):
         y = heap.all_reduce(st, nb=0, sm_num=4, tag="n_stage")
         torch.cuda.synchronize()
         assert torch.all(y == world * (world + 1) / 2)
+        # the fused GEMM+collective kernels in their multicast variants (push through the switch, summed fetch)
+        test_fused_gemm_collectives(heap, rank, world, dev, prefix="mc_")
     finally:
         heap.nvls.close()
         heap.nvls = None

@@ -140,7 +140,7 @@ class NvlsBuffer:
     # ------------------------------------------------------------------ buffers
     def region(self, nbytes: int):
         """Bump-allocate ``nbytes`` (same offset on every rank); returns the byte offset."""
-        off = (self._top + 255) // 256 * 256
+        off = (self._top + 1023) // 1024 * 1024
         if off + nbytes > self.size:
             raise MemoryError(f"NVLS buffer of {self.size >> 20} MiB is full")
         self._top = off + nbytes

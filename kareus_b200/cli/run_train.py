@@ -99,6 +99,8 @@ def main(argv=None) -> int:
     if cuda and a.tp > 1 and (par.comm_backend == "kernel" or par.tp_comm == "sp_fused"):
         from ..parallel.symm_heap import SymmetricHeap
         heap = SymmetricHeap.create(mesh.group("tp"), device)
+        if os.environ.get("KAREUS_NVLS", "0") == "1":
+            heap.enable_nvls(int(os.environ.get("KAREUS_NVLS_BYTES", str(3 << 30))))
     trainer = Trainer(cfg, par, tc, mesh=mesh, device=device, monitor=monitor, freq_client=freq_client,
                       comm_scheduler=sched, heap=heap, recompute_layers=a.recompute_layers)
     timers = Timers() if a.enable_timers else None
@@ -132,6 +134,9 @@ def main(argv=None) -> int:
             power.dump(out / f"power_monitor_global_rank-{rank}_local_rank-{local}.txt")
         if timers is not None:
             timers.export(out, rank, local)
+        if heap is not None and heap.nvls is not None:
+            heap.nvls.close(collective=False)     # unbind switch-multicast memory before this rank leaves
+            heap.nvls = None
         if world > 1:
             dist.barrier()
             if not a.keep_process_group:

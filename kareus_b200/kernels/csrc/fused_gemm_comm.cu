@@ -341,6 +341,20 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     uint32_t tile_i = 0;
     bool ok = true;
     bool go_seen = false;
+    // reduce-scatter: counters of remote tiles whose stores are out but not yet published.  One
+    // system-scope fence then covers several tiles (a fence waits for the acknowledgements of all
+    // earlier peer stores, i.e. an NVLink round trip); owners only read their tiles at the end of
+    // their own walk, so publishing a few tiles late costs nothing.
+    constexpr int PUB_BATCH = 4;
+    uint32_t* pub[PUB_BATCH];
+    int n_pub = 0;
+    auto publish = [&]() {
+      if (lane == 0 && n_pub > 0) {
+        fence_sys();
+        for (int i = 0; i < n_pub; ++i) red_relaxed_sys_add_u32(pub[i], 1u);
+      }
+      n_pub = 0;
+    };
     for (int t = cta; t < num_tiles && ok; t += p.n_gemm, ++tile_i) {
       const uint32_t buf = tile_i & 1u, bph = (tile_i >> 1) & 1u;
       int tm, tn;
@@ -359,6 +373,10 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         }
         const int owner = tm / tiles_per_rank;
         own = owner == c.rank;
+        if (own) {          // the own rows come last: everything still unpublished goes out first
+          __syncwarp();
+          publish();
+        }
         if (p.mc != nullptr) {
           // multicast: every partial tile goes to LOCAL staging [M, N]; own tiles are fetched summed below
           cbase = reinterpret_cast<__nv_bfloat16*>(p.uc + p.stage_off) + static_cast<long>(m0 + q * 32) * N;
@@ -477,11 +495,11 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         // publish this warp's 32 rows of the tile to the owner: the lanes' stores are ordered before
         // lane 0 by the warp barrier, and lane 0's system-scope release is cumulative over them
         __syncwarp();
-        if (lane == 0) {
+        {
           const int owner = tm / tiles_per_rank;
-          uint32_t* cnt = reinterpret_cast<uint32_t*>(c.base[owner] + p.cnt_off) +
-                          (static_cast<long>(c.rank) * tiles_per_rank + (tm - owner * tiles_per_rank)) * tiles_n + tn;
-          red_release_sys_add_u32(cnt, 1u);
+          pub[n_pub++] = reinterpret_cast<uint32_t*>(c.base[owner] + p.cnt_off) +
+                         (static_cast<long>(c.rank) * tiles_per_rank + (tm - owner * tiles_per_rank)) * tiles_n + tn;
+          if (n_pub == PUB_BATCH) publish();
         }
         __syncwarp();
       }
@@ -520,6 +538,10 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         }
       }
     }
+    // tiles published late must still go out when this CTA has no own tile after them (also on the
+    // error path: the stores were made, and peers should not wait longer than needed)
+    __syncwarp();
+    publish();
   }
 
   tc_fence_before();

@@ -132,6 +132,7 @@ def fused_table() -> None:
     # per-rank shapes of tensor-parallel degree `tp` (default: the number of ranks; KAREUS_TABLE_TP runs
     # another degree's shapes on this many ranks, e.g. the TP8 shapes on two GPUs)
     tp = int(os.environ.get("KAREUS_TABLE_TP", str(world)))
+    reps = int(os.environ.get("KAREUS_TABLE_REPS", "10"))
     M, H, F, HEADS, KV, D = 16384, 3072, 8192, 24, 8, 128
     q_out, f_out = (HEADS + 2 * KV) * D // tp, 2 * F // tp
     # name -> (in_features, out_features, class, kind of collective, is backward)
@@ -143,7 +144,8 @@ def fused_table() -> None:
              ("fc2 bwd: AG->dgrad", F // tp, H, FusedAGDgrad, "ag")]
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     if rank == 0:
-        print(f"| kernel (TP{tp} shapes on {world} ranks, M={M}, {sm} comm CTAs) | N | K | us | GEMM TFLOP/s | "
+        print(f"| kernel (TP{tp} shapes on {world} ranks, M={M}, {sm} comm CTAs, {reps} calls back to back) | N | K | us | "
+              "GEMM TFLOP/s | "
               "NVLink GB/s/dir | roofline us (gemm, link) | fraction | plain GEMM us |\n|---|---|---|---|---|---|---|---|---|")
     for name, k_in, n_out, cls, kind in cases:
         w = (torch.randn(n_out, k_in, device=dev) * 0.02).bfloat16()
@@ -168,6 +170,9 @@ def fused_table() -> None:
             else:
                 op._ag_gemm(x.reshape(-1, red), w, out, True, sm, 0)
 
+        # `reps` calls back to back per sample: the ranks' GPUs do not start a sample at the same instant
+        # (host skew after the barrier), and with a single call the early ranks' wait for the late one
+        # would be charged to the kernel.  Inputs and outputs (100 MB each) do not stay in L2 between calls.
         times = []
         for i in range(9):
             flush.zero_()
@@ -175,11 +180,13 @@ def fused_table() -> None:
             torch.cuda.synchronize()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda._sleep(3_000_000)
+            call()                      # absorbs the start skew
             a.record()
-            call()
+            for _ in range(reps):
+                call()
             b.record()
             torch.cuda.synchronize()
-            t = torch.tensor([a.elapsed_time(b)], device=dev)
+            t = torch.tensor([a.elapsed_time(b) / reps], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             if i >= 3:
                 times.append(t.item())

@@ -209,9 +209,40 @@ def fused_table() -> None:
     dist.destroy_process_group()
 
 
+def collectives_table() -> None:
+    """The heap's all-pairs collectives (plain peer loads/stores, no GEMM) on one nanobatch-sized tensor
+    (16384 x 3072 bf16 = 100 MB) over a grid of launch shapes: time per call (five calls back to back, max
+    over ranks) and bytes crossing NVLink per direction per second.  Shows what CTA count and block size a
+    kernel needs to fill the links."""
+    import torch.distributed as dist
+    from ..parallel.mesh import init_distributed
+    from ..parallel.symm_heap import SymmetricHeap
+    from . import cuda as KC
+    rank, world, local = init_distributed(timeout_s=120)
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    heap = SymmetricHeap.create(dist.group.WORLD, dev, size_bytes=2 << 30)
+    M, H = 16384, 3072
+    link = (world - 1) / world * M * H * 2
+    if rank == 0:
+        print(f"| collective ({world} ranks, {M}x{H} bf16) | CTAs | threads | us | NVLink GB/s/dir |\n|---|---|---|---|---|")
+    for kind, shape in (("all_gather", (M // world, H)), ("reduce_scatter", (M, H)), ("all_reduce", (M, H))):
+        best, table = heap.auto_tune(kind, shape, sm_candidates=(8, 16, 32, 64), block_candidates=(512, 1024), iters=5)
+        factor = 2.0 if kind == "all_reduce" else 1.0
+        if rank == 0:
+            for (sm, blk), ms in sorted(table.items()):
+                print(f"| {kind} | {sm} | {blk} | {ms * 1e3:.0f} | {factor * link / 1e6 / ms:.0f} |", flush=True)
+    KC.check_status()
+    dist.barrier()
+    heap.close()
+    dist.destroy_process_group()
+
+
 def main(case: str, reps: int = 3) -> None:
     from . import cuda as KC
     dev = "cuda"
+    if case == "collectives":
+        return collectives_table()
     if case == "gemm_table":
         return gemm_table()
     if case == "attn_table":

@@ -289,18 +289,18 @@ class PartitionProgram:
             launched = st.comm is None
             if self.n == 1 and st.comm is not None:
                 # a single nanobatch has nothing to hide the collective behind
-                self._launch_comm(st, ctxs, streams, shape, pending, planned)
+                self._launch_comm(st, ctxs, streams, shape, pending, planned, release_saved)
                 self._wait_all(pending, ctxs, streams)
                 launched = True
             for i, node in enumerate(st.compute):
                 if not launched and i == start:
-                    self._launch_comm(st, ctxs, streams, shape, pending, planned)
+                    self._launch_comm(st, ctxs, streams, shape, pending, planned, release_saved)
                     launched = True
                 self._run_compute(node, ctxs[st.nb], streams, grad_enabled, release_saved)
             if st.compute:
                 ctxs[st.nb].ready_event[st.segment] = streams.record(streams.compute())
             if not launched:
-                self._launch_comm(st, ctxs, streams, shape, pending, planned)
+                self._launch_comm(st, ctxs, streams, shape, pending, planned, release_saved)
             if self.sync == "partition_end":
                 self._wait_all(pending, ctxs, streams)
         self._wait_all(pending, ctxs, streams)
@@ -345,7 +345,8 @@ class PartitionProgram:
                 store.pop(tid)
 
     # -- collectives
-    def _launch_comm(self, st: Step, ctxs, streams: StreamSet, shape, pending, planned: bool = False) -> None:
+    def _launch_comm(self, st: Step, ctxs, streams: StreamSet, shape, pending, planned: bool = False,
+                     release_saved: bool = True) -> None:
         node, nb = st.comm, st.comm_nb
         nbctx = ctxs[nb]
         store = nbctx.store
@@ -376,6 +377,10 @@ class PartitionProgram:
             outs = node.operator.run(ins, sm_num=sm_num, block_size=block, backward=self.backward,
                                      nb=nb, ctx=ctx, **kw)
             done = None
+        if self.backward and release_saved and getattr(node.operator, "releases_ctx", False):
+            # a fused backward node is the last user of its layer's saved tensors (a profiler that re-runs
+            # one step keeps them: release_saved=False)
+            nbctx.release_op(node.op_id)
         if not isinstance(outs, (tuple, list)):
             outs = (outs,)
         for p, t in zip(node.outputs, outs):

@@ -239,6 +239,8 @@ class FusedGemmRS(_FusedBase):
 class FusedDgradRS(_FusedBase):
     """backward of a column-parallel layer: ``dX_shard = ReduceScatter(dY·W)`` and ``dW += dYᵀ·X``."""
 
+    releases_ctx = True       # last user of the layer's saved input: the engine drops it afterwards
+
     def run(self, tensors, sm_num=None, block_size=None, backward=True, nb=0, ctx=None, planned=False):
         (dy,) = tensors
         lin = self.linear
@@ -247,12 +249,13 @@ class FusedDgradRS(_FusedBase):
         dx, dy2 = self._gemm_rs(dy.reshape(-1, dy.shape[-1]), lin.weight, lin.in_features, True,
                                 sm_num if planned else 0, nb)
         _wgrad(dy2, x_full, lin.weight)
-        ctx.clear()
         return (dx.reshape((lead[0] // self.heap.world,) + tuple(lead[1:]) + (lin.in_features,)),)
 
 
 class FusedAGDgrad(_FusedBase):
     """backward of a row-parallel layer: ``dX = AllGather(dY)·W`` and ``dW += AllGather(dY)ᵀ·A``."""
+
+    releases_ctx = True
 
     def run(self, tensors, sm_num=None, block_size=None, backward=True, nb=0, ctx=None, planned=False):
         (dy,) = tensors
@@ -267,7 +270,6 @@ class FusedAGDgrad(_FusedBase):
             from ..engine.program import _per_nb_streams, _shared_comm_stream, wait_stream
             if _per_nb_streams():
                 wait_stream(torch.cuda.current_stream(dyg.device), _shared_comm_stream(dyg.device, slot=0))
-        ctx.clear()
         return (dx.reshape((lead[0] * self.heap.world,) + tuple(lead[1:]) + (lin.in_features,)),)
 
 

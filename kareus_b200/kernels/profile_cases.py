@@ -232,6 +232,27 @@ def collectives_table() -> None:
         if rank == 0:
             for (sm, blk), ms in sorted(table.items()):
                 print(f"| {kind} | {sm} | {blk} | {ms * 1e3:.0f} | {factor * link / 1e6 / ms:.0f} |", flush=True)
+    # NCCL on the same tensors, for the rate the library reaches on this box
+    x = torch.ones(M, H, dtype=torch.bfloat16, device=dev)
+    shard = torch.ones(M // world, H, dtype=torch.bfloat16, device=dev)
+    out_full = torch.empty(M, H, dtype=torch.bfloat16, device=dev)
+    for kind, fn, factor in (("nccl all_gather", lambda: dist.all_gather_into_tensor(out_full, shard), 1.0),
+                             ("nccl reduce_scatter", lambda: dist.reduce_scatter_tensor(shard, x), 1.0),
+                             ("nccl all_reduce", lambda: dist.all_reduce(x), 2.0)):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(5):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b) / 5], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        if rank == 0:
+            print(f"| {kind} | - | - | {t.item() * 1e3:.0f} | {factor * link / 1e6 / t.item():.0f} |", flush=True)
     KC.check_status()
     dist.barrier()
     heap.close()

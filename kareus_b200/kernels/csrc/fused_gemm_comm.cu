@@ -43,6 +43,7 @@
 #include "peer.cuh"
 #include "host_utils.h"
 #include <stdlib.h>
+#include <string.h>
 
 namespace kb {
 
@@ -76,6 +77,14 @@ struct FusedParams {
   uint8_t* uc;
   uint8_t* mc;
   uint64_t ready_off;     // AG: uint32 per 128-row tile, bumped on every rank by the tile's sender
+  int push_tma;           // RS over peer memory: partial tiles leave through TMA stores (maps in StageMaps)
+};
+
+// RS: one tensor map per peer over this rank's slot [rows_per_rank, N] of that peer's staging area.  The
+// epilogue hands each 32-row x 64-column block to the TMA unit instead of storing it with the warp's lanes:
+// the copy engine of the SM keeps far more bytes in flight towards the peer than 128 storing threads do.
+struct StageMaps {
+  CUtensorMap m[MAX_PEERS];
 };
 
 template <int BN>
@@ -84,7 +93,10 @@ struct FgSmem {
   static constexpr int B_BYTES = BN * FG_BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int TILE_BYTES = STAGE_BYTES * FG_STAGES;
-  static constexpr int TOTAL = TILE_BYTES + 256 + 4 * 4096 + 1024;   // + per-warp epilogue staging
+  static constexpr int STG_BYTES = 4 * 2 * 4096;    // per epilogue warp two 4 KB staging buffers (1 KiB aligned:
+                                                   // a TMA store reads them with the 128-byte swizzle)
+  static constexpr int BAR_OFF = TILE_BYTES + STG_BYTES;
+  static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
 
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
@@ -188,11 +200,11 @@ __device__ void ag_push_role(const FusedParams& p, int K, int* ok_slot) {
 template <int BN, bool B_MN>
 __global__ void __launch_bounds__(FG_THREADS, 1)
 fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                  const FusedParams p, int M, int N, int K) {
+                  const __grid_constant__ StageMaps stage_maps, const FusedParams p, int M, int N, int K) {
   using S = FgSmem<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + S::TILE_BYTES);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + S::BAR_OFF);
   uint64_t* empty = full + FG_STAGES;
   uint64_t* tfull = empty + FG_STAGES;
   uint64_t* tempty = tfull + 2;
@@ -348,8 +360,10 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     constexpr int PUB_BATCH = 4;
     uint32_t* pub[PUB_BATCH];
     int n_pub = 0;
+    bool tma_busy = false;      // this warp's lane 0 has TMA stores that may still read the staging buffers
     auto publish = [&]() {
       if (lane == 0 && n_pub > 0) {
+        tma_store_wait<0>();    // the tiles' TMA stores have been performed
         fence_sys();
         for (int i = 0; i < n_pub; ++i) red_relaxed_sys_add_u32(pub[i], 1u);
       }
@@ -405,9 +419,25 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       // XOR-swizzled by row) → global/peer memory as full 128-byte row segments.  Writing straight
       // from registers would give every lane its own row, i.e. 16-byte scattered writes, which
       // NVLink carries at a fraction of its bandwidth.
-      uint8_t* stg = smem + S::TILE_BYTES + 256 + q * 4096;
+      uint8_t* stg0 = smem + S::TILE_BYTES + q * 8192;
+      const bool use_tma = p.mode == MODE_RS && p.push_tma && !own && !own_mc && p.mc == nullptr;
+      if (!use_tma && tma_busy) {
+        // the lanes are about to write staging buffer 0 themselves: earlier TMA stores must have read it
+        if (lane == 0) tma_store_wait_read<0>();
+        __syncwarp();
+        tma_busy = false;
+      }
 #pragma unroll 1
       for (int cp = 0; cp < BN / 64; ++cp) {
+        uint8_t* stg = stg0 + (use_tma ? (cp & 1) * 4096 : 0);
+        if (use_tma) {
+          // buffer (cp & 1) was handed to the TMA unit two blocks ago: at most the newest store may still read
+          if (tma_busy) {
+            if (lane == 0) tma_store_wait_read<1>();
+            __syncwarp();
+          }
+          if (n0 + cp * 64 >= N) break;
+        }
         // own rows of a reduce-scatter: gather the peers' partial sums of this 32x64 block first, eight
         // independent 16-byte loads per lane and peer in flight, so their latency hides behind the
         // accumulator drain below
@@ -460,6 +490,18 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             const int unit = half * 4 + j;
             *reinterpret_cast<uint4*>(stg + lane * 128 + ((unit ^ (lane & 7)) << 4)) = o;
           }
+        }
+        if (use_tma) {
+          // the block in shared memory has exactly the layout a 128-byte-swizzled TMA box reads
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            const int owner = tm / tiles_per_rank;
+            tma_store_2d(&stage_maps.m[owner], stg, n0 + cp * 64, m0 + q * 32 - owner * p.rows_per_rank);
+            tma_store_commit();
+          }
+          tma_busy = true;
+          continue;
         }
         __syncwarp();
         const int u = lane & 7;
@@ -542,6 +584,8 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     // error path: the stores were made, and peers should not wait longer than needed)
     __syncwarp();
     publish();
+    if (lane == 0) tma_store_wait<0>();      // nothing of this CTA's shared memory is still being read
+    __syncwarp();
   }
 
   tc_fence_before();
@@ -558,6 +602,17 @@ static int launch_fused(const void* A, const void* W, const FusedParams& p, int 
   CUtensorMap tmA, tmB;
   int rc = make_tmap_2d_bf16(&tmA, A, K, M, lda, FG_BK, FG_BM);
   if (rc) return rc;
+  StageMaps maps;
+  memset(&maps, 0, sizeof(maps));
+  if (p.mode == MODE_RS && p.push_tma) {
+    // this rank's slot in every peer's staging area: [rows_per_rank, N] bf16, blocks of 32 rows x 64 columns
+    for (int r = 0; r < p.peer.world; ++r) {
+      if (r == p.peer.rank) continue;
+      const uint8_t* base = p.peer.base[r] + p.stage_off + static_cast<uint64_t>(p.peer.rank) * p.rows_per_rank * N * 2;
+      rc = make_tmap_2d_bf16(&maps.m[r], base, N, p.rows_per_rank, N, 64, 32);
+      if (rc) return rc;
+    }
+  }
   if (!B_MN) rc = make_tmap_2d_bf16(&tmB, W, K, N, ldw, FG_BK, BN);
   else       rc = make_tmap_2d_bf16(&tmB, W, N, K, ldw, 64, FG_BK);
   if (rc) return rc;
@@ -571,7 +626,7 @@ static int launch_fused(const void* A, const void* W, const FusedParams& p, int 
   }
   const int grid = p.n_first + p.n_gemm + p.n_last;
   KB_LAUNCH_EPOCH(kern, grid, FG_THREADS, smem, stream,
-                  (EpochLoc{2, static_cast<int>(offsetof(FusedParams, epoch)), 4}), tmA, tmB, p, M, N, K);
+                  (EpochLoc{3, static_cast<int>(offsetof(FusedParams, epoch)), 4}), tmA, tmB, maps, p, M, N, K);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 2000 + (int)e;
 }
@@ -663,6 +718,11 @@ static int gemm_rs_impl(void* const* bases, int rank, int world, uint64_t flag_o
   p.go = go;
   p.out = reinterpret_cast<__nv_bfloat16*>(out);
   p.uc = uc; p.mc = mc;
+  {
+    // TMA push of the partial tiles (KAREUS_RS_TMA=0: the warp's lanes store them); needs 16-byte rows
+    static const bool want = [] { const char* e = getenv("KAREUS_RS_TMA"); return !(e && e[0] == '0'); }();
+    p.push_tma = (want && mc == nullptr && (N & 7) == 0 && (stage_off & 15) == 0) ? 1 : 0;
+  }
   const bool narrow = (N <= 128) || (N % 256 != 0 && N % 256 <= 128);
   const int bn = narrow ? 128 : 256;
   const int tiles = (M / FG_BM) * ((N + bn - 1) / bn);

@@ -7,6 +7,7 @@
 //   fused AdamW over flat buffers, sum of squares (reference: TE/Apex multi_tensor kernels)
 #include <cuda_bf16.h>
 #include "launch.h"
+#include "host_utils.h"
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -34,6 +35,20 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
   if (threadIdx.x == 0) red[0] = t;
   __syncthreads();
   return red[0];
+}
+// One barrier per call: `red` holds two sets of 32 partial sums and consecutive calls alternate `parity`,
+// so the next call's writes cannot overtake this call's reads (a thread reaches call n+2 only after the
+// barrier of call n+1, which every thread passes after it has read the sums of call n).
+template <int THREADS>
+__device__ __forceinline__ float block_sum_alt(float v, float* red, int parity) {
+  v = warp_sum(v);
+  float* r = red + parity * 32;
+  if ((threadIdx.x & 31) == 0) r[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = 0.f;
+#pragma unroll
+  for (int i = 0; i < THREADS / 32; ++i) t += r[i];
+  return t;
 }
 template <int THREADS>
 __device__ __forceinline__ float block_max(float v, float* red) {
@@ -80,17 +95,39 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
                    __nv_bfloat16* __restrict__ y, float* __restrict__ rstd, int rows, int H, float eps) {
   constexpr int NORM_THREADS = THREADS;
   constexpr int NORM_VPT = VPT;
-  __shared__ float red[32];
+  __shared__ float red[64];
   const int nvec = H >> 3;
-  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  // the next row's vectors are requested before this row's reduction, so a CTA always has a row in flight
+  uint4 nx[NORM_VPT];
+  if (blockIdx.x < rows) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(blockIdx.x) * H);
+#pragma unroll
+    for (int i = 0; i < NORM_VPT; ++i) {
+      const int v = threadIdx.x + i * NORM_THREADS;
+      if (v < nvec) nx[i] = xr[v];
+    }
+  }
+  int parity = 0;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x, parity ^= 1) {
     const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * H);
     uint4 xv[NORM_VPT];
+#pragma unroll
+    for (int i = 0; i < NORM_VPT; ++i) xv[i] = nx[i];
+    const int nrow = row + gridDim.x;
+    if (nrow < rows) {
+      const uint4* xn = reinterpret_cast<const uint4*>(x + static_cast<size_t>(nrow) * H);
+#pragma unroll
+      for (int i = 0; i < NORM_VPT; ++i) {
+        const int v = threadIdx.x + i * NORM_THREADS;
+        if (v < nvec) nx[i] = xn[v];
+      }
+    }
     float ss = 0.f;
 #pragma unroll
     for (int i = 0; i < NORM_VPT; ++i) {
       const int v = threadIdx.x + i * NORM_THREADS;
       if (v < nvec) {
-        xv[i] = xr[v];
         float f[8];
         unpack8(xv[i], f);
 #pragma unroll
@@ -103,11 +140,10 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
 #pragma unroll
       for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
     }
-    const float tot = block_sum<NORM_THREADS>(ss, red);
+    const float tot = block_sum_alt<NORM_THREADS>(ss, red, parity);
     const float r = rsqrtf(tot / static_cast<float>(H) + eps);
     if (threadIdx.x == 0) rstd[row] = r;
     uint4* yr = reinterpret_cast<uint4*>(y + static_cast<size_t>(row) * H);
-    const uint4* wr = reinterpret_cast<const uint4*>(w);
 #pragma unroll
     for (int i = 0; i < NORM_VPT; ++i) {
       const int v = threadIdx.x + i * NORM_THREADS;
@@ -161,7 +197,7 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
                    __nv_bfloat16* __restrict__ dx, float* __restrict__ partial, int rows, int H) {
   constexpr int NORM_THREADS = THREADS;
   constexpr int NORM_VPT = VPT;
-  __shared__ float red[32];
+  __shared__ float red[64];
   const int nvec = H >> 3;
   float dwacc[NORM_VPT][8];
 #pragma unroll
@@ -169,10 +205,25 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
 #pragma unroll
     for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f;
   const uint4* wr = reinterpret_cast<const uint4*>(w);
-  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
-    const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * H);
-    const uint4* gr = reinterpret_cast<const uint4*>(dy + static_cast<size_t>(row) * H);
-    const float r = rstd[row];
+  // the next row's x and dy are requested before this row's reduction (see rmsnorm_fwd_kernel)
+  uint4 nxx[NORM_VPT], nxg[NORM_VPT];
+  float nr = 0.f;
+  if (blockIdx.x < rows) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(blockIdx.x) * H);
+    const uint4* gr = reinterpret_cast<const uint4*>(dy + static_cast<size_t>(blockIdx.x) * H);
+#pragma unroll
+    for (int i = 0; i < NORM_VPT; ++i) {
+      const int v = threadIdx.x + i * NORM_THREADS;
+      if (v < nvec) {
+        nxx[i] = xr[v];
+        nxg[i] = gr[v];
+      }
+    }
+    nr = rstd[blockIdx.x];
+  }
+  int parity = 0;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x, parity ^= 1) {
+    const float r = nr;
     float xh[NORM_VPT][8], g[NORM_VPT][8];
     float dot = 0.f;
 #pragma unroll
@@ -180,8 +231,8 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
       const int v = threadIdx.x + i * NORM_THREADS;
       if (v < nvec) {
         float xf[8], gf[8], wf[8];
-        unpack8(xr[v], xf);
-        unpack8(gr[v], gf);
+        unpack8(nxx[i], xf);
+        unpack8(nxg[i], gf);
         unpack8(wr[v], wf);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -192,7 +243,21 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
         }
       }
     }
-    const float c = block_sum<NORM_THREADS>(dot, red) / static_cast<float>(H);
+    const int nrow = row + gridDim.x;
+    if (nrow < rows) {
+      const uint4* xn = reinterpret_cast<const uint4*>(x + static_cast<size_t>(nrow) * H);
+      const uint4* gn = reinterpret_cast<const uint4*>(dy + static_cast<size_t>(nrow) * H);
+#pragma unroll
+      for (int i = 0; i < NORM_VPT; ++i) {
+        const int v = threadIdx.x + i * NORM_THREADS;
+        if (v < nvec) {
+          nxx[i] = xn[v];
+          nxg[i] = gn[v];
+        }
+      }
+      nr = rstd[nrow];
+    }
+    const float c = block_sum_alt<NORM_THREADS>(dot, red, parity) / static_cast<float>(H);
     uint4* dr = reinterpret_cast<uint4*>(dx + static_cast<size_t>(row) * H);
 #pragma unroll
     for (int i = 0; i < NORM_VPT; ++i) {
@@ -607,16 +672,15 @@ __global__ void sumsq_bf16_kernel(const __nv_bfloat16* __restrict__ x, long n, f
   if (threadIdx.x == 0) atomicAdd(out, tot);
 }
 
-// Variant of the RMSNorm kernels for a row of H elements: threads per CTA, vectors per thread and how
-// many CTAs of it fit an SM (register budget of the backward kernel).
-struct NormVariant { int id, threads, vpt, ctas_per_sm; };
+// Variant of the RMSNorm kernels for a row of H elements: threads per CTA and vectors per thread.
+struct NormVariant { int id, threads, vpt; };
 static inline NormVariant norm_variant(int H) {
   const int nvec = H >> 3;
-  if (nvec <= 128) return {0, 128, 1, 8};
-  if (nvec <= 256) return {1, 256, 1, 4};
-  if (nvec <= 384) return {2, 384, 1, 3};
-  if (nvec <= 512) return {3, 256, 2, 3};
-  return {4, 256, 4, 2};
+  if (nvec <= 128) return {0, 128, 1};
+  if (nvec <= 256) return {1, 256, 1};
+  if (nvec <= 384) return {2, 384, 1};
+  if (nvec <= 512) return {3, 256, 2};
+  return {4, 256, 4};
 }
 #define KB_NORM_DISPATCH(variant, CALL)           \
   switch ((variant).id) {                         \
@@ -626,6 +690,39 @@ static inline NormVariant norm_variant(int H) {
     case 3: { CALL(256, 2); break; }              \
     default: { CALL(256, 4); break; }             \
   }
+
+// CTAs of `kern` that an SM holds at once (registers and threads), asked from the runtime.
+template <typename Kern>
+static int resident_ctas(Kern kern, int threads) {
+  int n = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, threads, 0) != cudaSuccess || n < 1) n = 1;
+  return n;
+}
+// Persistent grid of the RMSNorm backward for rows of H elements (also the number of partial dw rows).
+static int norm_bwd_ctas(int H) {
+  static int cached[5] = {0, 0, 0, 0, 0};
+  const NormVariant nv = norm_variant(H);
+  if (cached[nv.id] == 0) {
+    int per_sm = 1;
+#define KB_OCC(T_, V_) per_sm = resident_ctas(rmsnorm_bwd_kernel<T_, V_>, T_)
+    KB_NORM_DISPATCH(nv, KB_OCC)
+#undef KB_OCC
+    cached[nv.id] = device_sm_count() * per_sm;
+  }
+  return cached[nv.id];
+}
+static int norm_fwd_ctas(int H) {
+  static int cached[5] = {0, 0, 0, 0, 0};
+  const NormVariant nv = norm_variant(H);
+  if (cached[nv.id] == 0) {
+    int per_sm = 1;
+#define KB_OCC(T_, V_) per_sm = resident_ctas(rmsnorm_fwd_kernel<T_, V_>, T_)
+    KB_NORM_DISPATCH(nv, KB_OCC)
+#undef KB_OCC
+    cached[nv.id] = device_sm_count() * per_sm;
+  }
+  return cached[nv.id];
+}
 
 static inline int grid_for(long work, int threads, int max_blocks) {
   long b = (work + threads - 1) / threads;
@@ -643,7 +740,7 @@ extern "C" int kb_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd
                               cudaStream_t st) {
   if (H % 8 == 0 && H >= 512) {
     const NormVariant nv = norm_variant(H);
-    const int grid = grid_for(rows, 1, 148 * 2 * nv.ctas_per_sm);
+    const int grid = grid_for(rows, 1, norm_fwd_ctas(H));          // one resident wave: rows are dealt evenly
 #define KB_FWD(T_, V_)                                                                                            \
     KB_LAUNCH((rmsnorm_fwd_kernel<T_, V_>), grid, T_, 0, st, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w,      \
               (__nv_bfloat16*)y, rstd, rows, H, eps)
@@ -658,7 +755,7 @@ extern "C" int kb_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd
 
 // Number of fp32 elements of scratch that kb_rmsnorm_bwd needs for a given H (0 for narrow rows).
 extern "C" long kb_rmsnorm_bwd_scratch_elems(int rows, int H) {
-  if (H % 8 == 0 && H >= 512 && H <= NORM_MAX_H) return (long)grid_for(rows, 1, 148 * norm_variant(H).ctas_per_sm) * H;
+  if (H % 8 == 0 && H >= 512 && H <= NORM_MAX_H) return (long)grid_for(rows, 1, norm_bwd_ctas(H)) * H;
   return 0;
 }
 
@@ -668,7 +765,7 @@ extern "C" int kb_rmsnorm_bwd_acc(const void* dy, const void* x, const float* rs
                                   float* scratch, int rows, int H, int accumulate, cudaStream_t st) {
   if (H % 8 == 0 && H >= 512 && H <= NORM_MAX_H) {
     const NormVariant nv = norm_variant(H);
-    const int grid = grid_for(rows, 1, 148 * nv.ctas_per_sm);      // must match kb_rmsnorm_bwd_scratch_elems
+    const int grid = grid_for(rows, 1, norm_bwd_ctas(H));          // must match kb_rmsnorm_bwd_scratch_elems
     if (!scratch) return 7;
 #define KB_BWD(T_, V_)                                                                                              \
     KB_LAUNCH((rmsnorm_bwd_kernel<T_, V_>), grid, T_, 0, st, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, rstd, \

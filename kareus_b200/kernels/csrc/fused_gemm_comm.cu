@@ -133,9 +133,10 @@ __device__ void ag_copy_role(const FusedParams& p, int K, uint8_t* smem, uint64_
       int loaded = 0, stored = 0;
       while (stored < nchunks && ok) {
         // keep the ring full
-        // a slot is refilled only after the store that used it has read it: with at most one
-        // store still reading, loads may run FG_SLOTS-2 chunks ahead of the stores
-        while (loaded < nchunks && loaded - stored < FG_SLOTS - 2) {
+        // a slot is refilled only after the store that used it has read it: at most one store is still
+        // reading (chunk stored-1), and chunk `loaded` shares its slot only when loaded - (stored-1) ==
+        // FG_SLOTS, so loads may run FG_SLOTS-1 chunks ahead of the stores
+        while (loaded < nchunks && loaded - stored < FG_SLOTS - 1) {
           const int slot = (issued + loaded) % FG_SLOTS;
           const long o = static_cast<long>(loaded) * FG_CHUNK;
           const uint32_t bytes = static_cast<uint32_t>(min(static_cast<long>(FG_CHUNK), tile_bytes - o));

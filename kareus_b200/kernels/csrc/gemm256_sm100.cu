@@ -36,7 +36,7 @@ __device__ __forceinline__ void g2_tile_coords(int t, int tiles_m, int tiles_n, 
 template <bool A_MN, bool B_MN, bool OUT_F32, bool ACCUM>
 __global__ void __launch_bounds__(G2_THREADS, 1)
 gemm256_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    void* __restrict__ Cout, int M, int N, int K, int ldc, int group_m, int* status) {
+                    void* __restrict__ Cout, int M, int N, int K, int ldc, int group_m, int ks, int* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + G2_TILE_BYTES);
@@ -51,6 +51,7 @@ gemm256_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int tiles_n = (N + G2_BN - 1) / G2_BN;
   const int num_tiles = tiles_m * tiles_n;
   const int nk = (K + G2_BK - 1) / G2_BK;
+  const int num_units = num_tiles * ks;   // split-K over accumulating outputs, as in gemm_sm100.cu
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < G2_STAGES; ++i) {
@@ -74,11 +75,12 @@ gemm256_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       prefetch_tmap(&tmB);
       uint32_t it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
         int tm, tn;
-        g2_tile_coords(t, tiles_m, tiles_n, group_m, tm, tn);
+        g2_tile_coords(u / ks, tiles_m, tiles_n, group_m, tm, tn);
         const int m0 = tm * G2_BM, n0 = tn * G2_BN;
-        for (int kb_ = 0; kb_ < nk; ++kb_, ++it) {
+        const int kb0 = split_begin(nk, ks, u % ks), kb1 = split_begin(nk, ks, u % ks + 1);
+        for (int kb_ = kb0; kb_ < kb1; ++kb_, ++it) {
           const int s = it % G2_STAGES;
           const uint32_t ph = (it / G2_STAGES) & 1u;
           if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag, status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
@@ -109,10 +111,11 @@ gemm256_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     constexpr uint32_t idesc = make_idesc_bf16(128, G2_BN, A_MN, B_MN);
     uint32_t it = 0, tile_i = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_i) {
+    for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x, ++tile_i) {
       if (!mbar_wait(tempty, (tile_i & 1u) ^ 1u, abort_flag, status, ST_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
       tc_fence_after();
-      for (int kb_ = 0; kb_ < nk; ++kb_, ++it) {
+      const int kb0 = split_begin(nk, ks, u % ks), kb1 = split_begin(nk, ks, u % ks + 1);
+      for (int kb_ = kb0; kb_ < kb1; ++kb_, ++it) {
         const int s = it % G2_STAGES;
         const uint32_t ph = (it / G2_STAGES) & 1u;
         if (!mbar_wait(&full[s], ph, abort_flag, status, ST_TIMEOUT_FULL)) { ok = false; break; }
@@ -130,11 +133,11 @@ gemm256_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               // MN-major → two 64-wide chunks (2 x 8 KB) further on
               const uint64_t ad = A_MN ? make_smem_desc(a_addr + h * 16384 + k * 2048, 8192, 1024)
                                        : make_smem_desc(a_addr + h * 16384 + k * 32, 16, 1024);
-              umma_ss(tmem_base + h * G2_BN, ad, bd, idesc, (kb_ > 0 || k > 0) ? 1u : 0u);
+              umma_ss(tmem_base + h * G2_BN, ad, bd, idesc, (kb_ > kb0 || k > 0) ? 1u : 0u);
             }
           }
           umma_commit(&empty[s]);
-          if (kb_ == nk - 1) umma_commit(tfull);
+          if (kb_ == kb1 - 1) umma_commit(tfull);
         }
         __syncwarp();
       }
@@ -143,9 +146,9 @@ gemm256_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const int q = warp & 3;
     uint32_t tile_i = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_i) {
+    for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x, ++tile_i) {
       int tm, tn;
-      g2_tile_coords(t, tiles_m, tiles_n, group_m, tm, tn);
+      g2_tile_coords(u / ks, tiles_m, tiles_n, group_m, tm, tn);
       const int m0 = tm * G2_BM, n0 = tn * G2_BN;
       if (!mbar_wait(tfull, tile_i & 1u, abort_flag, status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
@@ -208,6 +211,7 @@ gemm256_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                                          __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
                   float4* p = reinterpret_cast<float4*>(crow) + j;
                   if constexpr (ACCUM) {
+                    if (ks > 1) { red_add_f32x4(p, o); continue; }
                     const float4 old = *p;
                     o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
                   }
@@ -216,7 +220,10 @@ gemm256_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               } else {
                 for (int j = 0; j < 32 && col + j < N; ++j) {
                   float o = __uint_as_float(v[j]);
-                  if constexpr (ACCUM) o += crow[j];
+                  if constexpr (ACCUM) {
+                    if (ks > 1) { atomicAdd(crow + j, o); continue; }
+                    o += crow[j];
+                  }
                   crow[j] = o;
                 }
               }
@@ -255,7 +262,7 @@ gemm256_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
 template <bool A_MN, bool B_MN, bool OUT_F32, bool ACCUM>
 static int launch256(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc, int num_sms,
-                     int* status, cudaStream_t stream) {
+                     int ks, int* status, cudaStream_t stream) {
   CUtensorMap tmA, tmB;
   int rc;
   if (!A_MN) rc = make_tmap_2d_bf16(&tmA, A, K, M, lda, G2_BK, G2_BM);
@@ -272,24 +279,25 @@ static int launch256(const void* A, const void* B, void* C, int M, int N, int K,
     configured = true;
   }
   const int tiles_m = (M + G2_BM - 1) / G2_BM;
-  const int tiles = tiles_m * ((N + G2_BN - 1) / G2_BN);
+  if (!ACCUM || ks < 1) ks = 1;
+  const int tiles = tiles_m * ((N + G2_BN - 1) / G2_BN) * ks;
   int grid = tiles < num_sms ? tiles : num_sms;
   long panel = (long)G2_BM * K * 2;
   int group_m = (int)((40L << 20) / (panel > 0 ? panel : 1));
   if (group_m < 2) group_m = 2;
   if (group_m > tiles_m) group_m = tiles_m;
-  KB_LAUNCH(kern, grid, G2_THREADS, G2_SMEM, stream, tmA, tmB, C, M, N, K, ldc, group_m, status);
+  KB_LAUNCH(kern, grid, G2_THREADS, G2_SMEM, stream, tmA, tmB, C, M, N, K, ldc, group_m, ks, status);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 2000 + static_cast<int>(e);
 }
 
 int gemm256_dispatch(const void* A, const void* B, void* C, int M, int N, int K, int a_mn, int lda, int b_mn, int ldb,
-                     int ldc, int out_f32, int accumulate, int num_sms, int* status, cudaStream_t stream) {
+                     int ldc, int out_f32, int accumulate, int num_sms, int ks, int* status, cudaStream_t stream) {
 #define G2_GO(AM, BM_)                                                                                          \
   do {                                                                                                          \
-    if (out_f32 && accumulate) return launch256<AM, BM_, true, true>(A, B, C, M, N, K, lda, ldb, ldc, num_sms, status, stream);  \
-    if (out_f32) return launch256<AM, BM_, true, false>(A, B, C, M, N, K, lda, ldb, ldc, num_sms, status, stream);               \
-    return launch256<AM, BM_, false, false>(A, B, C, M, N, K, lda, ldb, ldc, num_sms, status, stream);                           \
+    if (out_f32 && accumulate) return launch256<AM, BM_, true, true>(A, B, C, M, N, K, lda, ldb, ldc, num_sms, ks, status, stream);  \
+    if (out_f32) return launch256<AM, BM_, true, false>(A, B, C, M, N, K, lda, ldb, ldc, num_sms, ks, status, stream);               \
+    return launch256<AM, BM_, false, false>(A, B, C, M, N, K, lda, ldb, ldc, num_sms, ks, status, stream);                           \
   } while (0)
   if (!a_mn && !b_mn) G2_GO(false, false);
   if (!a_mn && b_mn) G2_GO(false, true);

@@ -19,7 +19,7 @@
 namespace kb {
 
 int gemm256_dispatch(const void* A, const void* B, void* C, int M, int N, int K, int a_mn, int lda, int b_mn, int ldb,
-                     int ldc, int out_f32, int accumulate, int num_sms, int* status, cudaStream_t stream);
+                     int ldc, int out_f32, int accumulate, int num_sms, int ks, int* status, cudaStream_t stream);
 
 constexpr int GEMM_BM = 128;
 constexpr int GEMM_BK = 64;
@@ -72,7 +72,8 @@ __device__ __forceinline__ void apply_epilogue(uint32_t (&v)[32], const Epilogue
 template <int BN, bool A_MN, bool B_MN, bool OUT_F32, bool ACCUM>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 void* __restrict__ Cout, int M, int N, int K, int ldc, int group_m, int* status, Epilogue ep) {
+                 void* __restrict__ Cout, int M, int N, int K, int ldc, int group_m, int ks, int* status,
+                 Epilogue ep) {
   using S = GemmSmem<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -89,6 +90,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int tiles_n = (N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
   const int nk = (K + GEMM_BK - 1) / GEMM_BK;
+  // split-K (accumulating outputs only): unit u = (tile u / ks, K part u % ks); every part adds its
+  // partial sum to C with vector reductions, so parts of one tile may run on different SMs at once
+  const int num_units = num_tiles * ks;
   constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : 2 * BN;
 
   if (threadIdx.x == 0) {
@@ -116,12 +120,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       prefetch_tmap(&tmB);
       uint32_t it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
         int tm, tn;
-        tile_coords(t, tiles_m, tiles_n, group_m, tm, tn);
+        tile_coords(u / ks, tiles_m, tiles_n, group_m, tm, tn);
         const int m0 = tm * GEMM_BM;
         const int n0 = tn * BN;
-        for (int kb_ = 0; kb_ < nk; ++kb_, ++it) {
+        const int kb0 = split_begin(nk, ks, u % ks), kb1 = split_begin(nk, ks, u % ks + 1);
+        for (int kb_ = kb0; kb_ < kb1; ++kb_, ++it) {
           const int s = it % GEMM_STAGES;
           const uint32_t ph = (it / GEMM_STAGES) & 1u;
           if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag, status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
@@ -155,13 +160,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint32_t it = 0;
     uint32_t tile_i = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_i) {
+    for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x, ++tile_i) {
       const uint32_t buf = tile_i & 1u;
       const uint32_t bph = (tile_i >> 1) & 1u;
       if (!mbar_wait(&tempty[buf], bph ^ 1u, abort_flag, status, ST_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + buf * BN;
-      for (int kb_ = 0; kb_ < nk; ++kb_, ++it) {
+      const int kb0 = split_begin(nk, ks, u % ks), kb1 = split_begin(nk, ks, u % ks + 1);
+      for (int kb_ = kb0; kb_ < kb1; ++kb_, ++it) {
         const int s = it % GEMM_STAGES;
         const uint32_t ph = (it / GEMM_STAGES) & 1u;
         if (!mbar_wait(&full[s], ph, abort_flag, status, ST_TIMEOUT_FULL)) { ok = false; break; }
@@ -175,10 +181,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                      : make_smem_desc(a_addr + k * 32, 16, 1024);
             const uint64_t bd = B_MN ? make_smem_desc(b_addr + k * 2048, 8192, 1024)
                                      : make_smem_desc(b_addr + k * 32, 16, 1024);
-            umma_ss(d_tmem, ad, bd, idesc, (kb_ > 0 || k > 0) ? 1u : 0u);
+            umma_ss(d_tmem, ad, bd, idesc, (kb_ > kb0 || k > 0) ? 1u : 0u);
           }
           umma_commit(&empty[s]);                       // stage reusable once these MMAs retire
-          if (kb_ == nk - 1) umma_commit(&tfull[buf]);  // accumulator complete
+          if (kb_ == kb1 - 1) umma_commit(&tfull[buf]); // accumulator complete
         }
         __syncwarp();
       }
@@ -188,11 +194,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int q = warp & 3;                 // TMEM lane quarter this warp may read
     uint32_t tile_i = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_i) {
+    for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x, ++tile_i) {
       const uint32_t buf = tile_i & 1u;
       const uint32_t bph = (tile_i >> 1) & 1u;
       int tm, tn;
-      tile_coords(t, tiles_m, tiles_n, group_m, tm, tn);
+      tile_coords(u / ks, tiles_m, tiles_n, group_m, tm, tn);
       const int m0 = tm * GEMM_BM;
       const int n0 = tn * BN;
       if (!mbar_wait(&tfull[buf], bph, abort_flag, status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
@@ -260,6 +266,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                        __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
                 float4* p = reinterpret_cast<float4*>(crow) + j;
                 if constexpr (ACCUM) {
+                  if (ks > 1) { red_add_f32x4(p, o); continue; }
                   float4 old = *p;
                   o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
                 }
@@ -268,7 +275,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             } else {
               for (int j = 0; j < 32 && col + j < N; ++j) {
                 float o = __uint_as_float(v[j]);
-                if constexpr (ACCUM) o += crow[j];
+                if constexpr (ACCUM) {
+                  if (ks > 1) { atomicAdd(crow + j, o); continue; }
+                  o += crow[j];
+                }
                 crow[j] = o;
               }
             }
@@ -307,7 +317,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 // ----------------------------------------------------------------------------- host side
 template <int BN, bool A_MN, bool B_MN, bool OUT_F32, bool ACCUM>
 static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
-                       int num_sms, int* status, cudaStream_t stream, Epilogue ep) {
+                       int num_sms, int ks, int* status, cudaStream_t stream, Epilogue ep) {
   CUtensorMap tmA, tmB;
   int rc;
   // K-major operand: dims (K, rows), box (64, tile rows).  MN-major: dims (rows, K), box (64, 64).
@@ -325,7 +335,8 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
     if (e != cudaSuccess) return 1000 + static_cast<int>(e);
     configured = true;
   }
-  const int tiles = ((M + GEMM_BM - 1) / GEMM_BM) * ((N + BN - 1) / BN);
+  if (!ACCUM || ks < 1) ks = 1;
+  const int tiles = ((M + GEMM_BM - 1) / GEMM_BM) * ((N + BN - 1) / BN) * ks;
   int grid = tiles < num_sms ? tiles : num_sms;
   if (grid < 1) grid = 1;
   // m-tiles per group: keep the group's A panel near 40 MB so A and B panels share the 126 MB L2
@@ -334,23 +345,92 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
   int group_m = (int)((40L << 20) / (panel > 0 ? panel : 1));
   if (group_m < 4) group_m = 4;
   if (group_m > tiles_m) group_m = tiles_m;
-  KB_LAUNCH(kern, grid, GEMM_THREADS, smem, stream, tmA, tmB, C, M, N, K, ldc, group_m, status, ep);
+  KB_LAUNCH(kern, grid, GEMM_THREADS, smem, stream, tmA, tmB, C, M, N, K, ldc, group_m, ks, status, ep);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 2000 + static_cast<int>(e);
 }
 
 template <int BN, bool A_MN, bool B_MN>
 static int dispatch_out(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
-                        int out_f32, int accumulate, int num_sms, int* status, cudaStream_t stream, Epilogue ep) {
+                        int out_f32, int accumulate, int num_sms, int ks, int* status, cudaStream_t stream,
+                        Epilogue ep) {
   if (out_f32 && accumulate)
-    return launch_gemm<BN, A_MN, B_MN, true, true>(A, B, C, M, N, K, lda, ldb, ldc, num_sms, status, stream, ep);
+    return launch_gemm<BN, A_MN, B_MN, true, true>(A, B, C, M, N, K, lda, ldb, ldc, num_sms, ks, status, stream, ep);
   if (out_f32)
-    return launch_gemm<BN, A_MN, B_MN, true, false>(A, B, C, M, N, K, lda, ldb, ldc, num_sms, status, stream, ep);
+    return launch_gemm<BN, A_MN, B_MN, true, false>(A, B, C, M, N, K, lda, ldb, ldc, num_sms, 1, status, stream, ep);
   if (accumulate) return ST_BAD_ARG;
-  return launch_gemm<BN, A_MN, B_MN, false, false>(A, B, C, M, N, K, lda, ldb, ldc, num_sms, status, stream, ep);
+  return launch_gemm<BN, A_MN, B_MN, false, false>(A, B, C, M, N, K, lda, ldb, ldc, num_sms, 1, status, stream, ep);
+}
+
+// ----------------------------------------------------------------------------- split-K choice
+// Modelled time of an accumulating GEMM in units of one 64-deep K step of a 128x256 tile (~0.4 us):
+// `waves` rounds of one unit each; a unit costs its K steps plus a fixed part (pipeline fill, epilogue,
+// and with ks > 1 the reductions that every part sends to C).  Constants fitted to a sweep over the
+// weight-gradient shapes of a 3B Llama layer at tensor-parallel sizes 1, 2 and 8 on a B200:
+//   step   1.0 (128x256), 0.6 (128x128), 1.85 (256x256: twice the FLOPs, a little less L2 traffic per
+//          FLOP)
+//   fixed  14 + 2 ks (128-row tiles), 26 + 3 ks (256x256)
+static inline double model_time(long tiles, int ks, int nk, int grid, double step, double fixed0, double fixed_ks) {
+  const long units = tiles * ks;
+  const long waves = (units + grid - 1) / grid;
+  return waves * (static_cast<double>((nk + ks - 1) / ks) * step + fixed0 + fixed_ks * ks);
+}
+
+struct SplitChoice {
+  int ks;
+  double time;
+};
+static SplitChoice choose_split(long tiles, int nk, int grid, double step, double fixed0, double fixed_ks) {
+  static const bool allow = [] { const char* e = getenv("KB_GEMM_SPLITK"); return !(e && e[0] == '0'); }();
+  SplitChoice best{1, model_time(tiles, 1, nk, grid, step, fixed0, fixed_ks)};
+  if (!allow) return best;
+  for (int ks = 2; ks <= 8; ++ks) {
+    if (nk / ks < 8) break;
+    const double t = model_time(tiles, ks, nk, grid, step, fixed0, fixed_ks);
+    if (t < best.time * 0.97) best = SplitChoice{ks, t};       // a split must pay for its extra traffic
+  }
+  return best;
+}
+
+// Accumulating output (weight gradients: few tiles, long K): tile and K split by modelled time.
+struct AccumPlan {
+  bool tile256;
+  int ks;
+};
+static int g_force_tile = 0, g_force_ks = 0;   // measurement override, see kb_gemm_accum_force
+static AccumPlan plan_accumulate(int M, int N, int K, int num_sms, bool fits256) {
+  const int nk = (K + GEMM_BK - 1) / GEMM_BK;
+  if (g_force_ks > 0) {
+    const int ks = g_force_ks <= nk ? g_force_ks : nk;
+    return AccumPlan{g_force_tile == 256 && fits256, ks};
+  }
+  const bool narrow = (N <= 128) || (N % 256 != 0 && N % 256 <= 128);
+  const int bn = narrow ? 128 : 256;
+  const long tiles128 = (long)((M + GEMM_BM - 1) / GEMM_BM) * ((N + bn - 1) / bn);
+  const SplitChoice c128 = choose_split(tiles128, nk, num_sms, narrow ? 0.6 : 1.0, 14.0, 2.0);
+  if (fits256) {
+    const long tiles256 = (long)((M + 255) / 256) * ((N + 255) / 256);
+    const SplitChoice c256 = choose_split(tiles256, nk, num_sms, 1.85, 26.0, 3.0);
+    if (c256.time < c128.time) return AccumPlan{true, c256.ks};
+  }
+  return AccumPlan{false, c128.ks};
 }
 
 }  // namespace kb
+
+// Tile (128 or 256 rows) and K split that kb_gemm_bf16 uses for an accumulating fp32 output of this shape.
+extern "C" void kb_gemm_accum_plan(int M, int N, int K, int num_sms, int* tile_rows, int* ks) {
+  const bool fits256 = M >= 512 && N >= 512 && K >= 2048 && (N % 256 == 0 || N >= 4096);
+  const kb::AccumPlan pl = kb::plan_accumulate(M, N, K, num_sms, fits256);
+  *tile_rows = pl.tile256 ? 256 : 128;
+  *ks = pl.ks;
+}
+
+// Measurement aid: force the tile (128 / 256) and K split of accumulating GEMMs; ks = 0 returns to the model.
+extern "C" void kb_gemm_accum_force(int tile_rows, int ks) {
+  kb::g_force_tile = tile_rows;
+  kb::g_force_ks = ks;
+}
 
 // C[M,N] (+)= op(A) * op(B)^T.
 //   a_mn = 0: A is [M, K] row-major (lda = row stride in elements); a_mn = 1: A is stored [K, M].
@@ -371,23 +451,32 @@ extern "C" int kb_gemm_bias_act_bf16(const void* A, const void* B, void* C, int 
   if ((lda & 7) || (ldb & 7) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
     return ST_BAD_ARG;
   if (num_sms <= 0) num_sms = device_sm_count();
+  int ks = 1;
   {
     // large problems with a long K loop: 256x256 tile per SM (a third less L2 traffic per FLOP; its
     // epilogue is not overlapped, which only pays off when the main loop is long), see gemm256_sm100.cu
     static const bool allow256 = [] { const char* e = getenv("KB_GEMM256"); return !(e && e[0] == '0'); }();
     const long tiles256 = (long)((M + 255) / 256) * ((N + 255) / 256);
-    if (plain && allow256 && M >= 512 && N >= 512 && K >= 2048 && (N % 256 == 0 || N >= 4096) && tiles256 >= num_sms)
-      return gemm256_dispatch(A, B, C, M, N, K, a_mn, lda, b_mn, ldb, ldc, out_f32, accumulate, num_sms, status,
+    const bool fits256 = plain && allow256 && M >= 512 && N >= 512 && K >= 2048 && (N % 256 == 0 || N >= 4096);
+    if (fits256 && !(out_f32 && accumulate) && tiles256 >= num_sms)
+      return gemm256_dispatch(A, B, C, M, N, K, a_mn, lda, b_mn, ldb, ldc, out_f32, accumulate, num_sms, 1, status,
                               stream);
+    if (out_f32 && accumulate) {
+      const AccumPlan pl = plan_accumulate(M, N, K, num_sms, fits256);
+      ks = pl.ks;
+      if (pl.tile256)
+        return gemm256_dispatch(A, B, C, M, N, K, a_mn, lda, b_mn, ldb, ldc, out_f32, accumulate, num_sms, pl.ks,
+                                status, stream);
+    }
   }
   // narrow outputs waste less of the last wave with the 128-wide tile
   const bool narrow = (N <= 128) || (N % 256 != 0 && N % 256 <= 128);
 #define KB_GO(BN_)                                                                                         \
   do {                                                                                                     \
-    if (!a_mn && !b_mn) return dispatch_out<BN_, false, false>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, accumulate, num_sms, status, stream, ep); \
-    if (!a_mn && b_mn) return dispatch_out<BN_, false, true>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, accumulate, num_sms, status, stream, ep);   \
-    if (a_mn && !b_mn) return dispatch_out<BN_, true, false>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, accumulate, num_sms, status, stream, ep);   \
-    return dispatch_out<BN_, true, true>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, accumulate, num_sms, status, stream, ep);                       \
+    if (!a_mn && !b_mn) return dispatch_out<BN_, false, false>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, accumulate, num_sms, ks, status, stream, ep); \
+    if (!a_mn && b_mn) return dispatch_out<BN_, false, true>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, accumulate, num_sms, ks, status, stream, ep);   \
+    if (a_mn && !b_mn) return dispatch_out<BN_, true, false>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, accumulate, num_sms, ks, status, stream, ep);   \
+    return dispatch_out<BN_, true, true>(A, B, C, M, N, K, lda, ldb, ldc, out_f32, accumulate, num_sms, ks, status, stream, ep);                       \
   } while (0)
   if (narrow) KB_GO(128);
   KB_GO(256);

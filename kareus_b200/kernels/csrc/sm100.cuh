@@ -249,4 +249,16 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// First K step of part `part` when `nk` steps are split into `ks` nearly equal parts (part == ks: nk).
+__host__ __device__ __forceinline__ int split_begin(int nk, int ks, int part) {
+  return static_cast<int>(static_cast<long>(nk) * part / ks);
+}
+
+// C[0..3] += v, one 16-byte reduction that returns nothing (p 16-byte aligned).
+__device__ __forceinline__ void red_add_f32x4(float4* p, const float4& v) {
+  asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z),
+               "f"(v.w)
+               : "memory");
+}
+
 }  // namespace kb

@@ -16,6 +16,7 @@ Timing tables (CUDA events, no profiler; L2 flushed between launches):
 """
 from __future__ import annotations
 
+import os
 import sys
 
 import torch
@@ -70,6 +71,49 @@ def gemm_table() -> None:
     print("| GEMM | M | N | K | this library TFLOP/s | cuBLAS TFLOP/s |\n|---|---|---|---|---|---|")
     for r in rows:
         print(f"| {r[0]} | {r[1]} | {r[2]} | {r[3]} | {r[4]:.0f} | {r[5]:.0f} |")
+
+
+def wgrad_sweep() -> None:
+    """Weight-gradient GEMMs (fp32 accumulate, K = 16384 tokens) of the 3B layer at TP 1/2/8 with every
+    tile (128 / 256 rows) and K split forced in turn; the last column is what the library picks by itself."""
+    import ctypes
+    from . import cuda as KC
+    L = KC.lib()
+    L.kb_gemm_accum_force.argtypes = [ctypes.c_int, ctypes.c_int]
+    L.kb_gemm_accum_force.restype = None
+    L.kb_gemm_accum_plan.argtypes = [ctypes.c_int] * 4 + [ctypes.POINTER(ctypes.c_int)] * 2
+    L.kb_gemm_accum_plan.restype = None
+    dev = "cuda"
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    tokens = 16384
+    splits = (1, 2, 3, 4, 6, 8)
+    print("| wgrad | out x in | " + " | ".join(f"{t}/ks{k}" for t in (128, 256) for k in splits)
+          + " | picked | picked TFLOP/s | cuBLAS TFLOP/s |")
+    print("|---|---|" + "---|" * (2 * len(splits) + 3))
+    for tp in (1, 2, 8):
+        shapes = {"qkv": (5120 // tp, 3072), "proj": (3072, 3072 // tp), "fc1": (16384 // tp, 3072),
+                  "fc2": (3072, 8192 // tp)}
+        for name, (n_out, n_in) in shapes.items():
+            dy = torch.randn(tokens, n_out, device=dev).bfloat16()
+            x = torch.randn(tokens, n_in, device=dev).bfloat16()
+            acc = torch.zeros(n_out, n_in, device=dev)
+            flops = 2.0 * tokens * n_out * n_in
+            run = lambda: KC.gemm(dy, x, trans_a=True, trans_b=False, accumulate=acc)
+            cells = []
+            for tile in (128, 256):
+                for ks in splits:
+                    L.kb_gemm_accum_force(tile, ks)
+                    cells.append(flops / _timed(run, flush, iters=5, skip=2) / 1e9)
+            L.kb_gemm_accum_force(0, 0)
+            t_auto = _timed(run, flush)
+            t_lib = _timed(lambda: torch.matmul(dy.t(), x), flush)
+            tile_c, ks_c = ctypes.c_int(), ctypes.c_int()
+            L.kb_gemm_accum_plan(n_out, n_in, tokens, KC.sm_count(),
+                                 ctypes.byref(tile_c), ctypes.byref(ks_c))
+            print(f"| tp{tp} {name} | {n_out} x {n_in} | " + " | ".join(f"{c:.0f}" for c in cells)
+                  + f" | {tile_c.value}/ks{ks_c.value} | {flops / t_auto / 1e9:.0f} | {flops / t_lib / 1e9:.0f} |")
+            del dy, x, acc
+    KC.check_status()
 
 
 def attn_table() -> None:
@@ -160,15 +204,19 @@ def fused_table() -> None:
         rows_in = M // world if kind == "ag" else M
         x = torch.randn(rows_in, 1, red, device=dev).bfloat16()
 
+        # KAREUS_TABLE_PLANNED=1: the driver count is used as given (a plan's value); otherwise the
+        # all-gather kernels scale it by their output width as they do in an unplanned run
+        planned = os.environ.get("KAREUS_TABLE_PLANNED", "0") == "1"
+
         def call():
             if not bwd:
                 ctx = OpContext()
                 ctx.requires_grad = False
-                op.run((x,), sm_num=sm, nb=0, ctx=ctx)
+                op.run((x,), sm_num=sm, nb=0, ctx=ctx, planned=planned)
             elif cls is FusedDgradRS:
                 op._gemm_rs(x.reshape(-1, red), w, out, True, 0, 0)      # whole SM budget, none left free
             else:
-                op._ag_gemm(x.reshape(-1, red), w, out, True, sm, 0)
+                op._ag_gemm(x.reshape(-1, red), w, out, True, sm, 0, planned)
 
         # `reps` calls back to back per sample: the ranks' GPUs do not start a sample at the same instant
         # (host skew after the barrier), and with a single call the early ranks' wait for the late one
@@ -264,6 +312,8 @@ def main(case: str, reps: int = 3) -> None:
     dev = "cuda"
     if case == "collectives":
         return collectives_table()
+    if case == "wgrad_sweep":
+        return wgrad_sweep()
     if case == "gemm_table":
         return gemm_table()
     if case == "attn_table":

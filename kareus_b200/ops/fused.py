@@ -121,10 +121,25 @@ class _FusedBase:
         return t
 
     # ---- kernels ------------------------------------------------------------------------------
-    def _ag_gemm(self, x2, w, n_out, b_mn: bool, sm_num, nb: int):
+    @staticmethod
+    def auto_drivers(sm_num: int, n_out: int) -> int:
+        """Copy-driver CTAs when no plan names them.  Every driver keeps a fixed number of bytes in flight, so
+        the pull rate grows with their number; a kernel with little math (narrow N) can give up GEMM CTAs for
+        drivers until its GEMM takes as long as the gather: three times the base count up to N = 768, twice
+        up to N = 1280."""
+        if n_out <= 768:
+            return min(3 * sm_num, 48)
+        if n_out <= 1280:
+            return min(2 * sm_num, 48)
+        return sm_num
+
+    def _ag_gemm(self, x2, w, n_out, b_mn: bool, sm_num, nb: int, planned: bool = True):
         """Gather ``x2`` ([Ms, K] shard) over the group and multiply: returns ``(y [M, n_out], xg [M, K])``
         where ``xg`` is the gathered input inside the heap (valid until this site's next call)."""
         heap = self.heap
+        sm_num = int(sm_num or self.default_sm)
+        if not planned:
+            sm_num = self.auto_drivers(sm_num, n_out)
         world, rank = heap.world, heap.rank
         ms, k = x2.shape
         m = ms * world
@@ -216,7 +231,7 @@ class FusedAGGemm(_FusedBase):
         (x,) = tensors
         lin = self.linear
         lead = x.shape[:-1]
-        y, xg = self._ag_gemm(x.reshape(-1, x.shape[-1]), lin.weight, lin.out_features, False, sm_num, nb)
+        y, xg = self._ag_gemm(x.reshape(-1, x.shape[-1]), lin.weight, lin.out_features, False, sm_num, nb, planned)
         if ctx is not None and ctx.requires_grad:
             ctx.save_for_backward(_replay.clone(xg))  # gathered input for the wgrad GEMM
         return (y.reshape((lead[0] * self.heap.world,) + tuple(lead[1:]) + (lin.out_features,)),)
@@ -262,7 +277,7 @@ class FusedAGDgrad(_FusedBase):
         lin = self.linear
         (a2,) = ctx.saved_tensors
         lead = dy.shape[:-1]
-        dx, dyg = self._ag_gemm(dy.reshape(-1, dy.shape[-1]), lin.weight, lin.in_features, True, sm_num, nb)
+        dx, dyg = self._ag_gemm(dy.reshape(-1, dy.shape[-1]), lin.weight, lin.in_features, True, sm_num, nb, planned)
         _wgrad(dyg, a2, lin.weight)
         if dyg.is_cuda:
             # `dyg` lives in this call site's heap buffer, which the site's next call overwrites: when

@@ -44,6 +44,36 @@ def test_gemm_layouts(M, N, K, ta, tb):
         assert _rel(acc, want2) < 2e-3
 
 
+@pytest.mark.parametrize("tile,ks", [(128, 2), (128, 3), (128, 7), (256, 2), (256, 5)])
+@pytest.mark.parametrize("n_out,n_in,tokens", [(640, 3072, 4096), (3072, 384, 2048), (1024, 1024, 8192),
+                                               (520, 776, 4096)])
+def test_weight_gradient_split_k(tile, ks, n_out, n_in, tokens):
+    """dW += dYᵀ·X with the K (token) loop split over several CTAs per tile: every part adds its partial
+    sum with vector reductions.  Forced splits and what the library picks itself against fp32."""
+    import ctypes
+    KC = _K()
+    L = KC.lib()
+    L.kb_gemm_accum_force.argtypes = [ctypes.c_int, ctypes.c_int]
+    L.kb_gemm_accum_force.restype = None
+    g = torch.Generator(device="cuda").manual_seed(tile + ks + n_out)
+    dy = torch.randn(tokens, n_out, device="cuda", generator=g).bfloat16()
+    x = torch.randn(tokens, n_in, device="cuda", generator=g).bfloat16()
+    start = torch.randn(n_out, n_in, device="cuda", generator=g)
+    want = start + dy.float().t() @ x.float()
+    try:
+        L.kb_gemm_accum_force(tile, ks)
+        acc = start.clone()
+        KC.gemm(dy, x, trans_a=True, trans_b=False, accumulate=acc)
+        KC.check_status()
+        assert _rel(acc, want) < 2e-3
+    finally:
+        L.kb_gemm_accum_force(0, 0)
+    acc = start.clone()
+    KC.gemm(dy, x, trans_a=True, trans_b=False, accumulate=acc)
+    KC.check_status()
+    assert _rel(acc, want) < 2e-3
+
+
 def test_gemm_sm_limit_and_views():
     KC = _K()
     a = torch.randn(512, 1024, device="cuda").bfloat16()

@@ -1,16 +1,22 @@
 // Causal GQA flash-attention backward for sm_100a (head dim 128, bf16, fp32 accumulation).
 //
 // One CTA owns 128 keys of one (batch, query head) and walks the query tiles that can see them:
-//   warp 0      TMA producer: K and V once, then Q and dO per query tile
+//   warp 0      TMA producer: K and V once, then per query tile Q (two buffers, one tile ahead) and dO
 //   warp 1      MMA issuer (tcgen05, accumulators in TMEM):
 //                 S  = Q·Kᵀ          dP = dO·Vᵀ                       (per query tile)
 //                 dV += Pᵀ·dO        dK += dSᵀ·Q        dQ = dS·K      (per query tile)
-//   warps 2..5  one thread per query row: P = exp2(S·c − lse), dS = P∘(dP − δ)·scale, both as bf16
-//               into swizzled shared memory; later dQ from TMEM → fp32 vector reductions in global.
+//   warps 2..5  one thread per query row: P = exp2(S·c − lse) as soon as S is there (dO of the tile may
+//               still be on its way), then dS = P∘(dP − δ)·scale once dP is there; both as bf16 into
+//               swizzled shared memory
+//   warps 6..9  dQ from TMEM → fp32 vector reductions in global, while the next tile is worked on
+// The walk is a pipeline: S of tile i+1 is issued right behind the three products of tile i (its Q is
+// already in shared memory), the dO buffer is refilled as soon as those products retire, and dQ of
+// tile i is drained while P of tile i+1 is computed.
 // P and dS are stored once ([q][key], keys contiguous) and serve as K-major operands (dQ) and, read
 // through MN-major descriptors, as the transposed operands of dV and dK — no transposes anywhere.
-// TMEM: S|dQ (shared) + dP + dV + dK = 512 columns.  dK/dV stay in TMEM across the whole walk and
+// TMEM: S + dP|dQ (shared) + dV + dK = 512 columns.  dK/dV stay in TMEM across the whole walk and
 // are added to fp32 accumulators at the end (query heads of one KV group run in different CTAs).
+// Shared memory: K, V, Q x 2, dO, P, dS = 7 tiles of 32 KB.
 // A second kernel converts the fp32 accumulators into the packed bf16 gradient of the QKV GEMM.
 //
 // Chunked keys and queries (context parallelism, see attention_chunks.h): K/V tiles may come from
@@ -31,7 +37,7 @@ namespace kb {
 constexpr int FB_T = 128;                      // tile edge (queries, keys) and head dim
 constexpr int FB_TILE = FB_T * FB_T * 2;       // 32 KB bf16 tile as two 64-wide swizzled chunks
 constexpr int FB_CHUNK = 16384;
-constexpr int FB_THREADS = 192;
+constexpr int FB_THREADS = 320;
 
 struct BwdParams {
   const float* lse;      // [b, hq, sq]  natural log
@@ -53,8 +59,10 @@ __device__ __forceinline__ bool q_tile_sees(const BwdParams& p, int qt, int k0) 
 }
 
 struct FbSmem {
-  static constexpr int K_OFF = 0, V_OFF = FB_TILE, Q_OFF = 2 * FB_TILE, DO_OFF = 3 * FB_TILE, P_OFF = 4 * FB_TILE,
-                       DS_OFF = 5 * FB_TILE, BAR_OFF = 6 * FB_TILE, TOTAL = BAR_OFF + 256 + 1024;
+  // Q_OFF: two consecutive tiles (buffer = iteration & 1)
+  static constexpr int K_OFF = 0, V_OFF = FB_TILE, Q_OFF = 2 * FB_TILE, DO_OFF = 4 * FB_TILE, P_OFF = 5 * FB_TILE,
+                       DS_OFF = 6 * FB_TILE, BAR_OFF = 7 * FB_TILE, TOTAL = BAR_OFF + 256 + 1024;
+  static_assert(TOTAL <= 227 * 1024, "shared memory per CTA");
 };
 
 __device__ __forceinline__ float bwd_exp2(float x) {
@@ -73,13 +81,17 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FbSmem::BAR_OFF);
   uint64_t* kv_full = bars + 0;
-  uint64_t* qdo_full = bars + 1;
-  uint64_t* qdo_empty = bars + 2;   // MMAs that read Q/dO/P/dS of this iteration have retired
-  uint64_t* s_full = bars + 3;      // S and dP are in TMEM
-  uint64_t* pds_full = bars + 4;    // P and dS are in shared memory (4 warp arrivals)
-  uint64_t* dq_full = bars + 5;     // dQ (and this iteration's dV/dK updates) retired
-  uint64_t* dq_empty = bars + 6;    // dQ has been read out of TMEM (4 warp arrivals)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
+  uint64_t* q_full = bars + 1;      // [2] Q of iteration i is in buffer i & 1
+  uint64_t* q_empty = bars + 3;     // [2] the MMAs that read that buffer have retired
+  uint64_t* do_full = bars + 5;
+  uint64_t* do_empty = bars + 6;    // the MMAs that read dO (and P, dS) of this iteration have retired
+  uint64_t* s_full = bars + 7;      // S is in TMEM
+  uint64_t* dp_full = bars + 8;     // dP is in TMEM
+  uint64_t* pds_full = bars + 9;    // P and dS are in shared memory, S and dP have been read (4 warp arrivals)
+  uint64_t* dq_full = bars + 10;    // dQ (and this iteration's dV/dK updates) retired
+  uint64_t* dq_empty = bars + 11;   // dQ has been read out of TMEM (4 warp arrivals)
+  uint64_t* all_done = bars + 12;   // every MMA of the walk has retired
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -93,12 +105,18 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
-    mbar_init(qdo_full, 1);
-    mbar_init(qdo_empty, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&q_full[i], 1);
+      mbar_init(&q_empty[i], 1);
+    }
+    mbar_init(do_full, 1);
+    mbar_init(do_empty, 1);
     mbar_init(s_full, 1);
+    mbar_init(dp_full, 1);
     mbar_init(pds_full, 4);
     mbar_init(dq_full, 1);
     mbar_init(dq_empty, 4);
+    mbar_init(all_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -107,7 +125,10 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // dQ of a tile goes where its dP was: dP has been read by then, and S of the next tile can be issued
+  // while dQ is drained
   const uint32_t t_s = tmem_base, t_dp = tmem_base + 128, t_dv = tmem_base + 256, t_dk = tmem_base + 384;
+  const uint32_t t_dq = t_dp;
 
   if (warp == 0) {
     if (lane == 0 && n_it > 0) {
@@ -119,17 +140,24 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       tma_load_4d(smem + FbSmem::K_OFF + FB_CHUNK, &kv.k[src], kv_full, 64, g, batch, srow);
       tma_load_4d(smem + FbSmem::V_OFF, &kv.v[src], kv_full, 0, g, batch, srow);
       tma_load_4d(smem + FbSmem::V_OFF + FB_CHUNK, &kv.v[src], kv_full, 64, g, batch, srow);
+      // per visible tile: Q(it) into buffer it & 1, then dO(it).  The buffer of Q(it) was released by the
+      // products of tile it-2 and dO by those of tile it-1, so Q(it+1) goes out right behind dO(it): one
+      // tile ahead of the MMAs.
       int it = 0;
       for (int qt = 0; qt < n_q; ++qt) {
         if (!q_tile_sees(p, qt, k0)) continue;
-        if (!mbar_wait(qdo_empty, (it & 1u) ^ 1u, abort_flag, p.status, ST_TIMEOUT_EMPTY)) break;
-        ++it;
+        const int qb = it & 1;
         const int q0 = qt * FB_T;
-        mbar_expect_tx(qdo_full, 2 * FB_TILE);
-        tma_load_5d(smem + FbSmem::Q_OFF, &tmQ, qdo_full, 0, r, g, batch, q0);
-        tma_load_5d(smem + FbSmem::Q_OFF + FB_CHUNK, &tmQ, qdo_full, 64, r, g, batch, q0);
-        tma_load_4d(smem + FbSmem::DO_OFF, &tmDO, qdo_full, 0, head, batch, q0);
-        tma_load_4d(smem + FbSmem::DO_OFF + FB_CHUNK, &tmDO, qdo_full, 64, head, batch, q0);
+        if (!mbar_wait(&q_empty[qb], ((it >> 1) & 1u) ^ 1u, abort_flag, p.status, ST_TIMEOUT_EMPTY)) break;
+        uint8_t* qdst = smem + FbSmem::Q_OFF + qb * FB_TILE;
+        mbar_expect_tx(&q_full[qb], FB_TILE);
+        tma_load_5d(qdst, &tmQ, &q_full[qb], 0, r, g, batch, q0);
+        tma_load_5d(qdst + FB_CHUNK, &tmQ, &q_full[qb], 64, r, g, batch, q0);
+        if (!mbar_wait(do_empty, (it & 1u) ^ 1u, abort_flag, p.status, ST_TIMEOUT_EMPTY)) break;
+        mbar_expect_tx(do_full, FB_TILE);
+        tma_load_4d(smem + FbSmem::DO_OFF, &tmDO, do_full, 0, head, batch, q0);
+        tma_load_4d(smem + FbSmem::DO_OFF + FB_CHUNK, &tmDO, do_full, 64, head, batch, q0);
+        ++it;
       }
       if (*abort_flag) {
         const uint64_t t0 = globaltimer_ns();
@@ -141,23 +169,33 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     constexpr uint32_t id_mm = make_idesc_bf16(FB_T, FB_T, true, true);     // A MN-major, B MN-major
     constexpr uint32_t id_km = make_idesc_bf16(FB_T, FB_T, false, true);    // A K-major, B MN-major
     const uint32_t a_k = smem_u32(smem + FbSmem::K_OFF), a_v = smem_u32(smem + FbSmem::V_OFF);
-    const uint32_t a_q = smem_u32(smem + FbSmem::Q_OFF), a_do = smem_u32(smem + FbSmem::DO_OFF);
+    const uint32_t a_q0 = smem_u32(smem + FbSmem::Q_OFF), a_do = smem_u32(smem + FbSmem::DO_OFF);
     const uint32_t a_p = smem_u32(smem + FbSmem::P_OFF), a_ds = smem_u32(smem + FbSmem::DS_OFF);
     auto kmaj = [](uint32_t base, int k) { return make_smem_desc(base + (k >> 2) * FB_CHUNK + (k & 3) * 32, 16, 1024); };
     auto mnmaj = [](uint32_t base, int k) { return make_smem_desc(base + k * 2048, FB_CHUNK, 1024); };
     bool ok = n_it > 0;
     if (ok) ok = mbar_wait(kv_full, 0, abort_flag, p.status, ST_TIMEOUT_FULL);
+    if (ok) ok = mbar_wait(&q_full[0], 0, abort_flag, p.status, ST_TIMEOUT_FULL);
+    if (ok) {
+      tc_fence_after();
+      if (lane == 0) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) umma_ss(t_s, kmaj(a_q0, k), kmaj(a_k, k), id_kk, k > 0);
+        umma_commit(s_full);
+      }
+      __syncwarp();
+    }
     for (int it = 0; it < n_it && ok; ++it) {
       const uint32_t ph = it & 1u;
-      if (!mbar_wait(qdo_full, ph, abort_flag, p.status, ST_TIMEOUT_FULL)) { ok = false; break; }
+      const uint32_t a_q = a_q0 + (it & 1) * FB_TILE;
+      // dP(it) overwrites the columns that held dQ(it-1)
+      if (!mbar_wait(do_full, ph, abort_flag, p.status, ST_TIMEOUT_FULL)) { ok = false; break; }
       if (!mbar_wait(dq_empty, ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
       tc_fence_after();
       if (lane == 0) {
 #pragma unroll
-        for (int k = 0; k < 8; ++k) umma_ss(t_s, kmaj(a_q, k), kmaj(a_k, k), id_kk, k > 0);
-#pragma unroll
         for (int k = 0; k < 8; ++k) umma_ss(t_dp, kmaj(a_do, k), kmaj(a_v, k), id_kk, k > 0);
-        umma_commit(s_full);
+        umma_commit(dp_full);
       }
       __syncwarp();
       if (!mbar_wait(pds_full, ph, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
@@ -168,112 +206,156 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 #pragma unroll
         for (int k = 0; k < 8; ++k) umma_ss(t_dk, mnmaj(a_ds, k), mnmaj(a_q, k), id_mm, (it > 0 || k > 0));
 #pragma unroll
-        for (int k = 0; k < 8; ++k) umma_ss(t_s, kmaj(a_ds, k), mnmaj(a_k, k), id_km, k > 0);
-        umma_commit(qdo_empty);
+        for (int k = 0; k < 8; ++k) umma_ss(t_dq, kmaj(a_ds, k), mnmaj(a_k, k), id_km, k > 0);
+        umma_commit(&q_empty[it & 1]);
+        umma_commit(do_empty);
         umma_commit(dq_full);
       }
       __syncwarp();
+      if (it + 1 < n_it) {
+        // S of the next tile: its Q is already there, and S(it) has been read (pds_full above)
+        const int nb = (it + 1) & 1;
+        if (!mbar_wait(&q_full[nb], ((it + 1) >> 1) & 1u, abort_flag, p.status, ST_TIMEOUT_FULL)) { ok = false; break; }
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t a_qn = a_q0 + nb * FB_TILE;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) umma_ss(t_s, kmaj(a_qn, k), kmaj(a_k, k), id_kk, k > 0);
+          umma_commit(s_full);
+        }
+        __syncwarp();
+      }
     }
+    if (ok && lane == 0) umma_commit(all_done);
+    __syncwarp();
   } else {
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-    const float lg2e = 1.4426950408889634f;
+    const bool softmax_role = warp < 6;
     bool ok = n_it > 0;
     int it = -1;
-    for (int qt = 0; qt < n_q && ok; ++qt) {
-      if (!q_tile_sees(p, qt, k0)) continue;
-      ++it;
-      const uint32_t ph = it & 1u;
-      const int q0 = qt * FB_T;
-      const int q_off = p.geom.q_offset_of(q0, p.q_offset);
-      const int qrow = q0 + row;
-      const int qpos = q_off + qrow;
-      const bool valid = qrow < p.sq;
-      const size_t stat = (static_cast<size_t>(batch) * p.hq + head) * p.sq + (valid ? qrow : 0);
-      const float lse2 = valid ? p.lse[stat] * lg2e : 0.f;
-      const float dlt = valid ? p.delta[stat] : 0.f;
-      if (!mbar_wait(s_full, ph, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
-      tc_fence_after();
-      const bool tile_mask = (p.causal && k0 + FB_T - 1 > q_off + q0) || (k0 + FB_T > p.skv) || (q0 + FB_T > p.sq);
-      uint8_t* p_row = smem + FbSmem::P_OFF + row * 128;
-      uint8_t* ds_row = smem + FbSmem::DS_OFF + row * 128;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t sv[32], dv[32];
-        tmem_ld_32x32(t_s + lane_addr + c * 32, sv);
-        tmem_ld_32x32(t_dp + lane_addr + c * 32, dv);
-        tmem_ld_wait();
+    if (softmax_role) {
+      const float lg2e = 1.4426950408889634f;
+      for (int qt = 0; qt < n_q && ok; ++qt) {
+        if (!q_tile_sees(p, qt, k0)) continue;
+        ++it;
+        const uint32_t ph = it & 1u;
+        const int q0 = qt * FB_T;
+        const int q_off = p.geom.q_offset_of(q0, p.q_offset);
+        const int qrow = q0 + row;
+        const int qpos = q_off + qrow;
+        const bool valid = qrow < p.sq;
+        const size_t stat = (static_cast<size_t>(batch) * p.hq + head) * p.sq + (valid ? qrow : 0);
+        const float lse2 = valid ? p.lse[stat] * lg2e : 0.f;
+        const float dlt = valid ? p.delta[stat] : 0.f;
+        const bool tile_mask = (p.causal && k0 + FB_T - 1 > q_off + q0) || (k0 + FB_T > p.skv) || (q0 + FB_T > p.sq);
+        uint8_t* p_row = smem + FbSmem::P_OFF + row * 128;
+        uint8_t* ds_row = smem + FbSmem::DS_OFF + row * 128;
+        // S(it) ready: the products of tile it-1 were issued before it, so P and dS buffers are free
+        if (!mbar_wait(s_full, ph, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+        tc_fence_after();
+        uint32_t pk[64];                       // this row of P as packed bf16, kept for the dS pass
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          uint32_t wp[4], wd[4];
+        for (int c = 0; c < 4; ++c) {
+          uint32_t sv[32];
+          tmem_ld_32x32(t_s + lane_addr + c * 32, sv);
+          tmem_ld_wait();
 #pragma unroll
-          for (int h2 = 0; h2 < 4; ++h2) {
-            const int i = 8 * u + 2 * h2;
-            float e0 = bwd_exp2(__uint_as_float(sv[i]) * p.scale_log2 - lse2);
-            float e1 = bwd_exp2(__uint_as_float(sv[i + 1]) * p.scale_log2 - lse2);
-            if (tile_mask) {
-              const int key = k0 + c * 32 + i;
-              if (!valid || (p.causal && key > qpos) || key >= p.skv) e0 = 0.f;
-              if (!valid || (p.causal && key + 1 > qpos) || key + 1 >= p.skv) e1 = 0.f;
+          for (int u = 0; u < 4; ++u) {
+#pragma unroll
+            for (int h2 = 0; h2 < 4; ++h2) {
+              const int i = 8 * u + 2 * h2;
+              float e0 = bwd_exp2(__uint_as_float(sv[i]) * p.scale_log2 - lse2);
+              float e1 = bwd_exp2(__uint_as_float(sv[i + 1]) * p.scale_log2 - lse2);
+              if (tile_mask) {
+                const int key = k0 + c * 32 + i;
+                if (!valid || (p.causal && key > qpos) || key >= p.skv) e0 = 0.f;
+                if (!valid || (p.causal && key + 1 > qpos) || key + 1 >= p.skv) e1 = 0.f;
+              }
+              pk[c * 16 + u * 4 + h2] = pack_bf16x2(e0, e1);
             }
-            const float d0 = e0 * (__uint_as_float(dv[i]) - dlt) * p.scale;
-            const float d1 = e1 * (__uint_as_float(dv[i + 1]) - dlt) * p.scale;
-            wp[h2] = pack_bf16x2(e0, e1);
-            wd[h2] = pack_bf16x2(d0, d1);
+            const int unit = (c & 1) * 4 + u;
+            const int o = (c >> 1) * FB_CHUNK + ((unit ^ (row & 7)) << 4);
+            *reinterpret_cast<uint4*>(p_row + o) =
+                make_uint4(pk[c * 16 + u * 4], pk[c * 16 + u * 4 + 1], pk[c * 16 + u * 4 + 2], pk[c * 16 + u * 4 + 3]);
           }
-          const int unit = (c & 1) * 4 + u;
-          const int o = (c >> 1) * FB_CHUNK + ((unit ^ (row & 7)) << 4);
-          *reinterpret_cast<uint4*>(p_row + o) = make_uint4(wp[0], wp[1], wp[2], wp[3]);
-          *reinterpret_cast<uint4*>(ds_row + o) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
         }
-      }
-      tc_fence_before();
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(pds_full);
-      // dQ tile → fp32 vector reductions into the global accumulator
-      if (!mbar_wait(dq_full, ph, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
-      tc_fence_after();
-      float* dq_row = p.dq_acc + ((static_cast<size_t>(valid ? qrow : 0) * p.b + batch) * p.hq + head) * FB_T;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(t_s + lane_addr + c * 32, v);
-        tmem_ld_wait();
-        if (valid) {
+        if (!mbar_wait(dp_full, ph, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+        tc_fence_after();
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
-            red_add_v4(dq_row + c * 32 + 4 * j, __uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
-                       __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+        for (int c = 0; c < 4; ++c) {
+          uint32_t dv[32];
+          tmem_ld_32x32(t_dp + lane_addr + c * 32, dv);
+          tmem_ld_wait();
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            uint32_t wd[4];
+#pragma unroll
+            for (int h2 = 0; h2 < 4; ++h2) {
+              const int i = 8 * u + 2 * h2;
+              const float2 e = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pk[c * 16 + u * 4 + h2]));
+              const float d0 = e.x * (__uint_as_float(dv[i]) - dlt) * p.scale;
+              const float d1 = e.y * (__uint_as_float(dv[i + 1]) - dlt) * p.scale;
+              wd[h2] = pack_bf16x2(d0, d1);
+            }
+            const int unit = (c & 1) * 4 + u;
+            const int o = (c >> 1) * FB_CHUNK + ((unit ^ (row & 7)) << 4);
+            *reinterpret_cast<uint4*>(ds_row + o) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
+          }
         }
+        tc_fence_before();
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(pds_full);
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(dq_empty);
+    } else {
+      // dQ tile → fp32 vector reductions into the global accumulator
+      for (int qt = 0; qt < n_q && ok; ++qt) {
+        if (!q_tile_sees(p, qt, k0)) continue;
+        ++it;
+        const uint32_t ph = it & 1u;
+        const int qrow = qt * FB_T + row;
+        const bool valid = qrow < p.sq;
+        if (!mbar_wait(dq_full, ph, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+        tc_fence_after();
+        float* dq_row = p.dq_acc + ((static_cast<size_t>(valid ? qrow : 0) * p.b + batch) * p.hq + head) * FB_T;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(t_dq + lane_addr + c * 32, v);
+          tmem_ld_wait();
+          if (valid) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              red_add_v4(dq_row + c * 32 + 4 * j, __uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                         __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(dq_empty);
+      }
     }
-    // dV, dK of this key tile → fp32 accumulators (rows = keys)
+    // dV (warps 2..5) and dK (warps 6..9) of this key tile → fp32 accumulators (rows = keys)
     if (n_it > 0) {
-      // the last dq_full wait above already covered every MMA of the walk
+      if (ok) ok = mbar_wait(all_done, 0, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
       tc_fence_after();
       const int key = k0 + row;
       const bool kvalid = ok && key < p.skv;
       const size_t base = ((static_cast<size_t>(kvalid ? key : 0) * p.b + batch) * (p.hq / p.rep) + g) * FB_T;
+      float* dst = (softmax_role ? p.dv_acc : p.dk_acc) + base;
+      const uint32_t src = (softmax_role ? t_dv : t_dk) + lane_addr;
 #pragma unroll 1
-      for (int which = 0; which < 2; ++which) {
-        float* dst = (which == 0 ? p.dv_acc : p.dk_acc) + base;
-        const uint32_t src = (which == 0 ? t_dv : t_dk) + lane_addr;
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32(src + c * 32, v);
-          tmem_ld_wait();
-          if (kvalid) {
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(src + c * 32, v);
+        tmem_ld_wait();
+        if (kvalid) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
-              red_add_v4(dst + c * 32 + 4 * j, __uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
-                         __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
-          }
+          for (int j = 0; j < 8; ++j)
+            red_add_v4(dst + c * 32 + 4 * j, __uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                       __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
         }
       }
     }

@@ -5,10 +5,13 @@
 //   warp 1      MMA issuer (tcgen05, accumulators in TMEM):
 //                 S  = Q·Kᵀ          dP = dO·Vᵀ                       (per query tile)
 //                 dV += Pᵀ·dO        dK += dSᵀ·Q        dQ = dS·K      (per query tile)
-//   warps 2..5  one thread per query row: P = exp2(S·c − lse) as soon as S is there (dO of the tile may
-//               still be on its way), then dS = P∘(dP − δ)·scale once dP is there; both as bf16 into
-//               swizzled shared memory
-//   warps 6..9  dQ from TMEM → fp32 vector reductions in global, while the next tile is worked on
+//   warps 2..17 four threads per query row, 32 key columns each: P = exp2(S·c − lse) as soon as S is
+//               there (dO of the tile may still be on its way), then dS = P∘(dP − δ)·scale once dP is
+//               there; both as bf16 into swizzled shared memory.  Sixteen warps, four per scheduler: with
+//               one warp per scheduler this arithmetic, not the tensor pipe, set the pace of the walk
+//   warps 18..21 dQ from TMEM → shared memory (the dS buffer, free between the products of one tile and
+//               the dS pass of the next) → TMA reduce-add into the fp32 accumulator in global memory,
+//               32 columns at a time, while the next tile is worked on
 // The walk is a pipeline: S of tile i+1 is issued right behind the three products of tile i (its Q is
 // already in shared memory), the dO buffer is refilled as soon as those products retire, and dQ of
 // tile i is drained while P of tile i+1 is computed.
@@ -37,7 +40,8 @@ namespace kb {
 constexpr int FB_T = 128;                      // tile edge (queries, keys) and head dim
 constexpr int FB_TILE = FB_T * FB_T * 2;       // 32 KB bf16 tile as two 64-wide swizzled chunks
 constexpr int FB_CHUNK = 16384;
-constexpr int FB_THREADS = 320;
+constexpr int FB_SOFTMAX_WARPS = 16;             // 4 TMEM lane quarters x 4 chunks of 32 key columns
+constexpr int FB_THREADS = (2 + FB_SOFTMAX_WARPS + 4) * 32;
 
 struct BwdParams {
   const float* lse;      // [b, hq, sq]  natural log
@@ -74,9 +78,22 @@ __device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, 
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
+// Named barrier 1 of the four dQ warps; the second form returns whether `ok` held on all 128 threads.
+__device__ __forceinline__ void drain_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ bool drain_all(bool ok) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred P, Q;\n\tsetp.ne.u32 P, %1, 0;\n\tbar.red.and.pred Q, 1, 128, P;\n\tselp.u32 %0, 1, 0, Q;\n\t}"
+      : "=r"(r)
+      : "r"(static_cast<uint32_t>(ok))
+      : "memory");
+  return r != 0;
+}
+
 __global__ void __launch_bounds__(FB_THREADS, 1)
 flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ KvMaps kv,
-                      const __grid_constant__ CUtensorMap tmDO, const BwdParams p) {
+                      const __grid_constant__ CUtensorMap tmDO, const __grid_constant__ CUtensorMap tmDQ,
+                      const BwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FbSmem::BAR_OFF);
@@ -87,11 +104,12 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   uint64_t* do_empty = bars + 6;    // the MMAs that read dO (and P, dS) of this iteration have retired
   uint64_t* s_full = bars + 7;      // S is in TMEM
   uint64_t* dp_full = bars + 8;     // dP is in TMEM
-  uint64_t* pds_full = bars + 9;    // P and dS are in shared memory, S and dP have been read (4 warp arrivals)
+  uint64_t* pds_full = bars + 9;    // P and dS are in shared memory, S and dP have been read (one arrival per warp)
   uint64_t* dq_full = bars + 10;    // dQ (and this iteration's dV/dK updates) retired
-  uint64_t* dq_empty = bars + 11;   // dQ has been read out of TMEM (4 warp arrivals)
+  uint64_t* dq_empty = bars + 11;   // dQ has been read out of TMEM
   uint64_t* all_done = bars + 12;   // every MMA of the walk has retired
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  uint64_t* stage_free = bars + 13; // the dQ reductions have read their staging area (the dS buffer)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -113,10 +131,11 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     mbar_init(do_empty, 1);
     mbar_init(s_full, 1);
     mbar_init(dp_full, 1);
-    mbar_init(pds_full, 4);
+    mbar_init(pds_full, FB_SOFTMAX_WARPS);
     mbar_init(dq_full, 1);
-    mbar_init(dq_empty, 4);
+    mbar_init(dq_empty, 1);
     mbar_init(all_done, 1);
+    mbar_init(stage_free, 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -229,14 +248,20 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     if (ok && lane == 0) umma_commit(all_done);
     __syncwarp();
   } else {
-    const int quarter = warp & 3;
+    const int quarter = warp & 3;            // TMEM lanes this warp may read
     const int row = quarter * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-    const bool softmax_role = warp < 6;
+    const bool softmax_role = warp < 2 + FB_SOFTMAX_WARPS;
+    const int c = (warp - 2) >> 2;           // softmax warps: chunk of 32 key columns
     bool ok = n_it > 0;
     int it = -1;
     if (softmax_role) {
       const float lg2e = 1.4426950408889634f;
+      // 16-byte units of this thread inside its row of P / dS (two 64-wide swizzled chunks per row)
+      uint32_t unit_off[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        unit_off[u] = (c >> 1) * FB_CHUNK + row * 128 + ((((c & 1) * 4 + u) ^ (row & 7)) << 4);
       for (int qt = 0; qt < n_q && ok; ++qt) {
         if (!q_tile_sees(p, qt, k0)) continue;
         ++it;
@@ -250,14 +275,11 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         const float lse2 = valid ? p.lse[stat] * lg2e : 0.f;
         const float dlt = valid ? p.delta[stat] : 0.f;
         const bool tile_mask = (p.causal && k0 + FB_T - 1 > q_off + q0) || (k0 + FB_T > p.skv) || (q0 + FB_T > p.sq);
-        uint8_t* p_row = smem + FbSmem::P_OFF + row * 128;
-        uint8_t* ds_row = smem + FbSmem::DS_OFF + row * 128;
         // S(it) ready: the products of tile it-1 were issued before it, so P and dS buffers are free
         if (!mbar_wait(s_full, ph, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
         tc_fence_after();
-        uint32_t pk[64];                       // this row of P as packed bf16, kept for the dS pass
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        uint32_t pk[16];                       // this thread's 32 values of P as packed bf16, kept for dS
+        {
           uint32_t sv[32];
           tmem_ld_32x32(t_s + lane_addr + c * 32, sv);
           tmem_ld_wait();
@@ -273,18 +295,17 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 if (!valid || (p.causal && key > qpos) || key >= p.skv) e0 = 0.f;
                 if (!valid || (p.causal && key + 1 > qpos) || key + 1 >= p.skv) e1 = 0.f;
               }
-              pk[c * 16 + u * 4 + h2] = pack_bf16x2(e0, e1);
+              pk[u * 4 + h2] = pack_bf16x2(e0, e1);
             }
-            const int unit = (c & 1) * 4 + u;
-            const int o = (c >> 1) * FB_CHUNK + ((unit ^ (row & 7)) << 4);
-            *reinterpret_cast<uint4*>(p_row + o) =
-                make_uint4(pk[c * 16 + u * 4], pk[c * 16 + u * 4 + 1], pk[c * 16 + u * 4 + 2], pk[c * 16 + u * 4 + 3]);
+            *reinterpret_cast<uint4*>(smem + FbSmem::P_OFF + unit_off[u]) =
+                make_uint4(pk[u * 4], pk[u * 4 + 1], pk[u * 4 + 2], pk[u * 4 + 3]);
           }
         }
         if (!mbar_wait(dp_full, ph, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+        // the dS buffer doubled as staging area of the previous tile's dQ reductions
+        if (it > 0 && !mbar_wait(stage_free, (it - 1) & 1u, abort_flag, p.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
         tc_fence_after();
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        {
           uint32_t dv[32];
           tmem_ld_32x32(t_dp + lane_addr + c * 32, dv);
           tmem_ld_wait();
@@ -294,14 +315,12 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 #pragma unroll
             for (int h2 = 0; h2 < 4; ++h2) {
               const int i = 8 * u + 2 * h2;
-              const float2 e = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pk[c * 16 + u * 4 + h2]));
+              const float2 e = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pk[u * 4 + h2]));
               const float d0 = e.x * (__uint_as_float(dv[i]) - dlt) * p.scale;
               const float d1 = e.y * (__uint_as_float(dv[i + 1]) - dlt) * p.scale;
               wd[h2] = pack_bf16x2(d0, d1);
             }
-            const int unit = (c & 1) * 4 + u;
-            const int o = (c >> 1) * FB_CHUNK + ((unit ^ (row & 7)) << 4);
-            *reinterpret_cast<uint4*>(ds_row + o) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
+            *reinterpret_cast<uint4*>(smem + FbSmem::DS_OFF + unit_off[u]) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
           }
         }
         tc_fence_before();
@@ -310,51 +329,68 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         if (lane == 0) mbar_arrive(pds_full);
       }
     } else {
-      // dQ tile → fp32 vector reductions into the global accumulator
+      // dQ tile → fp32 reductions into the global accumulator, 32 columns (16 KB) at a time through the two
+      // halves of the dS buffer: 128-byte rows with their 16-byte units swizzled by row, as the tensor
+      // map of the accumulator expects
+      const bool leader = threadIdx.x == (2 + FB_SOFTMAX_WARPS) * 32;
+      uint8_t* stage = smem + FbSmem::DS_OFF;
       for (int qt = 0; qt < n_q && ok; ++qt) {
         if (!q_tile_sees(p, qt, k0)) continue;
         ++it;
         const uint32_t ph = it & 1u;
-        const int qrow = qt * FB_T + row;
-        const bool valid = qrow < p.sq;
-        if (!mbar_wait(dq_full, ph, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+        // one decision for the 128 threads (they meet at named barriers below); the leader comes here only
+        // after the previous tile's reductions have read the staging area
+        ok = drain_all(mbar_wait(dq_full, ph, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL));
+        if (!ok) break;
         tc_fence_after();
-        float* dq_row = p.dq_acc + ((static_cast<size_t>(valid ? qrow : 0) * p.b + batch) * p.hq + head) * FB_T;
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int cc = 0; cc < 4; ++cc) {
+          uint8_t* buf = stage + (cc & 1) * 16384;
+          if (cc >= 2) {
+            if (leader) tma_store_wait_read<1>();      // the reduction of chunk cc-2 has read this half
+            drain_sync();
+          }
           uint32_t v[32];
-          tmem_ld_32x32(t_dq + lane_addr + c * 32, v);
+          tmem_ld_32x32(t_dq + lane_addr + cc * 32, v);
           tmem_ld_wait();
-          if (valid) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
-              red_add_v4(dq_row + c * 32 + 4 * j, __uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
-                         __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<uint4*>(buf + row * 128 + ((j ^ (row & 7)) << 4)) =
+                make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          fence_proxy_async_smem();
+          if (cc == 3) tc_fence_before();
+          drain_sync();
+          if (leader) {
+            tma_reduce_add_4d(&tmDQ, buf, cc * 32, head, batch, qt * FB_T);   // rows past sq are clipped
+            tma_store_commit();
           }
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(dq_empty);
+        if (leader) {
+          mbar_arrive(dq_empty);                       // every thread's TMEM reads preceded the last barrier
+          tma_store_wait_read<0>();
+          mbar_arrive(stage_free);
+        }
       }
+      if (leader) tma_store_wait<0>();                 // nothing in flight out of shared memory at exit
     }
-    // dV (warps 2..5) and dK (warps 6..9) of this key tile → fp32 accumulators (rows = keys)
-    if (n_it > 0) {
+    // dV and dK of this key tile → fp32 accumulators (rows = keys); softmax warp (quarter, c) takes
+    // columns 32c..32c+31 of both
+    if (n_it > 0 && softmax_role) {
       if (ok) ok = mbar_wait(all_done, 0, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
       tc_fence_after();
       const int key = k0 + row;
       const bool kvalid = ok && key < p.skv;
       const size_t base = ((static_cast<size_t>(kvalid ? key : 0) * p.b + batch) * (p.hq / p.rep) + g) * FB_T;
-      float* dst = (softmax_role ? p.dv_acc : p.dk_acc) + base;
-      const uint32_t src = (softmax_role ? t_dv : t_dk) + lane_addr;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int which = 0; which < 2; ++which) {
+        float* dst = (which == 0 ? p.dv_acc : p.dk_acc) + base + c * 32;
         uint32_t v[32];
-        tmem_ld_32x32(src + c * 32, v);
+        tmem_ld_32x32((which == 0 ? t_dv : t_dk) + lane_addr + c * 32, v);
         tmem_ld_wait();
         if (kvalid) {
 #pragma unroll
           for (int j = 0; j < 8; ++j)
-            red_add_v4(dst + c * 32 + 4 * j, __uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+            red_add_v4(dst + 4 * j, __uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
                        __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
         }
       }
@@ -510,6 +546,15 @@ static int launch_bwd(const CUtensorMap& tmQ, const KvMaps& kv, const ChunkGeom&
     if (e != cudaSuccess) return 1000 + (int)e;
     configured = true;
   }
+  CUtensorMap tmDQ;
+  {
+    // fp32 accumulator [sq, b, hq, d]: boxes of 128 rows x 32 columns (128 bytes, swizzled) of one (b, head)
+    uint64_t dims[4] = {(uint64_t)d, (uint64_t)hq, (uint64_t)b, (uint64_t)sq};
+    uint64_t str[3] = {(uint64_t)d * 4, (uint64_t)hq * d * 4, (uint64_t)b * hq * d * 4};
+    uint32_t box[4] = {32, 1, 1, FB_T};
+    rc = make_tmap(&tmDQ, dq_acc, 4, 4, dims, str, box, 3);
+    if (rc) return rc;
+  }
   int n_kv = (skv + FB_T - 1) / FB_T;
   if (causal) {
     const int lim = (last_key + FB_T - 1) / FB_T;      // keys >= last_key are seen by no query
@@ -517,7 +562,7 @@ static int launch_bwd(const CUtensorMap& tmQ, const KvMaps& kv, const ChunkGeom&
   }
   if (n_kv > 0) {
     dim3 grid(n_kv, hq, b);
-    KB_LAUNCH(flash_attn_bwd_kernel, grid, FB_THREADS, FbSmem::TOTAL, stream, tmQ, kv, tmDO, p);
+    KB_LAUNCH(flash_attn_bwd_kernel, grid, FB_THREADS, FbSmem::TOTAL, stream, tmQ, kv, tmDO, tmDQ, p);
   }
   {
     long nvec = n_dq / 4;

@@ -4,8 +4,12 @@
 //   warp 0      TMA producer: Q once, then K and V tiles into a 2-stage ring (128B swizzle)
 //   warp 1      MMA issuer:   S = Q·Kᵀ (tcgen05, accumulator in TMEM, double buffered) and
 //                             O += P·V (P from shared memory, V as an MN-major operand)
-//   warps 2..5  softmax:      one thread per query row; S row from TMEM → scale, mask, running
-//                             max/sum in the log2 domain → P (bf16) into swizzled shared memory.
+//   warps 2..17 softmax:      four threads per query row, 32 key columns each (warp = TMEM lane quarter
+//                             x column chunk): S from TMEM once, kept in registers → scale, mask, row
+//                             maximum exchanged among the four threads through spare TMEM columns and a
+//                             128-thread named barrier → P (bf16) into swizzled shared memory, partial
+//                             row sums per thread.  Sixteen warps, four per scheduler: with one thread
+//                             per row and one warp per scheduler the exponentials set the pace.
 // The S of tile j+1 is issued before the softmax of tile j finishes, so tensor cores and the
 // exponent units overlap.  O stays in TMEM for the whole row tile; it is rescaled only when the
 // running maximum moves by more than 2^8 ("lazy rescale"), which happens on the first tiles only.
@@ -33,7 +37,8 @@ namespace kb {
 constexpr int FA_BM = 128;      // query rows per CTA
 constexpr int FA_BN = 128;      // keys per tile
 constexpr int FA_D = 128;       // head dim
-constexpr int FA_THREADS = 192;
+constexpr int FA_SOFTMAX_WARPS = 16;
+constexpr int FA_THREADS = (2 + FA_SOFTMAX_WARPS) * 32;
 constexpr int FA_TILE_BYTES = FA_BN * FA_D * 2;   // 32 KB: two 64-wide swizzled chunks of 16 KB
 constexpr int FA_CHUNK = 16384;
 
@@ -124,10 +129,10 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       mbar_init(&v_full[i], 1);
       mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], 4);
+      mbar_init(&s_empty[i], FA_SOFTMAX_WARPS);
     }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&p_full[i], 4);
+      mbar_init(&p_full[i], FA_SOFTMAX_WARPS);
       mbar_init(&pv_done[i], 1);
     }
     *abort_flag = 0;
@@ -140,6 +145,7 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_s = tmem_base;         // 2 x 128 columns
   const uint32_t tmem_o = tmem_base + 256;   // 128 columns
+  const uint32_t tmem_x = tmem_base + 384;   // 12 columns: row maxima (2 x 4) and row sums (4) of the column chunks
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
@@ -241,30 +247,30 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     }
   } else {
     // ------------------------------------------------------------------ softmax + epilogue
-    // Two passes over the S row straight out of tensor memory (max, then exp/sum/pack), 32 columns
-    // at a time with rolled outer loops: the code stays small enough for the instruction cache and
-    // needs few registers; packed f32x2 FMA/ADD halve the ALU work next to the exponentials.
     const int quarter = warp & 3;
+    const int c = (warp - 2) >> 2;                 // chunk of 32 key columns, and of 32 output columns
     const int row = quarter * 32 + lane;           // row inside the tile = TMEM lane
     const int qpos = q_off + q0 + row;             // absolute position of this query
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    const int group_bar = 1 + quarter;             // named barrier of the four warps that share these rows
+    const uint32_t full = 0xffffffffu;
     float m_ref = -INFINITY;   // reference maximum (scaled, log2 domain) used for the exponentials
-    float l_sum = 0.f;
+    float l_part = 0.f;        // sum of this thread's exponentials
     bool ok = n_kv > 0;
-    for (int j = 0; j < n_kv && ok; ++j) {
+    bool group_ok = true;      // false once the group has left the loop together after a failed wait
+    for (int j = 0; j < n_kv; ++j) {
       const int s = j & 1;
-      if (!mbar_wait(&s_full[s], (j >> 1) & 1u, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
-      tc_fence_after();
+      // a thread whose wait failed keeps coming to the group barrier (with good = false), so that the
+      // four warps leave together and nobody is left waiting at it
+      const bool good = __all_sync(full, ok && mbar_wait(&s_full[s], (j >> 1) & 1u, abort_flag, p.status,
+                                                         ST_TIMEOUT_TMEM_FULL));
       const int key0 = j * FA_BN;
       // warp-uniform: does any row of this tile need masking?
       const bool tile_mask = (p.causal && key0 + FA_BN - 1 > q_off + q0) || (key0 + FA_BN > p.skv);
-      const uint32_t s_addr = tmem_s + s * FA_BN + lane_addr;
-      // ---- pass 1: row maximum of the raw scores
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(s_addr + c * 32, v);
+      uint32_t v[32];
+      if (good) {
+        tc_fence_after();
+        tmem_ld_32x32(tmem_s + s * FA_BN + lane_addr + c * 32, v);
         tmem_ld_wait();
         if (tile_mask) {
 #pragma unroll
@@ -273,6 +279,7 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             if ((p.causal && key > qpos) || key >= p.skv) v[i] = 0xff800000u;   // -inf
           }
         }
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
         for (int i = 0; i < 32; i += 8) {
           mx4[0] = fmax3(mx4[0], __uint_as_float(v[i + 0]), __uint_as_float(v[i + 1]));
@@ -280,8 +287,23 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           mx4[2] = fmax3(mx4[2], __uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
           mx4[3] = fmax3(mx4[3], __uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
         }
+        const float mloc = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        // slot j & 1: a thread can be one barrier ahead of the slowest reader of its group, never two
+        tmem_st_32x32_x1(tmem_x + lane_addr + (j & 1) * 4 + c, __float_as_uint(mloc));
+        tmem_st_wait();
+        tc_fence_before();
       }
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
+      if (!bar128_all(group_bar, good)) { ok = false; group_ok = false; break; }
+      tc_fence_after();
+      uint32_t m4[4];
+      tmem_ld_32x32_x4(tmem_x + lane_addr + (j & 1) * 4, m4);
+      tmem_ld_wait();
+      // S has been read: its buffer may take the scores of tile j+2
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[s]);
+      const float mx = fmaxf(fmaxf(__uint_as_float(m4[0]), __uint_as_float(m4[1])),
+                             fmaxf(__uint_as_float(m4[2]), __uint_as_float(m4[3]))) * p.scale_log2;
       float rescale = 1.f;
       bool do_rescale = false;
       if (mx > m_ref + 8.f) {       // also true on the first tile (m_ref = -inf)
@@ -293,110 +315,101 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       }
       const float mref = (m_ref == -INFINITY) ? 0.f : m_ref;
       // O may only be touched once the previous P·V has retired (rare path: the running maximum
-      // moved by more than 2^8); the decision is made warp-uniform for the .aligned TMEM accesses
-      if (__any_sync(0xffffffffu, do_rescale)) {
-        if (!mbar_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1u, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) {
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+      // moved by more than 2^8); the decision is made warp-uniform for the .aligned TMEM accesses.
+      // This thread rescales its 32 columns of O.
+      if (__any_sync(full, do_rescale)) {
+        const bool got = __all_sync(full, mbar_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1u, abort_flag, p.status,
+                                                    ST_TIMEOUT_TMEM_FULL));
+        if (got) {
+          tc_fence_after();
           uint32_t o[32];
           tmem_ld_32x32(tmem_o + lane_addr + c * 32, o);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * rescale);
           tmem_st_32x32(tmem_o + lane_addr + c * 32, o);
+          tmem_st_wait();
+        } else {
+          ok = false;
         }
-        tmem_st_wait();
       }
       // the P buffer of this parity was last read by the P·V of tile j-2
-      if (j >= 2) {
-        if (!mbar_wait(&pv_done[s], ((j >> 1) & 1u) ^ 1u, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) {
+      if (ok && j >= 2) {
+        if (!__all_sync(full, mbar_wait(&pv_done[s], ((j >> 1) & 1u) ^ 1u, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)))
           ok = false;
-          break;
-        }
       }
-      // ---- pass 2: P = exp2(S·scale − m), row sum, bf16 pack into the swizzled operand layout
+      if (!ok) continue;            // the group learns of it at its next barrier
+      // ---- P = exp2(S·scale − m), partial row sum, bf16 pack into the swizzled operand layout
       // (16-byte unit u of row r goes to unit (u ^ (r & 7)) of that row inside its 64-key chunk)
-      uint8_t* p_row = smem + FaSmem::P_OFF + s * FA_TILE_BYTES + row * 128;
+      uint8_t* p_row = smem + FaSmem::P_OFF + s * FA_TILE_BYTES + (c >> 1) * FA_CHUNK + row * 128;
       const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
       const float2 nm2 = make_float2(-mref, -mref);
       float2 ps2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(s_addr + c * 32, v);
-        tmem_ld_wait();
-        if (tile_mask) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int key = key0 + c * 32 + i;
-            if ((p.causal && key > qpos) || key >= p.skv) v[i] = 0xff800000u;
-          }
+      for (int u = 0; u < 4; ++u) {
+        uint32_t w[4];
+#pragma unroll
+        for (int h2 = 0; h2 < 4; ++h2) {
+          const int i = 8 * u + 2 * h2;
+          float2 x = __ffma2_rn(make_float2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])), sc2, nm2);
+          x.x = fast_exp2(x.x);
+          x.y = fast_exp2(x.y);
+          ps2[h2 & 1] = __fadd2_rn(ps2[h2 & 1], x);
+          w[h2] = pack_bf16x2(x.x, x.y);
         }
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          uint32_t w[4];
-#pragma unroll
-          for (int h2 = 0; h2 < 4; ++h2) {
-            const int i = 8 * u + 2 * h2;
-            float2 x = __ffma2_rn(make_float2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])), sc2, nm2);
-            x.x = fast_exp2(x.x);
-            x.y = fast_exp2(x.y);
-            ps2[h2 & 1] = __fadd2_rn(ps2[h2 & 1], x);
-            w[h2] = pack_bf16x2(x.x, x.y);
-          }
-          const int unit = (c & 1) * 4 + u;              // 16-byte unit inside the 64-key chunk
-          uint8_t* dst = p_row + (c >> 1) * FA_CHUNK + ((unit ^ (row & 7)) << 4);
-          *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
-        }
+        const int unit = (c & 1) * 4 + u;              // 16-byte unit inside the 64-key chunk
+        *reinterpret_cast<uint4*>(p_row + ((unit ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
       }
-      l_sum = l_sum * rescale + (ps2[0].x + ps2[0].y) + (ps2[1].x + ps2[1].y);
+      l_part = l_part * rescale + (ps2[0].x + ps2[0].y) + (ps2[1].x + ps2[1].y);
       tc_fence_before();
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&s_empty[s]);
-        mbar_arrive(&p_full[s]);
-      }
+      if (lane == 0) mbar_arrive(&p_full[s]);
     }
-    // ---- epilogue: O / l → global, LSE
-    if (ok && n_kv > 0)
-      ok = mbar_wait(&pv_done[(n_kv - 1) & 1], ((n_kv - 1) >> 1) & 1u, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL);
+    // ---- epilogue: O / l → global, LSE; this thread writes its 32 columns of the row
+    const int qrow = q0 + row;
     if (n_kv > 0) {
-      tc_fence_after();
-      const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
-      const int qrow = q0 + row;
-      __nv_bfloat16* orow = p.out + ((static_cast<size_t>(qrow) * p.b + batch) * p.hq + head) * FA_D;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t o[32];
-        tmem_ld_32x32(tmem_o + lane_addr + c * 32, o);
-        tmem_ld_wait();
-        if (ok && qrow < p.sq) {
+      if (group_ok) {
+        const bool good = __all_sync(full, ok && mbar_wait(&pv_done[(n_kv - 1) & 1], ((n_kv - 1) >> 1) & 1u, abort_flag,
+                                                           p.status, ST_TIMEOUT_TMEM_FULL));
+        if (good) {
+          tmem_st_32x32_x1(tmem_x + lane_addr + 8 + c, __float_as_uint(l_part));
+          tmem_st_wait();
+          tc_fence_before();
+        }
+        if (bar128_all(group_bar, good)) {
+          tc_fence_after();
+          uint32_t l4[4];
+          tmem_ld_32x32_x4(tmem_x + lane_addr + 8, l4);
+          uint32_t o[32];
+          tmem_ld_32x32(tmem_o + lane_addr + c * 32, o);
+          tmem_ld_wait();
+          const float l_sum = (__uint_as_float(l4[0]) + __uint_as_float(l4[1])) +
+                              (__uint_as_float(l4[2]) + __uint_as_float(l4[3]));
+          const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
+          if (qrow < p.sq) {
+            __nv_bfloat16* orow = p.out + ((static_cast<size_t>(qrow) * p.b + batch) * p.hq + head) * FA_D + c * 32;
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            uint4 w;
-            w.x = pack_bf16x2(__uint_as_float(o[8 * u + 0]) * inv, __uint_as_float(o[8 * u + 1]) * inv);
-            w.y = pack_bf16x2(__uint_as_float(o[8 * u + 2]) * inv, __uint_as_float(o[8 * u + 3]) * inv);
-            w.z = pack_bf16x2(__uint_as_float(o[8 * u + 4]) * inv, __uint_as_float(o[8 * u + 5]) * inv);
-            w.w = pack_bf16x2(__uint_as_float(o[8 * u + 6]) * inv, __uint_as_float(o[8 * u + 7]) * inv);
-            reinterpret_cast<uint4*>(orow + c * 32)[u] = w;
+            for (int u = 0; u < 4; ++u) {
+              uint4 w;
+              w.x = pack_bf16x2(__uint_as_float(o[8 * u + 0]) * inv, __uint_as_float(o[8 * u + 1]) * inv);
+              w.y = pack_bf16x2(__uint_as_float(o[8 * u + 2]) * inv, __uint_as_float(o[8 * u + 3]) * inv);
+              w.z = pack_bf16x2(__uint_as_float(o[8 * u + 4]) * inv, __uint_as_float(o[8 * u + 5]) * inv);
+              w.w = pack_bf16x2(__uint_as_float(o[8 * u + 6]) * inv, __uint_as_float(o[8 * u + 7]) * inv);
+              reinterpret_cast<uint4*>(orow)[u] = w;
+            }
+            if (c == 0)
+              p.lse[(static_cast<size_t>(batch) * p.hq + head) * p.sq + qrow] =
+                  (l_sum > 0.f) ? (m_ref + log2f(l_sum)) * 0.6931471805599453f : -INFINITY;
           }
         }
       }
-      if (ok && qrow < p.sq)
-        p.lse[(static_cast<size_t>(batch) * p.hq + head) * p.sq + qrow] =
-            (l_sum > 0.f) ? (m_ref + log2f(l_sum)) * 0.6931471805599453f : -INFINITY;
     } else {
       // no visible key at all (only possible with a negative q_offset): zero output
-      const int qrow = q0 + row;
       if (qrow < p.sq) {
-        __nv_bfloat16* orow = p.out + ((static_cast<size_t>(qrow) * p.b + batch) * p.hq + head) * FA_D;
-        for (int i = 0; i < FA_D / 8; ++i) reinterpret_cast<uint4*>(orow)[i] = make_uint4(0, 0, 0, 0);
-        p.lse[(static_cast<size_t>(batch) * p.hq + head) * p.sq + qrow] = -INFINITY;
+        __nv_bfloat16* orow = p.out + ((static_cast<size_t>(qrow) * p.b + batch) * p.hq + head) * FA_D + c * 32;
+        for (int i = 0; i < 4; ++i) reinterpret_cast<uint4*>(orow)[i] = make_uint4(0, 0, 0, 0);
+        if (c == 0) p.lse[(static_cast<size_t>(batch) * p.hq + head) * p.sq + qrow] = -INFINITY;
       }
     }
   }

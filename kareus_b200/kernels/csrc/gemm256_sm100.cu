@@ -16,12 +16,13 @@ constexpr int G2_BM = 256;
 constexpr int G2_BN = 256;
 constexpr int G2_BK = 64;
 constexpr int G2_STAGES = 3;
-constexpr int G2_THREADS = 192;
+constexpr int G2_EPI_WARPS = 8;                 // 4 TMEM lane quarters x the 2 accumulators
+constexpr int G2_THREADS = (2 + G2_EPI_WARPS) * 32;
 constexpr int G2_A_BYTES = G2_BM * G2_BK * 2;   // 32 KB
 constexpr int G2_B_BYTES = G2_BN * G2_BK * 2;   // 32 KB
 constexpr int G2_STAGE_BYTES = G2_A_BYTES + G2_B_BYTES;
 constexpr int G2_TILE_BYTES = G2_STAGE_BYTES * G2_STAGES;
-constexpr int G2_SMEM = G2_TILE_BYTES + 256 + 4 * 4096 + 1024;   // + per-warp epilogue staging
+constexpr int G2_SMEM = G2_TILE_BYTES + 256 + G2_EPI_WARPS * 4096 + 1024;   // + per-warp epilogue staging
 
 __device__ __forceinline__ void g2_tile_coords(int t, int tiles_m, int tiles_n, int group_m, int& tm, int& tn) {
   const int per_group = group_m * tiles_n;
@@ -59,7 +60,7 @@ gemm256_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       mbar_init(&empty[i], 1);
     }
     mbar_init(tfull, 1);
-    mbar_init(tempty, 4);
+    mbar_init(tempty, G2_EPI_WARPS);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -152,15 +153,18 @@ gemm256_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const int m0 = tm * G2_BM, n0 = tn * G2_BN;
       if (!mbar_wait(tfull, tile_i & 1u, abort_flag, status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
-#pragma unroll 1
-      for (int h = 0; h < 2; ++h) {
+      // warps 2..5 read the accumulator of rows 0..127, warps 6..9 that of rows 128..255: two warps per
+      // scheduler, so one warp's TMEM loads and conversions hide behind the other's stores
+      {
+        const int h = (warp - 2) >> 2;
         const int row = m0 + h * 128 + q * 32 + lane;
         const uint32_t taddr = tmem_base + h * G2_BN + (static_cast<uint32_t>(q * 32) << 16);
+        bool stored = false;
         if constexpr (!OUT_F32) {
           // bf16 rows go through 4 KB of shared memory per warp so that stores are full 128-byte row
           // segments (see gemm_sm100.cu)
           if ((ldc & 7) == 0 && (N & 7) == 0) {
-            uint8_t* stg = smem + G2_TILE_BYTES + 256 + q * 4096;
+            uint8_t* stg = smem + G2_TILE_BYTES + 256 + (warp - 2) * 4096;
             __nv_bfloat16* cbase = reinterpret_cast<__nv_bfloat16*>(Cout) + static_cast<size_t>(m0 + h * 128 + q * 32) * ldc;
 #pragma unroll 1
             for (int cp = 0; cp < G2_BN / 64; ++cp) {
@@ -192,11 +196,11 @@ gemm256_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               }
               __syncwarp();
             }
-            continue;
+            stored = true;
           }
         }
 #pragma unroll 1
-        for (int c = 0; c < G2_BN / 32; ++c) {
+        for (int c = 0; c < (stored ? 0 : G2_BN / 32); ++c) {
           uint32_t v[32];
           tmem_ld_32x32(taddr + c * 32, v);
           tmem_ld_wait();

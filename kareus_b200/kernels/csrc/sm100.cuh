@@ -138,6 +138,13 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void*
                ::"l"(map), "r"(smem_u32(src)), "r"(x), "r"(y)
                : "memory");
 }
+// Tile of fp32 in shared memory added to the tile of global memory at the given coordinates (the L2
+// performs the additions); completion is tracked like a TMA store (commit / wait groups).
+__device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* map, const void* src, int x, int y, int z, int w) {
+  asm volatile("cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+               ::"l"(map), "r"(smem_u32(src)), "r"(x), "r"(y), "r"(z), "r"(w)
+               : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void tma_store_wait_read() {
@@ -187,6 +194,26 @@ __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r
         "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
         "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
+}
+// One 32-bit column / four columns of this warp's 32 lanes (lane i of the quarter ↔ thread i).
+__device__ __forceinline__ void tmem_st_32x32_x1(uint32_t taddr, uint32_t v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32x32_x4(uint32_t taddr, uint32_t (&r)[4]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(taddr)
+               : "memory");
+}
+// Named barrier `id` over 128 threads that also tells every thread whether `ok` held on all of them.
+__device__ __forceinline__ bool bar128_all(int id, bool ok) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred P, Q;\n\tsetp.ne.u32 P, %2, 0;\n\tbar.red.and.pred Q, %1, 128, P;\n\tselp.u32 %0, 1, 0, Q;\n\t}"
+      : "=r"(r)
+      : "r"(id), "r"(static_cast<uint32_t>(ok))
+      : "memory");
+  return r != 0;
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }

@@ -122,15 +122,16 @@ class _FusedBase:
 
     # ---- kernels ------------------------------------------------------------------------------
     @staticmethod
-    def auto_drivers(sm_num: int, n_out: int) -> int:
+    def auto_drivers(sm_num: int, n_out: int, budget: int = 0) -> int:
         """Copy-driver CTAs when no plan names them.  Every driver keeps a fixed number of bytes in flight, so
         the pull rate grows with their number; a kernel with little math (narrow N) can give up GEMM CTAs for
         drivers until its GEMM takes as long as the gather: three times the base count up to N = 768, twice
-        up to N = 1280."""
+        up to N = 1280, never more than a third of the SMs the kernel may use (``budget``, 0: the whole GPU)."""
+        cap = max(sm_num, (budget or 148) // 3)
         if n_out <= 768:
-            return min(3 * sm_num, 48)
+            return min(3 * sm_num, cap)
         if n_out <= 1280:
-            return min(2 * sm_num, 48)
+            return min(2 * sm_num, cap)
         return sm_num
 
     def _ag_gemm(self, x2, w, n_out, b_mn: bool, sm_num, nb: int, planned: bool = True):
@@ -138,8 +139,8 @@ class _FusedBase:
         where ``xg`` is the gathered input inside the heap (valid until this site's next call)."""
         heap = self.heap
         sm_num = int(sm_num or self.default_sm)
-        if not planned:
-            sm_num = self.auto_drivers(sm_num, n_out)
+        if not planned and os.environ.get("KAREUS_AG_AUTO", "1") != "0":
+            sm_num = self.auto_drivers(sm_num, n_out, _fused_sms())
         world, rank = heap.world, heap.rank
         ms, k = x2.shape
         m = ms * world

@@ -12,8 +12,9 @@
 //   waits for a tile's flag only if the tile is remote.  No tile crosses NVLink more than once, no
 //   TMA multicast is used, and the gathered activations stay in the buffer for the wgrad GEMM.
 // * gemm_rs — the GEMM CTAs visit row tiles in owner order (rank+1 first, own rows last).  For a
-//   peer's rows the epilogue stores the bf16 partial tile straight into the owner's staging slot
-//   through its peer pointer (full 128-byte row segments) and bumps a per-tile counter there.  For
+//   peer's rows the epilogue sends the bf16 partial tile straight into the owner's staging slot (TMA
+//   stores out of a double-buffered shared-memory staging area through per-peer tensor maps; with
+//   KAREUS_RS_TMA=0 plain 128-byte row-segment stores) and bumps a per-tile counter there.  For
 //   its own rows the epilogue waits for the other ranks' counters of that tile, adds their staged
 //   partials in fp32 and writes the finished sequence shard: no separate reduction pass exists.
 //   One extra CTA runs the start barrier (peers must have entered the call before their staging is

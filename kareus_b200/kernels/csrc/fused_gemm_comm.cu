@@ -79,6 +79,10 @@ struct FusedParams {
   uint8_t* mc;
   uint64_t ready_off;     // AG: uint32 per 128-row tile, bumped on every rank by the tile's sender
   int push_tma;           // RS over peer memory: partial tiles leave through TMA stores (maps in StageMaps)
+  // AG: gathered buffer [M, K] in ordinary local memory (null: inside the heap at xg_off).  xg_off then names
+  // the [Ms, K] buffer that holds each rank's own shard in its heap; the caller has also put this rank's
+  // shard into its rows of xg_local.
+  uint8_t* xg_local;
 };
 
 // RS: one tensor map per peer over this rank's slot [rows_per_rank, N] of that peer's staging area.  The
@@ -128,8 +132,9 @@ __device__ void ag_copy_role(const FusedParams& p, int K, uint8_t* smem, uint64_
     for (int rt = cta; rt < remote_tiles && ok; rt += p.n_first) {
       const int src = (c.rank + 1 + rt / tiles_per_rank) % c.world;
       const int tile = src * tiles_per_rank + rt % tiles_per_rank;     // tile index in the gathered buffer
-      const uint8_t* from = c.base[src] + p.xg_off + tile * tile_bytes;
-      uint8_t* to = c.base[c.rank] + p.xg_off + tile * tile_bytes;
+      const uint8_t* from = p.xg_local ? c.base[src] + p.xg_off + (rt % tiles_per_rank) * tile_bytes
+                                       : c.base[src] + p.xg_off + tile * tile_bytes;
+      uint8_t* to = (p.xg_local ? p.xg_local : c.base[c.rank] + p.xg_off) + tile * tile_bytes;
       const int nchunks = static_cast<int>((tile_bytes + FG_CHUNK - 1) / FG_CHUNK);
       int loaded = 0, stored = 0;
       while (stored < nchunks && ok) {
@@ -650,8 +655,10 @@ using namespace kb;
 // ready: local uint32[M/128] flags (persist across calls, epoch-valued).  n_comm copy-driver CTAs.
 static int ag_gemm_impl(void* const* bases, int rank, int world, uint64_t flag_off, uint64_t xg_off, const void* W,
                        void* Y, int M, int N, int K, int ldw, int b_mn, uint32_t* ready, uint32_t epoch, int n_comm,
-                       int num_sms, int* status, cudaStream_t stream, uint8_t* uc, uint8_t* mc, uint64_t ready_off) {
+                       int num_sms, int* status, cudaStream_t stream, uint8_t* uc, uint8_t* mc, uint64_t ready_off,
+                       void* xg_local = nullptr) {
   if (world < 2 || world > MAX_PEERS || M % (world * FG_BM) || (K & 7) || (xg_off & 1023)) return ST_BAD_ARG;
+  if (xg_local && (mc || (reinterpret_cast<uintptr_t>(xg_local) & 15))) return ST_BAD_ARG;
   if (num_sms <= 0) num_sms = device_sm_count();
   if (n_comm < 1) n_comm = 1;
   if (n_comm > MAX_SIGNAL_CTAS) n_comm = MAX_SIGNAL_CTAS;
@@ -667,7 +674,8 @@ static int ag_gemm_impl(void* const* bases, int rank, int world, uint64_t flag_o
   p.ready = mc ? reinterpret_cast<uint32_t*>(uc + ready_off) : ready;
   p.out = reinterpret_cast<__nv_bfloat16*>(Y);
   p.uc = uc; p.mc = mc; p.ready_off = ready_off;
-  const void* A = mc ? uc + xg_off : reinterpret_cast<const uint8_t*>(bases[rank]) + xg_off;
+  p.xg_local = reinterpret_cast<uint8_t*>(xg_local);
+  const void* A = xg_local ? xg_local : mc ? uc + xg_off : reinterpret_cast<const uint8_t*>(bases[rank]) + xg_off;
   const bool narrow = (N <= 128) || (N % 256 != 0 && N % 256 <= 128);
   const int bn = narrow ? 128 : 256;
   const int tiles = (M / FG_BM) * ((N + bn - 1) / bn);
@@ -683,6 +691,19 @@ extern "C" int kb_ag_gemm_bf16(void* const* bases, int rank, int world, uint64_t
                                uint32_t epoch, int n_comm, int num_sms, int* status, cudaStream_t stream) {
   return ag_gemm_impl(bases, rank, world, flag_off, xg_off, W, Y, M, N, K, ldw, b_mn, ready, epoch, n_comm, num_sms,
                       status, stream, nullptr, nullptr, 0);
+}
+
+// Same, with the gathered buffer in ordinary local memory (`xg_local`, [M, K], this rank's rows already filled
+// in): every rank's own shard sits in a [M/world, K] buffer at heap offset shard_off, the copy drivers pull the
+// peers' shards from there into xg_local.  The caller may keep xg_local (the weight-gradient GEMM of the
+// backward pass reads it) without copying it out of the heap.
+extern "C" int kb_ag_gemm_local_bf16(void* const* bases, int rank, int world, uint64_t flag_off, uint64_t shard_off,
+                                     void* xg_local, const void* W, void* Y, int M, int N, int K, int ldw, int b_mn,
+                                     uint32_t* ready, uint32_t epoch, int n_comm, int num_sms, int* status,
+                                     cudaStream_t stream) {
+  if (!xg_local) return ST_BAD_ARG;
+  return ag_gemm_impl(bases, rank, world, flag_off, shard_off, W, Y, M, N, K, ldw, b_mn, ready, epoch, n_comm, num_sms,
+                      status, stream, nullptr, nullptr, 0, xg_local);
 }
 
 // Switch-multicast variant: the gathered buffer (xg_off) and the per-tile ready flags (ready_off, uint32 per

@@ -36,11 +36,12 @@ def _lib():
     if not _DECLARED:
         P, I, U32, U64 = c_void_p, c_int, c_uint32, c_uint64
         L.kb_ag_gemm_bf16.argtypes = [P, I, I, U64, U64, P, P, I, I, I, I, I, P, U32, I, I, P, P]
+        L.kb_ag_gemm_local_bf16.argtypes = [P, I, I, U64, U64, P, P, P, I, I, I, I, I, P, U32, I, I, P, P]
         L.kb_gemm_rs_bf16.argtypes = [P, I, I, U64, U64, U64, P, I, P, I, I, P, I, I, I, P, U32, I, I, P, P]
         L.kb_fused_tiles_n.argtypes = [I]
         L.kb_ag_gemm_mc_bf16.argtypes = [P, I, I, U64, P, P, U64, U64, P, P, I, I, I, I, I, U32, I, I, P, P]
         L.kb_gemm_rs_mc_bf16.argtypes = [P, I, I, U64, P, P, U64, U64, P, I, P, I, I, P, I, I, I, P, U32, I, I, P, P]
-        for n in ("kb_ag_gemm_bf16", "kb_gemm_rs_bf16", "kb_fused_tiles_n", "kb_ag_gemm_mc_bf16", "kb_gemm_rs_mc_bf16"):
+        for n in ("kb_ag_gemm_bf16", "kb_ag_gemm_local_bf16", "kb_gemm_rs_bf16", "kb_fused_tiles_n", "kb_ag_gemm_mc_bf16", "kb_gemm_rs_mc_bf16"):
             getattr(L, n).restype = c_int
         _DECLARED = True
     return L
@@ -134,10 +135,13 @@ class _FusedBase:
             return min(2 * sm_num, cap)
         return sm_num
 
-    def _ag_gemm(self, x2, w, n_out, b_mn: bool, sm_num, nb: int, planned: bool = True):
-        """Gather ``x2`` ([Ms, K] shard) over the group and multiply: returns ``(y [M, n_out], xg [M, K])``
-        where ``xg`` is the gathered input inside the heap (valid until this site's next call)."""
+    def _ag_gemm(self, x2, w, n_out, b_mn: bool, sm_num, nb: int, planned: bool = True, keep: bool = False):
+        """Gather ``x2`` ([Ms, K] shard) over the group and multiply: returns ``(y [M, n_out], xg [M, K])``.
+        ``xg`` is the gathered input inside the heap (valid until this site's next call), or with ``keep`` a
+        tensor of its own that the caller may hold on to: the copy drivers then write the peers' shards
+        straight into it, and only this rank's shard goes through the heap."""
         heap = self.heap
+        self._xg_owned = False          # set by the branch that returns a tensor of its own
         sm_num = int(sm_num or self.default_sm)
         if not planned and os.environ.get("KAREUS_AG_AUTO", "1") != "0":
             sm_num = self.auto_drivers(sm_num, n_out, _fused_sms())
@@ -164,6 +168,24 @@ class _FusedBase:
                                            _fused_sms(), st.data_ptr(), KC._stream())
             KC._check(rc, f"ag_gemm (multicast) {self.name}")
             KC._count()
+            return y, xg
+        if keep and os.environ.get("KAREUS_AG_KEEP", "1") != "0":
+            off, _ = heap.buffer(ch, "xs", ms * k * 2)
+            x2c = x2 if x2.is_contiguous() else x2.contiguous()
+            xg = torch.empty(m, k, dtype=torch.bfloat16, device=x2.device)
+            _replay.copy_(heap.view(off, (ms, k), torch.bfloat16), x2c)      # what the peers pull
+            _replay.copy_(xg[rank * ms:(rank + 1) * ms], x2c)
+            ready = self._local_flags(("ready", nb), m // 128)
+            ch.bump()
+            y = torch.empty(m, n_out, dtype=torch.bfloat16, device=x2.device)
+            st = KC.status_word(x2.device)
+            rc = _lib().kb_ag_gemm_local_bf16(heap._bases_arr, rank, world, ch.flag_off, off, xg.data_ptr(),
+                                              w.data_ptr(), y.data_ptr(), m, n_out, k, w.stride(0), 1 if b_mn else 0,
+                                              ready.data_ptr(), ch.epoch, int(sm_num or self.default_sm),
+                                              _fused_sms(), st.data_ptr(), KC._stream())
+            KC._check(rc, f"ag_gemm {self.name}")
+            KC._count()
+            self._xg_owned = True
             return y, xg
         off, _ = heap.buffer(ch, "xg", m * k * 2)
         xg = heap.view(off, (m, k), torch.bfloat16)
@@ -232,9 +254,12 @@ class FusedAGGemm(_FusedBase):
         (x,) = tensors
         lin = self.linear
         lead = x.shape[:-1]
-        y, xg = self._ag_gemm(x.reshape(-1, x.shape[-1]), lin.weight, lin.out_features, False, sm_num, nb, planned)
-        if ctx is not None and ctx.requires_grad:
-            ctx.save_for_backward(_replay.clone(xg))  # gathered input for the wgrad GEMM
+        keep = ctx is not None and ctx.requires_grad       # the wgrad GEMM of the backward pass reads xg
+        y, xg = self._ag_gemm(x.reshape(-1, x.shape[-1]), lin.weight, lin.out_features, False, sm_num, nb, planned,
+                              keep=keep)
+        if keep:
+            # a buffer of the call site (heap or NVLS buffer) is overwritten by the next layer: copy it out
+            ctx.save_for_backward(xg if self._xg_owned else _replay.clone(xg))
         return (y.reshape((lead[0] * self.heap.world,) + tuple(lead[1:]) + (lin.out_features,)),)
 
 

@@ -55,13 +55,17 @@ def test_fused_gemm_collectives(heap, rank, world, dev, prefix=""):
         dist.all_gather_into_tensor(xs, x)
         want = xs.float().reshape(-1, k) @ w.float().t()
         op = FusedAGGemm(lin, heap, 8)
-        for rep in range(3):
+        for rep in range(4):
+            # with a backward pass to come the gathered input lands in a tensor of its own (kept for the
+            # weight gradient); without, in the call site's heap buffer
             ctx = OpContext()
+            ctx.requires_grad = rep != 1
             (y,) = op.run((x,), sm_num=sm, nb=0, ctx=ctx)
             torch.cuda.synchronize()
             KC.check_status()
             assert rel(y.reshape(-1, n), want) < 1e-2, ("ag_gemm", ms, k, n, rep, rel(y.reshape(-1, n), want))
-            assert torch.equal(ctx.saved_tensors[0], xs.reshape(-1, k))
+            if ctx.requires_grad:
+                assert torch.equal(ctx.saved_tensors[0], xs.reshape(-1, k))
         a = torch.randn(ms * world, 1, k, device=dev, generator=g).bfloat16()
         part = (a.float().reshape(-1, k) @ w.float().t())
         full = part.clone()

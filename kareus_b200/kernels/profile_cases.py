@@ -116,6 +116,62 @@ def wgrad_sweep() -> None:
     KC.check_status()
 
 
+def memory_table() -> None:
+    """Every memory-bound kernel of a training step at the Llama-3.2-3B shapes: CUDA-event time, algorithmic
+    bytes (each operand read or written once) and the fraction of the measured copy bandwidth."""
+    import json
+    from pathlib import Path
+    from . import cuda as KC, ref
+    dev = "cuda"
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    peaks = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    hbm = json.loads(peaks.read_text())["hbm_gbs"] if peaks.exists() else 6650.0
+    rows_, H, F, V = 32768, 3072, 8192, 128256
+    x = torch.randn(rows_, H, device=dev).bfloat16()
+    w = torch.ones(H, device=dev).bfloat16()
+    y, rstd = KC.rmsnorm_fwd(x, w, 1e-5)
+    dw = torch.zeros(H, device=dev)
+    gu = torch.randn(rows_, 2 * F, device=dev).bfloat16()
+    act = KC.swiglu_fwd(gu)
+    qkv = torch.randn(4096, 8, 8, 5, 128, device=dev).bfloat16()
+    fr = ref.rope_table(4096, 128, 500000.0, device=dev)
+    logits = torch.randn(8192, V, device=dev).bfloat16()
+    tgt = torch.randint(0, V, (8192,), device=dev)
+    m, s_, t_ = KC.cross_entropy_local_stats(logits, tgt, 0)
+    ones = torch.ones_like(m)
+    n = 128 * 1024 * 1024
+    g32, m32, v32, w32 = (torch.randn(n, device=dev) for _ in range(4))
+    p16 = w32.bfloat16()
+    emb = torch.randn(V, H, device=dev).bfloat16()
+    tok = torch.randint(0, V, (4096, 8), device=dev)
+    demb = torch.randn(4096, 8, H, device=dev).bfloat16()
+    gemb = torch.zeros(V, H, device=dev)
+    b2 = 2
+    cases = [
+        ("rmsnorm fwd", lambda: KC.rmsnorm_fwd(x, w, 1e-5), 2 * x.numel() * b2),
+        ("rmsnorm bwd (+dw into the main gradient)", lambda: KC.rmsnorm_bwd(y, x, rstd, w, dw_accum=dw), 3 * x.numel() * b2),
+        ("swiglu fwd", lambda: KC.swiglu_fwd(gu), (gu.numel() + act.numel()) * b2),
+        ("swiglu bwd", lambda: KC.swiglu_bwd(act, gu), (act.numel() + 2 * gu.numel()) * b2),
+        ("rope on q and k, in place", lambda: KC.rope_inplace(qkv[..., :3, :], qkv[..., 3, :], fr), 2 * qkv[..., :4, :].numel() * b2),
+        ("dropout-add fwd (p = 0.1)", lambda: KC.dropout_add_fwd(x, y, 0.1, 7), 3 * x.numel() * b2),
+        ("dropout bwd", lambda: KC.dropout_add_bwd(x, 0.1, 7), 2 * x.numel() * b2),
+        ("residual add", lambda: KC.add(x, y), 3 * x.numel() * b2),
+        ("cross entropy: max / sum / target logit", lambda: KC.cross_entropy_local_stats(logits, tgt, 0), logits.numel() * b2),
+        ("cross entropy: gradient in place", lambda: KC.cross_entropy_finish(logits, tgt, 0, m, s_, ones), 2 * logits.numel() * b2),
+        ("AdamW (fp32 master, moments; bf16 weights out)", lambda: KC.adamw_step(p16, g32, m32, v32, w32, 1e-4, 0.9, 0.98, 1e-8, 0.01, 3),
+         n * (4 * 4 + 3 * 4 + 2)),
+        ("sum of squares (gradient norm)", lambda: KC.sumsq(g32), n * 4),
+        ("embedding gather", lambda: KC.embedding_fwd(tok, emb, 0), 2 * tok.numel() * H * b2),
+        ("embedding scatter-add (fp32 gradient)", lambda: KC.embedding_bwd(demb, tok, gemb, 0), tok.numel() * H * (b2 + 8)),
+    ]
+    print(f"| kernel | us | algorithmic MB | GB/s | of measured copy ({hbm:.0f} GB/s) |\n|---|---|---|---|---|")
+    for name, fn, nbytes in cases:
+        t = _timed(fn, flush)
+        gbs = nbytes / t / 1e6
+        print(f"| {name} | {t * 1e3:.0f} | {nbytes / 1e6:.0f} | {gbs:.0f} | {gbs / hbm:.2f} |")
+    KC.check_status()
+
+
 def attn_table() -> None:
     """Causal GQA flash attention at the 3B shapes (per nanobatch of 4 sequences): TP 1 (24/8 heads) and
     TP 8 (3/1 heads), forward and backward, vs the flash-attention wheel when it is installed."""
@@ -312,6 +368,8 @@ def main(case: str, reps: int = 3) -> None:
     dev = "cuda"
     if case == "collectives":
         return collectives_table()
+    if case == "memory_table":
+        return memory_table()
     if case == "wgrad_sweep":
         return wgrad_sweep()
     if case == "gemm_table":

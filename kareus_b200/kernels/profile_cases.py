@@ -363,7 +363,14 @@ def collectives_table() -> None:
     dist.destroy_process_group()
 
 
+# every command of this module: tables (CUDA events) and single-kernel cases (for a profiler capture)
+CASES = ("collectives", "memory_table", "wgrad_sweep", "gemm_table", "attn_table", "fused", "gemm", "gemm_wgrad",
+         "attn_fwd", "attn_bwd", "norm", "swiglu", "rope", "ce", "adamw", "step")
+
+
 def main(case: str, reps: int = 3) -> None:
+    if case not in CASES:
+        raise SystemExit(f"unknown case {case!r}; one of: {', '.join(CASES)}")
     from . import cuda as KC
     dev = "cuda"
     if case == "collectives":

@@ -121,3 +121,19 @@ model:
     rc = pretrain.main(["--config", str(tmp_path / "c.yaml"), "--out", str(tmp_path / "exp"), "model.hidden_dropout=0.0"])
     assert rc == 0 and "step 1 loss" in capsys.readouterr().out
     assert (tmp_path / "exp" / "tiny_yaml" / "cp1_tp1_mbs2_seq32" / "nanobatch" / "timers" / "instructions-0-0.csv").exists()
+
+
+def test_bench_reference_arm_says_why_it_is_unavailable():
+    """`bench.py --impl reference` prints one JSON line with the reason and exits 0 (the reference's training
+    stack cannot be installed offline); it must not start the package's own engine."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parents[1]
+    r = subprocess.run([sys.executable, str(root / "bench.py"), "--impl", "reference", "--gpus", "1", "--steps", "2",
+                        "--warmup", "3"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    line = json.loads(r.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and isinstance(line["unavailable"], str) and line["unavailable"]
+    assert "value" not in line

@@ -19,6 +19,7 @@ def main(argv=None) -> int:
     ap.add_argument("--out", default="nemo_experiments")
     ap.add_argument("--method", default=None)
     ap.add_argument("--clock-mode", default="advisory", choices=["off", "advisory", "locked"])
+    ap.add_argument("--eod-token", type=int, default=None, help="end-of-document id (for model.data.eod_mask_loss)")
     ap.add_argument("overrides", nargs="*")
     a = ap.parse_args(argv)
     import yaml
@@ -55,6 +56,14 @@ def main(argv=None) -> int:
                   "--profile-ranks", *map(str, sw.nsys_ranks)]
     if sw.enable_megatron_timers:
         argv2.append("--enable-timers")
+    if sw.data_prefix:
+        from pathlib import Path
+        if Path(sw.data_prefix + ".idx").exists():
+            argv2 += ["--data-path", sw.data_prefix, "--data-split", sw.data_split, "--data-seed", str(train.seed)]
+            if sw.eod_mask_loss and a.eod_token is not None:
+                argv2 += ["--eod-token", str(a.eod_token)]
+        else:
+            print(f"model.data.data_prefix {sw.data_prefix}.idx not found: training on synthetic tokens", flush=True)
     return run_train.main(argv2)
 
 

@@ -44,6 +44,11 @@ def main(argv=None) -> int:
                     help="open the CUDA profiler capture range at this step (nsys --capture-range=cudaProfilerApi)")
     ap.add_argument("--profile-end-step", type=int, default=None)
     ap.add_argument("--profile-ranks", type=int, nargs="*", default=[0])
+    ap.add_argument("--data-path", default=None,
+                    help="prefix of a Megatron-format indexed token file (<prefix>.bin/.idx); default: synthetic tokens")
+    ap.add_argument("--data-split", default="949,50,1", help="train,validation,test weights over the documents")
+    ap.add_argument("--data-seed", type=int, default=1234)
+    ap.add_argument("--eod-token", type=int, default=None, help="mask the loss on this end-of-document token")
     ap.add_argument("--save", default=None, help="write a distributed checkpoint (model + optimizer) here at the end")
     ap.add_argument("--save-interval", type=int, default=0, help="also save every N steps")
     ap.add_argument("--load", default=None, help="resume from this distributed checkpoint (any TP x PP x DP layout)")
@@ -117,9 +122,24 @@ def main(argv=None) -> int:
         first = trainer.step_index
         if rank == 0:
             print(f"resumed from {a.load} at step {first}", flush=True)
+    batches = None
+    if a.data_path:
+        from ..data import GPTDataset, GPTDatasetConfig, IndexedDataset, PretrainingBatches, split_documents
+        tokens = IndexedDataset(a.data_path)
+        train_docs = split_documents(tokens.num_documents, [float(w) for w in a.data_split.split(",")])[0]
+        ds = GPTDataset(tokens, GPTDatasetConfig(seq_len=a.seq, num_samples=a.steps * a.gbs, seed=a.data_seed,
+                                                 documents=train_docs, eod_token=a.eod_token,
+                                                 vocab_size=cfg.vocab_size))
+        # the run resumes at the sample where the checkpointed step count left off
+        batches = PretrainingBatches(ds, a.mbs, M, dp_rank=mesh.dp_rank, dp_size=dp, consumed_samples=first * a.gbs,
+                                     cp=a.cp, cp_rank=mesh.cp_rank)
+        if rank == 0:
+            print(f"data: {a.data_path}: {tokens.num_documents} documents, {tokens.num_tokens} tokens, "
+                  f"{ds.num_epochs} epoch(s) for {a.steps} steps", flush=True)
     try:
         for step in range(first, a.steps):
-            batch = synthetic_batch(cfg, tc, M, seed=step, cp=a.cp, cp_rank=mesh.cp_rank)
+            batch = next(batches) if batches is not None else \
+                synthetic_batch(cfg, tc, M, seed=step, cp=a.cp, cp_rank=mesh.cp_rank)
             loss = trainer.train_step(batch, loss_denominator=float(a.gbs * a.seq))
             if rank == 0:
                 print(f"step {step} loss {loss:.4f}", flush=True)
@@ -128,6 +148,8 @@ def main(argv=None) -> int:
         if a.save:
             trainer.save_checkpoint(a.save)
     finally:
+        if batches is not None:
+            batches.close()
         ctl.close()
         if power is not None:
             power.stop()

@@ -33,6 +33,10 @@ class RunSwitches:
     nsys_start_step: int = 10
     nsys_end_step: int = 10
     nsys_ranks: Tuple[int, ...] = (0,)
+    # model.data.{data_prefix,splits_string,eod_mask_loss}: the (first) indexed token file of the blend
+    data_prefix: Optional[str] = None
+    data_split: str = "900,50,50"
+    eod_mask_loss: bool = False
 
 
 def _set_path(d: dict, dotted: str, value) -> None:
@@ -111,4 +115,16 @@ def load_run_config(path, overrides: Iterable[str] = (), world_size: Optional[in
         sw.nsys_start_step = int(ns.get("start_step", 10))
         sw.nsys_end_step = int(ns.get("end_step", 10))
         sw.nsys_ranks = tuple(int(r) for r in (ns.get("ranks") or [0]))
+    data = m.get("data") or {}
+    prefix = data.get("data_prefix")
+    if isinstance(prefix, (list, tuple)):
+        # a blend is written [weight, prefix, weight, prefix, ...]; this runtime reads its first file
+        paths = [p for p in prefix if isinstance(p, str)]
+        prefix = paths[0] if paths else None
+    if isinstance(prefix, dict):
+        train_part = prefix.get("train")
+        prefix = next((p for p in (train_part or []) if isinstance(p, str)), None)
+    sw.data_prefix = str(prefix) if prefix else None
+    sw.data_split = str(data.get("splits_string", sw.data_split))
+    sw.eod_mask_loss = bool(data.get("eod_mask_loss", False))
     return model, par, train, sw

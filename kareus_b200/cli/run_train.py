@@ -49,6 +49,10 @@ def main(argv=None) -> int:
     ap.add_argument("--data-split", default="949,50,1", help="train,validation,test weights over the documents")
     ap.add_argument("--data-seed", type=int, default=1234)
     ap.add_argument("--eod-token", type=int, default=None, help="mask the loss on this end-of-document token")
+    ap.add_argument("--eval-interval", type=int, default=0,
+                    help="every N steps report the loss on held-out batches (validation documents of --data-path, "
+                         "or synthetic tokens of other seeds); 0: never")
+    ap.add_argument("--eval-iters", type=int, default=1, help="global batches per evaluation")
     ap.add_argument("--save", default=None, help="write a distributed checkpoint (model + optimizer) here at the end")
     ap.add_argument("--save-interval", type=int, default=0, help="also save every N steps")
     ap.add_argument("--load", default=None, help="resume from this distributed checkpoint (any TP x PP x DP layout)")
@@ -136,6 +140,31 @@ def main(argv=None) -> int:
         if rank == 0:
             print(f"data: {a.data_path}: {tokens.num_documents} documents, {tokens.num_tokens} tokens, "
                   f"{ds.num_epochs} epoch(s) for {a.steps} steps", flush=True)
+    val_ds = None
+    if a.data_path and a.eval_interval > 0:
+        val_docs = split_documents(tokens.num_documents, [float(w) for w in a.data_split.split(",")])[1]
+        if val_docs[1] > val_docs[0]:
+            # the same held-out batches at every evaluation, in file order
+            val_ds = GPTDataset(tokens, GPTDatasetConfig(seq_len=a.seq, num_samples=a.eval_iters * a.gbs, seed=a.data_seed,
+                                                         documents=val_docs, eod_token=a.eod_token,
+                                                         vocab_size=cfg.vocab_size, shuffle_samples=False))
+        elif rank == 0:
+            print("the validation share of --data-split is empty: evaluating on synthetic tokens", flush=True)
+
+    def evaluate(step: int) -> None:
+        losses = []
+        if val_ds is not None:
+            with PretrainingBatches(val_ds, a.mbs, M, dp_rank=mesh.dp_rank, dp_size=dp, cp=a.cp,
+                                    cp_rank=mesh.cp_rank) as vb:
+                for vbatch in vb:
+                    losses.append(trainer.evaluate(vbatch))
+        else:
+            for k in range(a.eval_iters):
+                losses.append(trainer.evaluate(synthetic_batch(cfg, tc, M, seed=1_000_000 + k, cp=a.cp,
+                                                               cp_rank=mesh.cp_rank)))
+        if rank == 0 and losses:
+            print(f"step {step} validation loss {sum(losses) / len(losses):.4f} ({len(losses)} batches)", flush=True)
+
     try:
         for step in range(first, a.steps):
             batch = next(batches) if batches is not None else \
@@ -143,6 +172,8 @@ def main(argv=None) -> int:
             loss = trainer.train_step(batch, loss_denominator=float(a.gbs * a.seq))
             if rank == 0:
                 print(f"step {step} loss {loss:.4f}", flush=True)
+            if a.eval_interval > 0 and (step + 1) % a.eval_interval == 0:
+                evaluate(step)
             if a.save and a.save_interval and (step + 1) % a.save_interval == 0 and step + 1 < a.steps:
                 trainer.save_checkpoint(a.save)
         if a.save:

@@ -148,6 +148,25 @@ class PipelineSchedule:
         for h in self.hooks:
             h.on_instruction_end(name)
 
+    def run_forward_only(self, num_microbatches: int) -> List[torch.Tensor]:
+        """Evaluation: every microbatch goes forward through the stages, nothing comes back.  Returns the
+        per-microbatch losses on the last stage (empty elsewhere).  The caller disables autograd."""
+        mesh, p2p = self.mesh, self.p2p
+        first, last = mesh.is_first_stage, mesh.is_last_stage
+        losses: List[torch.Tensor] = []
+        for mb in range(num_microbatches):
+            inputs = None if first else list(p2p.exchange(recv_from=p2p.prev).wait())
+            self._begin("forward")
+            out = self.forward_fn(mb, inputs)
+            self._end("forward")
+            if last:
+                losses.append(out.detach())
+            else:
+                p2p.exchange(send=list(out), send_to=p2p.next)
+        if p2p is not None:
+            p2p.finish_sends()
+        return losses
+
     def run(self, num_microbatches: int) -> List[torch.Tensor]:
         mesh, p2p = self.mesh, self.p2p
         first, last = mesh.is_first_stage, mesh.is_last_stage

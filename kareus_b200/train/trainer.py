@@ -88,8 +88,10 @@ class Trainer:
         return {k: v.to(self.device, non_blocking=True) for k, v in batch.items()}
 
     # ------------------------------------------------------------------ step
-    def forward_backward(self, batch: Dict[str, torch.Tensor], loss_denominator: float) -> torch.Tensor:
-        """All microbatches of one step; returns the summed loss (device scalar; 0 off the last stage)."""
+    def forward_backward(self, batch: Dict[str, torch.Tensor], loss_denominator: float,
+                         forward_only: bool = False) -> torch.Tensor:
+        """All microbatches of one step; returns the summed loss (device scalar; 0 off the last stage).
+        ``forward_only``: no backward pass (evaluation; the caller disables autograd)."""
         mesh, M = self.mesh, self.num_microbatches
         mbs = self.cfg.micro_batch_size
         tokens, labels, mask = batch["tokens"], batch["labels"], batch["loss_mask"]
@@ -107,8 +109,8 @@ class Trainer:
         if mesh.pp > 1 and self.p2p is None:
             dt = next(self.model.parameters()).dtype
             self.p2p = P2P(mesh, self._msg_shapes(mbs, tokens.shape[1]), dt, self.device)
-        sched = PipelineSchedule(mesh, self.p2p, forward_fn, hooks=self._hooks)
-        losses = sched.run(M)
+        sched = PipelineSchedule(mesh, self.p2p, forward_fn, hooks=() if forward_only else self._hooks)
+        losses = sched.run_forward_only(M) if forward_only else sched.run(M)
         if losses:
             return torch.stack(losses).sum()
         return torch.zeros((), device=self.device)
@@ -140,6 +142,21 @@ class Trainer:
             self.monitor.end_window(STEP_WINDOW)
         self.step_index += 1
         return out
+
+    @torch.no_grad()
+    def evaluate(self, batch: Dict[str, torch.Tensor], loss_denominator: Optional[float] = None) -> float:
+        """Mean loss of one global batch without touching gradients, optimizer state or the step count (the
+        reference's validation pass: ``trainer.val_check_interval`` / ``limit_val_batches`` of its run
+        configs).  Same batch layout and the same value on every rank as ``train_step``."""
+        if loss_denominator is None:
+            loss_denominator = float(batch["loss_mask"].sum()) * self.par.dp * self.par.cp
+        was_training = self.model.training
+        self.model.eval()
+        try:
+            loss = self.forward_backward(self.to_device(batch), loss_denominator, forward_only=True)
+        finally:
+            self.model.train(was_training)
+        return self.reduce_loss(loss)
 
     # ------------------------------------------------------------------ checkpoint
     def save_checkpoint(self, ckpt_dir, common: Optional[dict] = None) -> None:

@@ -219,3 +219,19 @@ model:
     (tmp_path / "d.yaml").write_text(yaml_text.format(prefix=str(tmp_path / "missing")))
     assert pretrain.main(["--config", str(tmp_path / "d.yaml"), "--out", str(tmp_path / "exp2")]) == 0
     assert "training on synthetic tokens" in capsys.readouterr().out
+
+
+def test_validation_loss_on_held_out_documents(tmp_path, capsys):
+    from kareus_b200.cli import run_train
+    prefix, _ = _corpus(tmp_path, n_docs=400, vocab=120)
+    rc = run_train.main(["--model", "tiny", "--mbs", "2", "--gbs", "4", "--seq", "32", "--method", "nanobatch",
+                         "--data-path", prefix, "--data-split", "8,2,0", "--steps", "4", "--eval-interval", "2",
+                         "--eval-iters", "2", "--out", str(tmp_path / "runs"), "--keep-process-group"])
+    assert rc == 0
+    out = capsys.readouterr().out
+    assert out.count("validation loss") == 2 and "(2 batches)" in out
+    # without a token file the held-out batches are synthetic
+    rc = run_train.main(["--model", "tiny", "--mbs", "2", "--gbs", "4", "--seq", "32", "--method", "megatron",
+                         "--steps", "2", "--eval-interval", "1", "--out", str(tmp_path / "runs2"),
+                         "--keep-process-group"])
+    assert rc == 0 and capsys.readouterr().out.count("validation loss") == 2

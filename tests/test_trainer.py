@@ -70,3 +70,41 @@ def test_tied_embedding_across_pipeline_stages_matches_single():
     copies and the copy counted once in the gradient norm."""
     want = _run_steps(1, 1, 1, tie=True)
     run_distributed(_tied_worker, 2, want)
+
+
+def _eval_then_train(tp, pp, dp):
+    """(evaluation loss, loss of the training step on the same batch, evaluation loss after the step)."""
+    from kareus_b200.config import ParallelConfig, TrainConfig, get_model_config
+    from kareus_b200.parallel.mesh import Mesh
+    from kareus_b200.train.trainer import Trainer, synthetic_batch
+    cfg = get_model_config("tiny")
+    par = ParallelConfig(tp=tp, pp=pp, dp=dp, num_nanobatches=2, recompute=True)
+    tc = TrainConfig(micro_batch_size=2, global_batch_size=8, seq_len=32, lr=2e-3, warmup_steps=0, max_steps=10,
+                     dtype="fp64")
+    mesh = Mesh(tp=tp, pp=pp, dp=dp)
+    tr = Trainer(cfg, par, tc, mesh=mesh, dtype="fp64")
+    full = synthetic_batch(cfg, tc, tc.num_microbatches(1), seed=100, pin=False)
+    share = tr.num_microbatches * tc.micro_batch_size
+    batch = {k: v[mesh.dp_rank * share:(mesh.dp_rank + 1) * share] for k, v in full.items()}
+    den = float(full["loss_mask"].sum())
+    before = [p.detach().clone() for p in tr.model.parameters()]
+    e0 = tr.evaluate(batch, loss_denominator=den)
+    assert all(torch.equal(a, b) for a, b in zip(before, tr.model.parameters())) and tr.step_index == 0
+    t0 = tr.train_step(batch, loss_denominator=den)
+    e1 = tr.evaluate(batch, loss_denominator=den)
+    return e0, t0, e1
+
+
+def _eval_worker(rank, world, tp, pp, dp, want):
+    got = _eval_then_train(tp, pp, dp)
+    for a, b in zip(got, want):
+        assert abs(a - b) < 1e-8, (got, want)
+
+
+@pytest.mark.parametrize("tp,pp,dp", [(1, 2, 1), (1, 1, 2)])
+def test_evaluation_pass(tp, pp, dp):
+    """Forward-only evaluation gives the loss a training step reports for the same weights, changes nothing,
+    and works through pipeline stages and data-parallel ranks."""
+    want = _eval_then_train(1, 1, 1)
+    assert abs(want[0] - want[1]) < 1e-10 and want[2] < want[0]
+    run_distributed(_eval_worker, tp * pp * dp, tp, pp, dp, want)

@@ -7,12 +7,16 @@
 Methods: ``megatron`` (one nanobatch, no plan), ``nanobatch`` (two nanobatches, fixed schedule),
 ``perseus`` / ``nanobatch_perseus`` (frequency plan only), ``kareus`` (frequency + overlap plan).
 Each rank writes ``<out>/<model>/<cp.._tp.._mbs.._seq..>/<method>/zeus_monitor_global_rank-G_local_rank-L.txt``
-with the windows ``training_step`` and ``training_step_fwd_bwd_step_call``.
+with the windows ``training_step`` and ``training_step_fwd_bwd_step_call``; rank 0 also appends one JSON object per
+step (loss, learning rate, gradient norm, step time, tokens/s, consumed samples, validation loss) to
+``metrics_global_rank-0.jsonl`` there.
 """
 from __future__ import annotations
 
 import argparse
+import json
 import os
+import time
 from pathlib import Path
 
 import torch
@@ -65,6 +69,7 @@ def main(argv=None) -> int:
     from ..energy import EnergyMonitor, FrequencyController, PipelineFrequencyOptimizer, PointSolution, PowerMonitor
     from ..parallel.mesh import Mesh, init_distributed
     from ..plan import PipelineCommScheduler, parse_schedule_file
+    from ..train.optimizer import cosine_lr
     from ..train.trainer import Trainer, synthetic_batch
     from ..utils.timers import Timers
 
@@ -151,6 +156,14 @@ def main(argv=None) -> int:
         elif rank == 0:
             print("the validation share of --data-split is empty: evaluating on synthetic tokens", flush=True)
 
+    metrics_file = open(out / f"metrics_global_rank-{rank}.jsonl", "a") if rank == 0 else None
+
+    def log_metrics(**kv) -> None:
+        """One JSON object per line: per-step training metrics and evaluation results of this run."""
+        if metrics_file is not None:
+            metrics_file.write(json.dumps(kv) + "\n")
+            metrics_file.flush()
+
     def evaluate(step: int) -> None:
         losses = []
         if val_ds is not None:
@@ -164,14 +177,21 @@ def main(argv=None) -> int:
                                                                cp_rank=mesh.cp_rank)))
         if rank == 0 and losses:
             print(f"step {step} validation loss {sum(losses) / len(losses):.4f} ({len(losses)} batches)", flush=True)
+            log_metrics(step=step, validation_loss=sum(losses) / len(losses), validation_batches=len(losses))
 
     try:
         for step in range(first, a.steps):
             batch = next(batches) if batches is not None else \
                 synthetic_batch(cfg, tc, M, seed=step, cp=a.cp, cp_rank=mesh.cp_rank)
-            loss = trainer.train_step(batch, loss_denominator=float(a.gbs * a.seq))
+            t0 = time.perf_counter()
+            loss = trainer.train_step(batch, loss_denominator=float(a.gbs * a.seq))     # reads the loss: synchronises
+            dt = time.perf_counter() - t0
             if rank == 0:
                 print(f"step {step} loss {loss:.4f}", flush=True)
+                norm = trainer.optimizer.last_grad_norm
+                log_metrics(step=step, loss=loss, lr=cosine_lr(step, tc),
+                            grad_norm=float(norm) if norm is not None else None, step_time_s=dt,
+                            tokens_per_s=a.gbs * a.seq / dt, consumed_samples=(step + 1) * a.gbs)
             if a.eval_interval > 0 and (step + 1) % a.eval_interval == 0:
                 evaluate(step)
             if a.save and a.save_interval and (step + 1) % a.save_interval == 0 and step + 1 < a.steps:
@@ -179,6 +199,8 @@ def main(argv=None) -> int:
         if a.save:
             trainer.save_checkpoint(a.save)
     finally:
+        if metrics_file is not None:
+            metrics_file.close()
         if batches is not None:
             batches.close()
         ctl.close()

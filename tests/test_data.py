@@ -235,3 +235,17 @@ def test_validation_loss_on_held_out_documents(tmp_path, capsys):
                          "--steps", "2", "--eval-interval", "1", "--out", str(tmp_path / "runs2"),
                          "--keep-process-group"])
     assert rc == 0 and capsys.readouterr().out.count("validation loss") == 2
+
+
+def test_metrics_log(tmp_path):
+    from kareus_b200.cli import run_train
+    rc = run_train.main(["--model", "tiny", "--mbs", "2", "--gbs", "4", "--seq", "32", "--method", "nanobatch",
+                         "--steps", "3", "--eval-interval", "3", "--out", str(tmp_path / "runs"),
+                         "--keep-process-group"])
+    assert rc == 0
+    f = tmp_path / "runs" / "tiny" / "cp1_tp1_mbs2_seq32" / "nanobatch" / "metrics_global_rank-0.jsonl"
+    rows = [json.loads(l) for l in f.read_text().splitlines()]
+    steps = [r for r in rows if "loss" in r]
+    assert [r["step"] for r in steps] == [0, 1, 2] and steps[-1]["consumed_samples"] == 12
+    assert all(r["grad_norm"] > 0 and r["lr"] > 0 and r["tokens_per_s"] > 0 for r in steps)
+    assert [r for r in rows if "validation_loss" in r][0]["step"] == 2

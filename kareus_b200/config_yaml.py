@@ -73,10 +73,13 @@ def load_run_config(path, overrides: Iterable[str] = (), world_size: Optional[in
     opt = m.get("optim", {}) or {}
     sched = opt.get("sched", {}) or {}
     heads = int(m["num_attention_heads"])
+    # the reference's run configs carry no vocabulary size: it follows from the tokenizer they name
+    tok_type = str((m.get("tokenizer") or {}).get("type", "")).lower()
+    default_vocab = 151936 if "qwen" in tok_type else 128256
     model = ModelConfig(
         name=str(raw.get("name", "model")), hidden_size=int(m["hidden_size"]), num_attention_heads=heads,
         num_query_groups=int(m.get("num_query_groups") or heads), ffn_hidden_size=int(m["ffn_hidden_size"]),
-        num_layers=int(m["num_layers"]), vocab_size=int(m.get("vocab_size", 128256)),
+        num_layers=int(m["num_layers"]), vocab_size=int(m.get("vocab_size") or default_vocab),
         head_dim=int(m["kv_channels"]) if m.get("kv_channels") else None,
         rope_theta=float(m.get("rotary_base", 500000.0)), norm_eps=float(m.get("layernorm_epsilon", 1e-5)),
         hidden_dropout=float(m.get("hidden_dropout", 0.0)), qk_layernorm=bool(m.get("qk_layernorm", False)),

@@ -201,3 +201,21 @@ def test_resume_under_another_layout_continues_the_same_run(tmp_path):
     assert "optimizer.state.exp_avg.decoder.layers.mlp.linear_fc2.weight" in md
     assert "optimizer.state.fp32_param.embedding.word_embeddings.weight" in md
     run_distributed(_load_worker, 4, path)
+
+
+def test_reference_run_configs_load():
+    """The YAML files the reference ships (set KAREUS_REFERENCE_DIR) load as they are: model shape, layout,
+    data section; the vocabulary follows the tokenizer they name."""
+    import os
+    from pathlib import Path
+    import pytest
+    from kareus_b200.config_yaml import load_run_config
+    ref = Path(os.environ.get("KAREUS_REFERENCE_DIR", "/nonexistent")) / "tests" / "artifact" / "conf"
+    if not ref.exists():
+        pytest.skip("KAREUS_REFERENCE_DIR not set")
+    m, p, t, sw = load_run_config(ref / "megatron_llama3.2_3b_config.yaml")
+    assert (m.num_layers, m.hidden_size, m.ffn_hidden_size, m.vocab_size) == (28, 3072, 8192, 128256)
+    assert (p.tp, p.pp, p.cp, p.recompute) == (8, 2, 1, True) and (t.micro_batch_size, t.global_batch_size) == (8, 64)
+    assert sw.data_prefix.endswith("llama_dataset_text_document") and sw.data_split == "900,50,50"
+    m, p, t, sw = load_run_config(ref / "megatron_qwen3_1.7b_config.yaml")
+    assert m.qk_layernorm and m.tie_embeddings and m.vocab_size == 151936 and m.hidden_size == 2048

@@ -15,6 +15,17 @@ import os
 import torch
 
 
+def env_freq_grid():
+    """``FREQ_START`` / ``FREQ_END`` / ``FREQ_STEP`` (MHz) of the reference's driver scripts, highest clock first;
+    ``None`` unless start and end are set."""
+    lo, hi = os.environ.get("FREQ_START"), os.environ.get("FREQ_END")
+    if not lo or not hi:
+        return None
+    step = abs(int(os.environ.get("FREQ_STEP", "30"))) or 30
+    a, b = sorted((int(lo), int(hi)))
+    return list(range(b, a - 1, -step))
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--partition", default="fwd_attn",
@@ -26,7 +37,7 @@ def main(argv=None) -> int:
     ap.add_argument("-cp", "--context_parallel_size", type=int, default=1)
     ap.add_argument("-b", "--batch_size", type=int, default=8)
     ap.add_argument("-s", "--seq_len", type=int, default=4096)
-    ap.add_argument("--gpu_type", default="B200")
+    ap.add_argument("--gpu_type", default=os.environ.get("GPU_TYPE", "B200"))
     ap.add_argument("--out", default=".")
     ap.add_argument("--tp-comm", default="allreduce")
     ap.add_argument("--comm-backend", default="kernel")
@@ -68,7 +79,7 @@ def main(argv=None) -> int:
     from ..energy.nvml import FakeNVML
     monitor = EnergyMonitor([local] if cuda else [0], nvml=None if cuda else FakeNVML(1))
     ctl = FrequencyController(local if cuda else 0, a.clock_mode, nvml=monitor.nvml)
-    freqs = list(a.freqs) if a.freqs else get_freq_grid(a.gpu_type)
+    freqs = list(a.freqs) if a.freqs else env_freq_grid() or get_freq_grid(a.gpu_type)
 
     if a.nonpartition:
         from ..models.llama import GPTModel

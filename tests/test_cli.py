@@ -137,3 +137,16 @@ def test_bench_reference_arm_says_why_it_is_unavailable():
     line = json.loads(r.stdout.strip().splitlines()[-1])
     assert line["impl"] == "reference" and isinstance(line["unavailable"], str) and line["unavailable"]
     assert "value" not in line
+
+
+def test_profiler_clock_grid_from_driver_environment(monkeypatch):
+    """FREQ_START / FREQ_END / FREQ_STEP of the reference's driver scripts give the profiler's clock grid."""
+    from kareus_b200.cli.run_bayesian import env_freq_grid
+    for k in ("FREQ_START", "FREQ_END", "FREQ_STEP"):
+        monkeypatch.delenv(k, raising=False)
+    assert env_freq_grid() is None
+    monkeypatch.setenv("FREQ_START", "900")
+    monkeypatch.setenv("FREQ_END", "1410")
+    monkeypatch.setenv("FREQ_STEP", "30")
+    grid = env_freq_grid()
+    assert grid[0] == 1410 and grid[-1] == 900 and len(grid) == 18

@@ -354,6 +354,8 @@ def main() -> int:
                        "parallelism": layout, "nanobatches": args.nano, "tp_comm": par.tp_comm,
                        "cp_comm": args.cp_comm if args.cp > 1 else None,
                        "comm_backend": par.comm_backend, "comm_sm": args.comm_sm,
+                       "ag_drivers": ("as comm_sm" if os.environ.get("KAREUS_AG_AUTO", "1") == "0" else
+                                      "comm_sm x3 up to N=768, x2 up to N=1280, at most a third of the kernel's SMs"),
                        "sync": os.environ.get("KAREUS_SYNC", "partition_end"),
                        "comm_streams": os.environ.get("KAREUS_COMM_STREAMS", "shared"),
                        "fused_sms": os.environ.get("KAREUS_FUSED_SMS", "0"), "recompute": f"full, {args.recompute_layers} layers per chunk",

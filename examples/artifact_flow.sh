@@ -1,0 +1,55 @@
+#!/usr/bin/env bash
+# The whole artifact flow on one node, phase by phase: profile the partitions, compose and plan, train with every
+# method, compare energy and time.  Counterpart of the reference's tests/artifact scripts (kareus_run_bayesian.sh,
+# megatron_perseus_run_profiling.sh, run_megatron.sh, run_nanobatch.sh, run_perseus.sh, run_kareus.sh,
+# compare_method.py).  Everything is a `python -m kareus_b200.cli.<driver>` call under torchrun; edit freely.
+#
+#   NPROC=8 TP=8 MODEL=llama3.2_3b bash examples/artifact_flow.sh            # B200 node
+#   NPROC=2 TP=2 MODEL=tiny SEQ=32 MBS=4 GBS=8 STEPS=4 QUICK=1 bash examples/artifact_flow.sh   # CPU smoke run
+#
+# Clock mode: "advisory" (default) leaves the GPU clocks alone and profiles at the default clock; "locked" sets them
+# through NVML and needs the rights to do so.
+set -euo pipefail
+
+MODEL=${MODEL:-llama3.2_3b}; NPROC=${NPROC:-8}; TP=${TP:-$NPROC}; PP=${PP:-1}; CP=${CP:-1}
+MBS=${MBS:-8}; GBS=${GBS:-64}; SEQ=${SEQ:-4096}; STEPS=${STEPS:-30}
+WORK=${WORK:-kareus_runs}; GPU_TYPE=${GPU_TYPE:-B200}; CLOCK_MODE=${CLOCK_MODE:-advisory}
+TP_COMM=${TP_COMM:-sp_fused}; MASTER_PORT=${MASTER_PORT:-6000}; QUICK=${QUICK:-0}
+SKIP_PROFILING=${SKIP_PROFILING:-false}
+TAG="cp${CP}_tp${TP}_mbs${MBS}_seq${SEQ}"
+RUN="python -m torch.distributed.run --nnodes=1 --nproc-per-node ${NPROC} --master-addr 127.0.0.1 --master-port ${MASTER_PORT}"
+if [ "$QUICK" = "1" ]; then      # a few configurations per partition, short measurements
+  BO_ARGS="--n-init 3 --batches 1 --acq-batch 1 --measure-s 0.05 --cooldown-s 0 --freqs 1500 1200"
+  PERSEUS_ARGS="--freqs 1500 1200 --steps 2 --skip 1"; SKIP=1; TAKE=$((STEPS - 1)); MAXIT="--max-iterations 30"
+  [ "$(python -c 'import torch; print(int(torch.cuda.is_available()))')" = "0" ] && TP_COMM=sp && BO_ARGS="$BO_ARGS --comm-backend nccl"
+else
+  BO_ARGS=""; PERSEUS_ARGS=""; SKIP=10; TAKE=20; MAXIT=""
+fi
+mkdir -p "$WORK"
+
+if [ "$SKIP_PROFILING" != "true" ]; then
+  echo "== 1. profile every partition of the tensor-parallel path, then the non-partition pieces"
+  $RUN -m kareus_b200.cli.run_bayesian --partition all --tp-comm "$TP_COMM" -m "$MODEL" -w "$NPROC" -tp "$TP" -cp "$CP" \
+      -b "$MBS" -s "$SEQ" --gpu_type "$GPU_TYPE" --clock-mode "$CLOCK_MODE" --out "$WORK/bayesian" $BO_ARGS
+  $RUN -m kareus_b200.cli.run_bayesian --nonpartition -m "$MODEL" -w "$NPROC" -tp "$TP" -cp "$CP" -b "$MBS" -s "$SEQ" \
+      --gpu_type "$GPU_TYPE" --clock-mode "$CLOCK_MODE" --out "$WORK/bayesian" $BO_ARGS
+  echo "== 2. per-instruction time/energy at every clock for the frequency-only baseline"
+  $RUN -m kareus_b200.cli.run_perseus_profile --method perseus --model "$MODEL" --tp "$TP" --pp "$PP" --mbs "$MBS" \
+      --gbs "$GBS" --seq "$SEQ" --gpu_type "$GPU_TYPE" --clock-mode "$CLOCK_MODE" --out "$WORK/perseus_profile.csv" $PERSEUS_ARGS
+fi
+
+echo "== 3. baselines: one nanobatch, two nanobatches"
+for METHOD in megatron nanobatch; do
+  $RUN -m kareus_b200.cli.run_train --method $METHOD --model "$MODEL" --tp "$TP" --pp "$PP" --cp "$CP" --mbs "$MBS" \
+      --gbs "$GBS" --seq "$SEQ" --steps "$STEPS" --tp-comm "$TP_COMM" --clock-mode "$CLOCK_MODE" --out "$WORK/runs"
+done
+
+echo "== 4. compose the partition frontiers, plan, train under the max-throughput plan"
+$RUN -m kareus_b200.cli.run_kareus --model "$MODEL" --tp "$TP" --pp "$PP" --cp "$CP" --mbs "$MBS" --gbs "$GBS" --seq "$SEQ" \
+    --steps "$STEPS" --bayesian-dir "$WORK/bayesian" --workdir "$WORK/runs" --gpu_type "$GPU_TYPE" \
+    --clock-mode "$CLOCK_MODE" --tp-comm "$TP_COMM" $MAXIT
+
+echo "== 5. energy and time of each method against the one-nanobatch baseline"
+python -m kareus_b200.cli.compare --base "$WORK/runs/$MODEL/$TAG/megatron" \
+    --runs "$WORK/runs/$MODEL/$TAG/nanobatch" "$WORK/runs/$MODEL/$TAG/kareus" --skip "$SKIP" --take "$TAKE" \
+    --num_stages "$PP" --gpu_type "$GPU_TYPE"

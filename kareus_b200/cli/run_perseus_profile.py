@@ -56,7 +56,7 @@ def main(argv=None) -> int:
                      dtype="bf16" if cuda else "fp32")
     from ..energy.nvml import FakeNVML
     monitor = EnergyMonitor([local] if cuda else [0], nvml=None if cuda else FakeNVML(1))
-    ctl = FrequencyController(local, a.clock_mode, nvml=monitor.nvml)
+    ctl = FrequencyController(local if cuda else 0, a.clock_mode, nvml=monitor.nvml)   # simulated NVML: one device
     trainer = Trainer(cfg, par, tc, mesh=mesh, device=device)
     if a.route == "timers":
         from pathlib import Path

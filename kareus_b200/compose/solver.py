@@ -312,5 +312,14 @@ def plan_pipeline(num_stages: int, num_micro_batches: int, options: Dict[int, Di
     specs = {s: {k: OperationSpec.build(v, noise_factor) for k, v in kinds.items()} for s, kinds in options.items()}
     stages, flat, edges = build_1f1b_dag(num_stages, num_micro_batches, specs)
     solver = PhillipsDessouky(flat, edges, unit_time, use_native)
+    produced = False
     for res in solver.run(max_iterations):
+        produced = True
         yield res, stages
+    if not produced:
+        # nothing can be shortened (e.g. one measured option per instruction): the minimum-energy schedule
+        # is the whole frontier, and still a plan that a run can execute
+        for inst in flat:
+            inst.assigned_knob = inst.spec.knob_for(inst.duration)
+        total = _schedule(flat, edges)[2]
+        yield IterationResult(0, solver.total_cost(), 0.0, total, total * unit_time), stages

@@ -18,6 +18,10 @@ TP_COMM=${TP_COMM:-sp_fused}; MASTER_PORT=${MASTER_PORT:-6000}; QUICK=${QUICK:-0
 SKIP_PROFILING=${SKIP_PROFILING:-false}
 TAG="cp${CP}_tp${TP}_mbs${MBS}_seq${SEQ}"
 RUN="python -m torch.distributed.run --nnodes=1 --nproc-per-node ${NPROC} --master-addr 127.0.0.1 --master-port ${MASTER_PORT}"
+# the partition profiler works on one pipeline stage: the ranks of one tensor x context parallel group
+NPROF=$((TP * CP))
+RUNP="python -m torch.distributed.run --nnodes=1 --nproc-per-node ${NPROF} --master-addr 127.0.0.1 --master-port ${MASTER_PORT}"
+DP=$((NPROC / (TP * CP * PP))); NUM_MBS=$((GBS / (MBS * DP)))
 if [ "$QUICK" = "1" ]; then      # a few configurations per partition, short measurements
   BO_ARGS="--n-init 3 --batches 1 --acq-batch 1 --measure-s 0.05 --cooldown-s 0 --freqs 1500 1200"
   PERSEUS_ARGS="--freqs 1500 1200 --steps 2 --skip 1"; SKIP=1; TAKE=$((STEPS - 1)); MAXIT="--max-iterations 30"
@@ -28,11 +32,15 @@ fi
 mkdir -p "$WORK"
 
 if [ "$SKIP_PROFILING" != "true" ]; then
-  echo "== 1. profile every partition of the tensor-parallel path, then the non-partition pieces"
-  $RUN -m kareus_b200.cli.run_bayesian --partition all --tp-comm "$TP_COMM" -m "$MODEL" -w "$NPROC" -tp "$TP" -cp "$CP" \
-      -b "$MBS" -s "$SEQ" --gpu_type "$GPU_TYPE" --clock-mode "$CLOCK_MODE" --out "$WORK/bayesian" $BO_ARGS
-  $RUN -m kareus_b200.cli.run_bayesian --nonpartition -m "$MODEL" -w "$NPROC" -tp "$TP" -cp "$CP" -b "$MBS" -s "$SEQ" \
-      --gpu_type "$GPU_TYPE" --clock-mode "$CLOCK_MODE" --out "$WORK/bayesian" $BO_ARGS
+  if [ "$NPROF" -gt 1 ]; then
+    echo "== 1. profile every partition of the tensor-parallel path, then the non-partition pieces"
+    $RUNP -m kareus_b200.cli.run_bayesian --partition all --tp-comm "$TP_COMM" -m "$MODEL" -w "$NPROF" -tp "$TP" -cp "$CP" \
+        -b "$MBS" -s "$SEQ" --gpu_type "$GPU_TYPE" --clock-mode "$CLOCK_MODE" --out "$WORK/bayesian" $BO_ARGS
+    $RUNP -m kareus_b200.cli.run_bayesian --nonpartition -m "$MODEL" -w "$NPROF" -tp "$TP" -cp "$CP" -b "$MBS" -s "$SEQ" \
+        --gpu_type "$GPU_TYPE" --clock-mode "$CLOCK_MODE" --out "$WORK/bayesian" $BO_ARGS
+  else
+    echo "== 1. no tensor or context parallelism: nothing overlaps, nothing to profile per partition"
+  fi
   echo "== 2. per-instruction time/energy at every clock for the frequency-only baseline"
   $RUN -m kareus_b200.cli.run_perseus_profile --method perseus --model "$MODEL" --tp "$TP" --pp "$PP" --mbs "$MBS" \
       --gbs "$GBS" --seq "$SEQ" --gpu_type "$GPU_TYPE" --clock-mode "$CLOCK_MODE" --out "$WORK/perseus_profile.csv" $PERSEUS_ARGS
@@ -44,12 +52,25 @@ for METHOD in megatron nanobatch; do
       --gbs "$GBS" --seq "$SEQ" --steps "$STEPS" --tp-comm "$TP_COMM" --clock-mode "$CLOCK_MODE" --out "$WORK/runs"
 done
 
-echo "== 4. compose the partition frontiers, plan, train under the max-throughput plan"
-$RUN -m kareus_b200.cli.run_kareus --model "$MODEL" --tp "$TP" --pp "$PP" --cp "$CP" --mbs "$MBS" --gbs "$GBS" --seq "$SEQ" \
-    --steps "$STEPS" --bayesian-dir "$WORK/bayesian" --workdir "$WORK/runs" --gpu_type "$GPU_TYPE" \
-    --clock-mode "$CLOCK_MODE" --tp-comm "$TP_COMM" $MAXIT
+COMPARE="$WORK/runs/$MODEL/$TAG/nanobatch"
+if [ -f "$WORK/perseus_profile.csv" ]; then
+  echo "== 4a. frequency-only plan from the per-instruction profile, train under its max-throughput point"
+  python -m kareus_b200.cli.run_optimization --inst_profile "$WORK/perseus_profile.csv" --output_dir "$WORK/perseus_plans" \
+      --num_stages "$PP" --num_mbs "$NUM_MBS" --gpu_type "$GPU_TYPE" ${MAXIT/--max-iterations/--max_iterations}
+  FREQS=$(ls "$WORK"/perseus_plans/freqs_pipeline_*.py | sort | tail -1)      # the highest-numbered plan is the fastest
+  $RUN -m kareus_b200.cli.run_train --method perseus --model "$MODEL" --tp "$TP" --pp "$PP" --cp "$CP" --mbs "$MBS" \
+      --gbs "$GBS" --seq "$SEQ" --steps "$STEPS" --tp-comm "$TP_COMM" --clock-mode "$CLOCK_MODE" --freqs "$FREQS" \
+      --out "$WORK/runs"
+  COMPARE="$COMPARE $WORK/runs/$MODEL/$TAG/perseus"
+fi
+if [ "$NPROF" -gt 1 ]; then
+  echo "== 4b. compose the partition frontiers, plan, train under the max-throughput plan"
+  $RUN -m kareus_b200.cli.run_kareus --model "$MODEL" --tp "$TP" --pp "$PP" --cp "$CP" --mbs "$MBS" --gbs "$GBS" --seq "$SEQ" \
+      --steps "$STEPS" --bayesian-dir "$WORK/bayesian" --workdir "$WORK/runs" --gpu_type "$GPU_TYPE" \
+      --clock-mode "$CLOCK_MODE" --tp-comm "$TP_COMM" $MAXIT
+  COMPARE="$COMPARE $WORK/runs/$MODEL/$TAG/kareus"
+fi
 
 echo "== 5. energy and time of each method against the one-nanobatch baseline"
-python -m kareus_b200.cli.compare --base "$WORK/runs/$MODEL/$TAG/megatron" \
-    --runs "$WORK/runs/$MODEL/$TAG/nanobatch" "$WORK/runs/$MODEL/$TAG/kareus" --skip "$SKIP" --take "$TAKE" \
+python -m kareus_b200.cli.compare --base "$WORK/runs/$MODEL/$TAG/megatron" --runs $COMPARE --skip "$SKIP" --take "$TAKE" \
     --num_stages "$PP" --gpu_type "$GPU_TYPE"

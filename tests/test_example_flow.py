@@ -15,10 +15,23 @@ def test_artifact_flow_on_two_cpu_ranks(tmp_path):
                        text=True, timeout=900)
     assert r.returncode == 0, r.stdout[-3000:] + "\n" + r.stderr[-3000:]
     lines = [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{") and '"run"' in l]
-    assert [Path(l["run"]).name for l in lines] == ["megatron", "nanobatch", "kareus"]
+    assert [Path(l["run"]).name for l in lines] == ["megatron", "nanobatch", "perseus", "kareus"]
     assert all(l["iterations"] == 3 and l["ranks"] == 2 for l in lines)
     assert "energy_reduction_pct" in lines[1]
     runs = tmp_path / "w" / "runs" / "tiny" / "cp1_tp2_mbs4_seq32"
     assert list((runs / "kareus" / "lowtime").glob("freqs_pipeline_*.py"))
     assert (tmp_path / "w" / "perseus_profile.csv").exists()
     assert (tmp_path / "w" / "bayesian" / "logs" / "tiny" / "cp1-tp2-bs4-seq32" / "fwd_attn_ag" / "eval_results.jsonl").exists()
+
+
+def test_artifact_flow_with_pipeline_stages_only(tmp_path):
+    """Two pipeline stages, no tensor parallelism: nothing to profile per partition, the frequency-only plan is
+    the whole story."""
+    env = dict(os.environ, NPROC="2", TP="1", PP="2", MODEL="tiny", SEQ="32", MBS="2", GBS="8", STEPS="4", QUICK="1",
+               WORK=str(tmp_path / "w"), MASTER_PORT="29963", CUDA_VISIBLE_DEVICES="")
+    r = subprocess.run(["bash", str(ROOT / "examples" / "artifact_flow.sh")], cwd=ROOT, env=env, capture_output=True,
+                       text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + "\n" + r.stderr[-3000:]
+    lines = [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{") and '"run"' in l]
+    assert [Path(l["run"]).name for l in lines] == ["megatron", "nanobatch", "perseus"]
+    assert list((tmp_path / "w" / "perseus_plans").glob("freqs_pipeline_*.py"))

@@ -2,7 +2,9 @@
 
 Rule (reference ``tests/artifact/create_frontier.sh:20-26,96-143``): sort plan files by name,
 take a stride of ``ceil(total/15)`` walking down from the last file, re-sort ascending, then drop
-positions 0, 2, 4, 6 and 8.  The highest-numbered file (max throughput) always survives.
+positions 0, 2, 4, 6 and 8.  With the solver's usual output (hundreds of plans, 15 picked) the highest-numbered
+file (max throughput) is position 14 and survives; with fewer than ten picked files it could sit on a dropped
+position, so it is kept explicitly: a frontier is never empty.
 """
 from __future__ import annotations
 
@@ -25,7 +27,8 @@ def sample_frontier(names: Sequence[str], num_samples: int = 15,
     else:
         picked = files
     dropset = set(drop)
-    return [f for i, f in enumerate(picked) if i not in dropset]
+    last = len(picked) - 1
+    return [f for i, f in enumerate(picked) if i not in dropset or i == last]
 
 
 def select_max_throughput(names: Sequence[str]) -> str:

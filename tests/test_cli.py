@@ -150,3 +150,13 @@ def test_profiler_clock_grid_from_driver_environment(monkeypatch):
     monkeypatch.setenv("FREQ_STEP", "30")
     grid = env_freq_grid()
     assert grid[0] == 1410 and grid[-1] == 900 and len(grid) == 18
+
+
+def test_small_frontiers_keep_the_max_throughput_plan():
+    from kareus_b200.plan.frontier import sample_frontier
+    names = [f"freqs_pipeline_{i:05d}.py" for i in range(2496)]
+    picked = sample_frontier(names)
+    assert len(picked) == 10 and picked[-1] == names[-1]            # the reference's counts: unchanged
+    for n in (1, 2, 3, 5, 7, 9):
+        got = sample_frontier(names[:n])
+        assert got and got[-1] == names[n - 1], (n, got)

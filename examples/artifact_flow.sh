@@ -16,6 +16,8 @@ MBS=${MBS:-8}; GBS=${GBS:-64}; SEQ=${SEQ:-4096}; STEPS=${STEPS:-30}
 WORK=${WORK:-kareus_runs}; GPU_TYPE=${GPU_TYPE:-B200}; CLOCK_MODE=${CLOCK_MODE:-advisory}
 TP_COMM=${TP_COMM:-sp_fused}; MASTER_PORT=${MASTER_PORT:-6000}; QUICK=${QUICK:-0}
 SKIP_PROFILING=${SKIP_PROFILING:-false}
+# with context parallelism the partition plan covers the all-reduce flavour of tensor parallelism
+[ "$CP" -gt 1 ] && TP_COMM=allreduce
 TAG="cp${CP}_tp${TP}_mbs${MBS}_seq${SEQ}"
 RUN="python -m torch.distributed.run --nnodes=1 --nproc-per-node ${NPROC} --master-addr 127.0.0.1 --master-port ${MASTER_PORT}"
 # the partition profiler works on one pipeline stage: the ranks of one tensor x context parallel group
@@ -25,21 +27,24 @@ DP=$((NPROC / (TP * CP * PP))); NUM_MBS=$((GBS / (MBS * DP)))
 if [ "$QUICK" = "1" ]; then      # a few configurations per partition, short measurements
   BO_ARGS="--n-init 3 --batches 1 --acq-batch 1 --measure-s 0.05 --cooldown-s 0 --freqs 1500 1200"
   PERSEUS_ARGS="--freqs 1500 1200 --steps 2 --skip 1"; SKIP=1; TAKE=$((STEPS - 1)); MAXIT="--max-iterations 30"
-  [ "$(python -c 'import torch; print(int(torch.cuda.is_available()))')" = "0" ] && TP_COMM=sp && BO_ARGS="$BO_ARGS --comm-backend nccl"
+  if [ "$(python -c 'import torch; print(int(torch.cuda.is_available()))')" = "0" ]; then
+    [ "$TP_COMM" = "sp_fused" ] && TP_COMM=sp          # the fused kernels need GPUs
+    BO_ARGS="$BO_ARGS --comm-backend nccl"
+  fi
 else
   BO_ARGS=""; PERSEUS_ARGS=""; SKIP=10; TAKE=20; MAXIT=""
 fi
 mkdir -p "$WORK"
 
 if [ "$SKIP_PROFILING" != "true" ]; then
-  if [ "$NPROF" -gt 1 ]; then
+  if [ "$TP" -gt 1 ]; then
     echo "== 1. profile every partition of the tensor-parallel path, then the non-partition pieces"
     $RUNP -m kareus_b200.cli.run_bayesian --partition all --tp-comm "$TP_COMM" -m "$MODEL" -w "$NPROF" -tp "$TP" -cp "$CP" \
         -b "$MBS" -s "$SEQ" --gpu_type "$GPU_TYPE" --clock-mode "$CLOCK_MODE" --out "$WORK/bayesian" $BO_ARGS
     $RUNP -m kareus_b200.cli.run_bayesian --nonpartition -m "$MODEL" -w "$NPROF" -tp "$TP" -cp "$CP" -b "$MBS" -s "$SEQ" \
         --gpu_type "$GPU_TYPE" --clock-mode "$CLOCK_MODE" --out "$WORK/bayesian" $BO_ARGS
   else
-    echo "== 1. no tensor or context parallelism: nothing overlaps, nothing to profile per partition"
+    echo "== 1. no tensor parallelism: the partition plan (overlap of tensor-parallel collectives) does not apply"
   fi
   echo "== 2. per-instruction time/energy at every clock for the frequency-only baseline"
   $RUN -m kareus_b200.cli.run_perseus_profile --method perseus --model "$MODEL" --tp "$TP" --pp "$PP" --mbs "$MBS" \
@@ -63,7 +68,7 @@ if [ -f "$WORK/perseus_profile.csv" ]; then
       --out "$WORK/runs"
   COMPARE="$COMPARE $WORK/runs/$MODEL/$TAG/perseus"
 fi
-if [ "$NPROF" -gt 1 ]; then
+if [ "$TP" -gt 1 ]; then
   echo "== 4b. compose the partition frontiers, plan, train under the max-throughput plan"
   $RUN -m kareus_b200.cli.run_kareus --model "$MODEL" --tp "$TP" --pp "$PP" --cp "$CP" --mbs "$MBS" --gbs "$GBS" --seq "$SEQ" \
       --steps "$STEPS" --bayesian-dir "$WORK/bayesian" --workdir "$WORK/runs" --gpu_type "$GPU_TYPE" \

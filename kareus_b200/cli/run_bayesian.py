@@ -95,6 +95,13 @@ def main(argv=None) -> int:
     import copy
     from ..profile.space import CP_PARTITIONS, SP_FUSED_PARTITIONS, TP_PARTITIONS
     if a.partition == "all":
+        if tp == 1:
+            raise SystemExit("--partition all needs tensor parallelism: the partitions are the segments of a layer around "
+                             "its tensor-parallel collectives (context-parallel partitions are profiled together with "
+                             "them, as in the reference's TP x CP configurations)")
+        if cp > 1 and a.tp_comm != "allreduce":
+            raise SystemExit("--partition all with context parallelism profiles the all-reduce flavour of tensor "
+                             "parallelism (the reference's TP x CP layouts): pass --tp-comm allreduce")
         parts = CP_PARTITIONS if cp > 1 else (SP_FUSED_PARTITIONS if a.tp_comm in ("sp", "sp_fused") else TP_PARTITIONS)
     else:
         parts = (a.partition,)

@@ -280,7 +280,9 @@ class AttentionOp(GraphOperator):
 
     def _backward_cp(self, ctx, dout):
         q, k_loc, v_loc, out, lse0, lse1 = ctx.saved_tensors
-        k, v = ctx.extra.pop("regathered")
+        # left in place: the engine drops the operator's context after backward, and a profiler that runs this
+        # step again (release_saved=False) finds it still there
+        k, v = ctx.extra["regathered"]
         s, b = q.shape[0], q.shape[1]
         c = s // 2
         do = dout.reshape(s, b, q_heads(q), self.d)

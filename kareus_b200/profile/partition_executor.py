@@ -41,10 +41,22 @@ class PartitionExecutor:
         self.comm = comm or CommFactory(mesh, par.comm_backend)
         self.layer = TransformerLayer(model_cfg, par, self.comm, 0, dt, self.device, seed=seed)
         n = par.num_nanobatches
-        self.chunk = _Chunk(self.layer.operators(), n, "partition_end")
+        # same step naming as the model's block: with tensor x context parallelism (all-reduce flavour) steps
+        # carry the reference's context-parallel keys (fwd_qkv_ar, fwd_qkv_ag, fwd_ao_ag, ...)
+        cp_keys = par.cp > 1 and par.tp > 1 and par.tp_comm == "allreduce"
         self.backward = key.startswith("bwd_")
-        prog = self.chunk.bwd if self.backward else self.chunk.fwd
-        cands = [s for s in prog.steps if s.key == key and s.compute]
+        self.layers = [self.layer]
+        for depth in (1, 2):
+            # some steps exist only between two layers: a layer's first segment beside the collective that
+            # the previous layer's last segment started (fwd_qkv_ar, bwd_o_ar of the context-parallel plan)
+            if depth == 2:
+                self.layers.append(TransformerLayer(model_cfg, par, self.comm, 1, dt, self.device, seed=seed + 1))
+            ops = [op for l in self.layers for op in l.operators()]
+            self.chunk = _Chunk(ops, n, "partition_end", cp_keys=cp_keys)
+            prog = self.chunk.bwd if self.backward else self.chunk.fwd
+            cands = [s for s in prog.steps if s.key == key and s.compute]
+            if cands:
+                break
         if not cands:
             raise KeyError(f"partition key {key!r} does not occur with tp_comm={par.tp_comm!r}, cp={par.cp}; "
                            f"program keys: {sorted(set(prog.expected_keys()))}")

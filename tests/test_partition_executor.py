@@ -81,3 +81,29 @@ def test_fused_sequence_parallel_partitions_name_real_slots():
             assert slot in steps[-1].slots, (key, slot, steps[-1].slots)
         assert partition_space(key, "sp_fused")[0] == kind
     assert partition_space("fwd_attn", "allreduce")[0] == "all_reduce"
+
+
+def _cp_partition_worker(rank, world):
+    """Context-parallel partitions on TP2 x CP2: one that only exists between two layers (a layer's first
+    segment beside the previous layer's MLP all-reduce) and a backward one whose attention backward consumes
+    re-gathered K/V, each executed several times as the profiler does."""
+    import torch
+    from kareus_b200.config import ParallelConfig, get_model_config
+    from kareus_b200.parallel.collectives import CommFactory
+    from kareus_b200.parallel.mesh import Mesh
+    from kareus_b200.profile.partition_executor import PartitionExecutor
+    cfg = get_model_config("tiny")
+    mesh = Mesh(tp=2, cp=2, dp=1, pp=1)
+    par = ParallelConfig(tp=2, cp=2, num_nanobatches=2, tp_comm="allreduce", comm_backend="nccl", recompute=False)
+    for key in ("fwd_qkv_ar", "bwd_a_ag", "bwd_o_ar", "bwd_qkv_rs"):
+        ex = PartitionExecutor(cfg, par, key, 2, 64, mesh=mesh, comm=CommFactory(mesh, "nccl"), device="cpu",
+                               dtype="fp32")
+        assert ex.step.key == key and ex.step.comm is not None, key
+        slot = sorted(ex.slots())[0]
+        for _ in range(3):
+            ex.execute(overlap_window=(slot, "none"), resource_shape=(4, 1024))
+
+
+def test_context_parallel_partitions_run_repeatedly():
+    from dist_utils import run_distributed
+    run_distributed(_cp_partition_worker, 4, timeout=300.0)

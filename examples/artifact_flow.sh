@@ -16,6 +16,7 @@ MBS=${MBS:-8}; GBS=${GBS:-64}; SEQ=${SEQ:-4096}; STEPS=${STEPS:-30}
 WORK=${WORK:-kareus_runs}; GPU_TYPE=${GPU_TYPE:-B200}; CLOCK_MODE=${CLOCK_MODE:-advisory}
 TP_COMM=${TP_COMM:-sp_fused}; MASTER_PORT=${MASTER_PORT:-6000}; QUICK=${QUICK:-0}
 SKIP_PROFILING=${SKIP_PROFILING:-false}
+PERSEUS_METHODS=${PERSEUS_METHODS:-"perseus nanobatch_perseus"}      # frequency-only plans: one / two nanobatches
 # with context parallelism the partition plan covers the all-reduce flavour of tensor parallelism
 [ "$CP" -gt 1 ] && TP_COMM=allreduce
 TAG="cp${CP}_tp${TP}_mbs${MBS}_seq${SEQ}"
@@ -46,9 +47,12 @@ if [ "$SKIP_PROFILING" != "true" ]; then
   else
     echo "== 1. no tensor parallelism: the partition plan (overlap of tensor-parallel collectives) does not apply"
   fi
-  echo "== 2. per-instruction time/energy at every clock for the frequency-only baseline"
-  $RUN -m kareus_b200.cli.run_perseus_profile --method perseus --model "$MODEL" --tp "$TP" --pp "$PP" --mbs "$MBS" \
-      --gbs "$GBS" --seq "$SEQ" --gpu_type "$GPU_TYPE" --clock-mode "$CLOCK_MODE" --out "$WORK/perseus_profile.csv" $PERSEUS_ARGS
+  echo "== 2. per-instruction time/energy at every clock for the frequency-only baselines"
+  for METHOD in $PERSEUS_METHODS; do
+    $RUN -m kareus_b200.cli.run_perseus_profile --method $METHOD --model "$MODEL" --tp "$TP" --pp "$PP" --mbs "$MBS" \
+        --gbs "$GBS" --seq "$SEQ" --gpu_type "$GPU_TYPE" --clock-mode "$CLOCK_MODE" --out "$WORK/${METHOD}_profile.csv" \
+        $PERSEUS_ARGS
+  done
 fi
 
 echo "== 3. baselines: one nanobatch, two nanobatches"
@@ -58,16 +62,18 @@ for METHOD in megatron nanobatch; do
 done
 
 COMPARE="$WORK/runs/$MODEL/$TAG/nanobatch"
-if [ -f "$WORK/perseus_profile.csv" ]; then
-  echo "== 4a. frequency-only plan from the per-instruction profile, train under its max-throughput point"
-  python -m kareus_b200.cli.run_optimization --inst_profile "$WORK/perseus_profile.csv" --output_dir "$WORK/perseus_plans" \
-      --num_stages "$PP" --num_mbs "$NUM_MBS" --gpu_type "$GPU_TYPE" ${MAXIT/--max-iterations/--max_iterations}
-  FREQS=$(ls "$WORK"/perseus_plans/freqs_pipeline_*.py | sort | tail -1)      # the highest-numbered plan is the fastest
-  $RUN -m kareus_b200.cli.run_train --method perseus --model "$MODEL" --tp "$TP" --pp "$PP" --cp "$CP" --mbs "$MBS" \
+for METHOD in $PERSEUS_METHODS; do
+  [ -f "$WORK/${METHOD}_profile.csv" ] || continue
+  echo "== 4a. $METHOD: frequency-only plan from the per-instruction profile, train under its max-throughput point"
+  python -m kareus_b200.cli.run_optimization --inst_profile "$WORK/${METHOD}_profile.csv" \
+      --output_dir "$WORK/${METHOD}_plans" --num_stages "$PP" --num_mbs "$NUM_MBS" --gpu_type "$GPU_TYPE" \
+      ${MAXIT/--max-iterations/--max_iterations}
+  FREQS=$(ls "$WORK/${METHOD}_plans"/freqs_pipeline_*.py | sort | tail -1)    # the highest-numbered plan is the fastest
+  $RUN -m kareus_b200.cli.run_train --method $METHOD --model "$MODEL" --tp "$TP" --pp "$PP" --cp "$CP" --mbs "$MBS" \
       --gbs "$GBS" --seq "$SEQ" --steps "$STEPS" --tp-comm "$TP_COMM" --clock-mode "$CLOCK_MODE" --freqs "$FREQS" \
       --out "$WORK/runs"
-  COMPARE="$COMPARE $WORK/runs/$MODEL/$TAG/perseus"
-fi
+  COMPARE="$COMPARE $WORK/runs/$MODEL/$TAG/$METHOD"
+done
 if [ "$TP" -gt 1 ]; then
   echo "== 4b. compose the partition frontiers, plan, train under the max-throughput plan"
   $RUN -m kareus_b200.cli.run_kareus --model "$MODEL" --tp "$TP" --pp "$PP" --cp "$CP" --mbs "$MBS" --gbs "$GBS" --seq "$SEQ" \

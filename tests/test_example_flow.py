@@ -20,12 +20,12 @@ def test_artifact_flow_on_two_cpu_ranks(tmp_path):
                        text=True, timeout=900)
     assert r.returncode == 0, r.stdout[-3000:] + "\n" + r.stderr[-3000:]
     lines = [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{") and '"run"' in l]
-    assert [Path(l["run"]).name for l in lines] == ["megatron", "nanobatch", "perseus", "kareus"]
+    assert [Path(l["run"]).name for l in lines] == ["megatron", "nanobatch", "perseus", "nanobatch_perseus", "kareus"]
     assert all(l["iterations"] == 3 and l["ranks"] == 2 for l in lines)
     assert "energy_reduction_pct" in lines[1]
     runs = tmp_path / "w" / "runs" / "tiny" / "cp1_tp2_mbs4_seq32"
     assert list((runs / "kareus" / "lowtime").glob("freqs_pipeline_*.py"))
-    assert (tmp_path / "w" / "perseus_profile.csv").exists()
+    assert (tmp_path / "w" / "perseus_profile.csv").exists() and (tmp_path / "w" / "nanobatch_perseus_profile.csv").exists()
     assert (tmp_path / "w" / "bayesian" / "logs" / "tiny" / "cp1-tp2-bs4-seq32" / "fwd_attn_ag" / "eval_results.jsonl").exists()
 
 
@@ -39,7 +39,7 @@ def test_artifact_flow_with_pipeline_stages_only(tmp_path):
                        text=True, timeout=900)
     assert r.returncode == 0, r.stdout[-3000:] + "\n" + r.stderr[-3000:]
     lines = [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{") and '"run"' in l]
-    assert [Path(l["run"]).name for l in lines] == ["megatron", "nanobatch", "perseus"]
+    assert [Path(l["run"]).name for l in lines] == ["megatron", "nanobatch", "perseus", "nanobatch_perseus"]
     assert list((tmp_path / "w" / "perseus_plans").glob("freqs_pipeline_*.py"))
 
 
@@ -53,7 +53,7 @@ def test_artifact_flow_with_tensor_and_context_parallelism(tmp_path):
                        text=True, timeout=1200)
     assert r.returncode == 0, r.stdout[-3000:] + "\n" + r.stderr[-3000:]
     lines = [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{") and '"run"' in l]
-    assert [Path(l["run"]).name for l in lines] == ["megatron", "nanobatch", "perseus", "kareus"]
+    assert [Path(l["run"]).name for l in lines] == ["megatron", "nanobatch", "perseus", "nanobatch_perseus", "kareus"]
     logs = tmp_path / "w" / "bayesian" / "logs" / "tiny" / "cp2-tp2-bs2-seq64"
     for key in ("fwd_qkv_ar", "fwd_qkv_ag", "fwd_ao_ag", "fwd_ao_ar", "fwd_mlp", "bwd_qkv_ar", "bwd_qkv_rs", "bwd_a_rs",
                 "bwd_a_ag", "bwd_o_ag", "bwd_o_ar", "bwd_mlp"):

@@ -56,6 +56,8 @@ def main(argv=None) -> int:
                   "--profile-ranks", *map(str, sw.nsys_ranks)]
     if sw.enable_megatron_timers:
         argv2.append("--enable-timers")
+    if not par.recompute:
+        argv2.append("--no-recompute")
     if sw.data_prefix:
         from pathlib import Path
         if Path(sw.data_prefix + ".idx").exists():

@@ -44,6 +44,9 @@ def main(argv=None) -> int:
     ap.add_argument("--enable-power-monitor", action="store_true")
     ap.add_argument("--enable-timers", action="store_true")
     ap.add_argument("--recompute-layers", type=int, default=4)
+    ap.add_argument("--no-recompute", action="store_true",
+                    help="keep all activations (the reference's activations_checkpoint_granularity: null); overlap plans "
+                         "are then read in the per-microbatch (forward, backward) pair layout")
     ap.add_argument("--profile-start-step", type=int, default=None,
                     help="open the CUDA profiler capture range at this step (nsys --capture-range=cudaProfilerApi)")
     ap.add_argument("--profile-end-step", type=int, default=None)
@@ -82,7 +85,7 @@ def main(argv=None) -> int:
     nano = 1 if a.method in ("megatron", "perseus") else 2
     tp_comm = a.tp_comm if a.tp > 1 else "allreduce"
     par = ParallelConfig(tp=a.tp, cp=a.cp, pp=a.pp, dp=dp, num_nanobatches=nano, tp_comm=tp_comm,
-                         comm_backend=a.comm_backend if cuda else "nccl", recompute=True)
+                         comm_backend=a.comm_backend if cuda else "nccl", recompute=not a.no_recompute)
     mesh = Mesh(tp=a.tp, cp=a.cp, dp=dp, pp=a.pp)
     cfg = get_model_config(a.model)
     tc = TrainConfig(micro_batch_size=a.mbs, global_batch_size=a.gbs, seq_len=a.seq,
@@ -110,10 +113,10 @@ def main(argv=None) -> int:
     if a.method == "kareus" and a.scheds:
         parsed = [None]
         if rank == 0:
-            parsed[0] = parse_schedule_file(a.scheds, True, a.cp > 1)
+            parsed[0] = parse_schedule_file(a.scheds, not a.no_recompute, a.cp > 1)
         if world > 1:
             dist.broadcast_object_list(parsed, src=0)      # rank 0 parses, everyone receives
-        sched = PipelineCommScheduler.from_parsed(parsed[0], mesh.pp_rank, M, True, a.cp > 1)
+        sched = PipelineCommScheduler.from_parsed(parsed[0], mesh.pp_rank, M, not a.no_recompute, a.cp > 1)
     heap = None
     if cuda and a.tp > 1 and (par.comm_backend == "kernel" or par.tp_comm == "sp_fused"):
         from ..parallel.symm_heap import SymmetricHeap

@@ -80,6 +80,20 @@ def _sched_item(kind: str, knob: tuple, mode: str) -> ScheduleItem:
     return ScheduleItem(kind, tuple(d.items()), cp)
 
 
+def _pair_items(stage_instructions, num_mbs: int, mode: str) -> List[ScheduleItem]:
+    """One item per microbatch holding the forward keys of its forward instruction and the backward keys of its
+    backward instruction."""
+    cp = mode == "cp"
+    fk = FWD_KEYS_CP if cp else FWD_KEYS_TP
+    bk = BWD_KEYS_CP if cp else BWD_KEYS_TP
+    by_mb: Dict[int, Dict[str, object]] = {mb: {k: None for k in fk + bk} for mb in range(num_mbs)}
+    for inst in stage_instructions:
+        d = _sched_item(inst.kind, inst.assigned_knob, mode).as_dict()
+        for k in (fk if inst.kind == "forward" else bk):
+            by_mb[inst.micro_batch][k] = d[k]
+    return [ScheduleItem("both", tuple(by_mb[mb].items()), cp) for mb in range(num_mbs)]
+
+
 def run_optimization(inst_profile, output_dir, num_stages: int, num_mbs: int, gpu_type: str = "B200",
                      unit_time: float = 1e-3, noise_factor: float = 0.9, use_activation_checkpointing: bool = True,
                      p2p_power: Optional[float] = None, max_iterations: Optional[int] = None,
@@ -104,10 +118,13 @@ def run_optimization(inst_profile, output_dir, num_stages: int, num_mbs: int, gp
                        total_cost_p2p=real_cost)
         (out / f"freqs_pipeline_{res.iteration:05d}.py").write_text(emit_freqs_text(freqs, **trailer))
         if mode != "freq":
-            if not use_activation_checkpointing:
-                raise NotImplementedError("the pair layout is emitted by emit_schedule_text for parsed plans only")
-            items = [[_sched_item(i.kind, i.assigned_knob, mode) for i in st] for st in stages]
+            if use_activation_checkpointing:
+                items = [[_sched_item(i.kind, i.assigned_knob, mode) for i in st] for st in stages]
+            else:
+                # without recompute a plan lists, per stage, one (forward, backward) pair per microbatch
+                # (writer in the reference: tests/kareus/run_optimization.py:205-252, 297-333)
+                items = [_pair_items(st, num_mbs, mode) for st in stages]
             (out / f"scheds_pipeline_{res.iteration:05d}.py").write_text(
-                emit_schedule_text(items, True, **trailer))
+                emit_schedule_text(items, use_activation_checkpointing, **trailer))
     log.close()
     return summary

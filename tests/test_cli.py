@@ -160,3 +160,25 @@ def test_small_frontiers_keep_the_max_throughput_plan():
     for n in (1, 2, 3, 5, 7, 9):
         got = sample_frontier(names[:n])
         assert got and got[-1] == names[n - 1], (n, got)
+
+
+def _noac_worker(rank, world, out):
+    """Two nanobatches, no activation recompute: train under a plan in the per-microbatch pair layout."""
+    import torch.distributed as dist
+    from kareus_b200.cli import run_train
+    from kareus_b200.plan.schedule import DEFAULT_CONFIG, ScheduleItem, emit_schedule_text, FWD_KEYS_TP, BWD_KEYS_TP
+    plan = out + "/scheds_pipeline_00001.py"
+    if rank == 0:
+        item = ScheduleItem("both", tuple((k, DEFAULT_CONFIG) for k in FWD_KEYS_TP + BWD_KEYS_TP), False)
+        with open(plan, "w") as f:
+            f.write(emit_schedule_text([[item, item]], False, 1, 0.0, 1.0, 2.0))
+    dist.barrier()
+    rc = run_train.main(["--method", "kareus", "--model", "tiny", "--tp", "2", "--mbs", "4", "--gbs", "8", "--seq", "32",
+                         "--steps", "2", "--tp-comm", "allreduce", "--scheds", plan, "--no-recompute", "--out",
+                         out + "/runs", "--keep-process-group"])
+    assert rc == 0
+
+
+def test_training_without_recompute_under_a_pair_layout_plan(tmp_path):
+    from dist_utils import run_distributed
+    run_distributed(_noac_worker, 2, str(tmp_path), timeout=300.0)

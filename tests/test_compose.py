@@ -157,6 +157,23 @@ def test_driver_writes_compatible_plan_files(tmp_path):
     assert len(kept) == 10 and kept[-1] == names[-1]
     fr = frontier_from_plans(out, 2, 190.0)
     assert len(fr) == 60 and fr[0][0] > fr[-1][0]
+    # the same logs planned for a run WITHOUT activation recompute: the profile drops the recompute columns and
+    # the plan lists one (forward, backward) pair per microbatch and stage
+    csv2 = generate_profile_csv("llama3.2_3b", 8, 1, 2, 8, 4096, bayesian_profile_dir=str(tmp_path / "bo"),
+                                output_dir=str(tmp_path / "noac"), gpu_type="B200", use_activation_checkpointing=False)
+    assert csv2.read_text().splitlines()[0] == "stage,instruction,frequency,attention_configs,mlp_configs,time,energy"
+    out2 = tmp_path / "lowtime_noac"
+    run_optimization(csv2, out2, num_stages=2, num_mbs=8, gpu_type="B200", use_native=False, max_iterations=5,
+                     use_activation_checkpointing=False)
+    text = (out2 / "scheds_pipeline_00004.py").read_text()
+    pairs = parse_schedule_file(out2 / "scheds_pipeline_00004.py", False, False)
+    assert len(pairs) == 2 and len(pairs[0]) == 8 and pairs[0][0].kind == "both" and "(('forward'," in text
+    s2 = PipelineCommScheduler.from_parsed(pairs, 0, 8, use_activation_checkpointing=False)
+    s2.on_instruction_begin("forward")
+    assert s2.current_schedule.get("fwd_mlp").block_size == 1024
+    s2.on_instruction_end("forward")
+    s2.on_instruction_begin("backward")
+    assert s2.current_schedule.get("bwd_attn") is not None
 
 
 def test_compare_methods(tmp_path):

@@ -182,3 +182,43 @@ def _noac_worker(rank, world, out):
 def test_training_without_recompute_under_a_pair_layout_plan(tmp_path):
     from dist_utils import run_distributed
     run_distributed(_noac_worker, 2, str(tmp_path), timeout=300.0)
+
+
+def test_plan_server_process_serves_a_training_run(tmp_path, capsys):
+    """The stand-alone plan server (environment of the reference's drivers) hands the clocks of a plan file to a
+    training run that only knows its URL."""
+    import json
+    import os
+    import socket
+    import subprocess
+    import sys
+    import time
+    import urllib.request
+    from kareus_b200.cli import run_train
+    from kareus_b200.plan.freqs import emit_freqs_text
+    plan = tmp_path / "freqs_pipeline_00007.py"
+    plan.write_text(emit_freqs_text([[("forward", 1500), ("backward", 1200), ("forward", 1500), ("backward", 1200)]],
+                                    iteration=7, cost_change=0.0, total_cost=1.0, total_cost_p2p=2.0))
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    env = dict(os.environ, PFO_PORT=str(port), ZEUS_PFO_SCHEDULER_ARGS=json.dumps({"solution_path": str(plan)}))
+    proc = subprocess.Popen([sys.executable, "-m", "kareus_b200.cli.pfo_server", "--once-after", "60"], env=env,
+                            stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    try:
+        url = f"http://127.0.0.1:{port}"
+        for _ in range(100):
+            try:
+                with urllib.request.urlopen(url + "/health", timeout=1) as r:
+                    assert json.loads(r.read())["stages"] == 1
+                break
+            except OSError:
+                time.sleep(0.1)
+        else:
+            raise AssertionError("the plan server did not come up")
+        rc = run_train.main(["--method", "perseus", "--model", "tiny", "--mbs", "2", "--gbs", "4", "--seq", "32", "--steps",
+                             "2", "--pfo-url", url, "--out", str(tmp_path / "runs"), "--keep-process-group"])
+        assert rc == 0 and "step 1 loss" in capsys.readouterr().out
+    finally:
+        proc.terminate()
+        proc.wait(timeout=10)

@@ -60,8 +60,14 @@ def main(argv=None) -> int:
         summary = run_optimization(csv_path, plans, a.pp, num_mbs, a.gpu_type, max_iterations=a.max_iterations,
                                    use_activation_checkpointing=not a.no_recompute)
         print(f"planned {len(summary)} frontier points: T {summary[0]['time_s']:.3f}s → {summary[-1]['time_s']:.3f}s")
-        if a.frontier:
-            create_frontier(plans, plans / "frontier")
+    if rank == 0 and a.frontier:
+        have = list((plans / "frontier").glob("*_pipeline_*.py"))
+        if not a.skip_planning:
+            for p in have:                                # samples of an earlier planning run
+                p.unlink()
+            have = []
+        if not have:
+            create_frontier(plans, plans / "frontier")   # also after --skip-planning, from the plans already there
     if world > 1:
         dist.barrier()
     chosen = []
@@ -71,12 +77,13 @@ def main(argv=None) -> int:
         chosen = [select_max_throughput([p.name for p in plans.glob("freqs_pipeline_*.py")])]
     for name in chosen:
         src = (plans / "frontier" / name) if a.frontier else (plans / name)
-        out = str(Path(a.workdir)) if not a.frontier else str(base / "frontier" / name[len("freqs_"):-3])
+        # one run directory per sampled plan: <method>/frontier/pipeline_NNNNN/zeus_monitor_*.txt
+        run_dir = str(base / "frontier" / name[len("freqs_"):-3]) if a.frontier else None
         argv2 = ["--method", "kareus", "--model", a.model, "--tp", str(a.tp), "--cp", str(a.cp), "--pp", str(a.pp),
                  "--mbs", str(a.mbs), "--gbs", str(a.gbs), "--seq", str(a.seq), "--steps", str(a.steps),
                  "--freqs", str(src), "--scheds", str(src.parent / name.replace("freqs", "scheds")),
-                 "--clock-mode", a.clock_mode, "--tp-comm", a.tp_comm, "--comm-backend", a.comm_backend, "--out", out,
-                 "--keep-process-group"] + (["--no-recompute"] if a.no_recompute else [])
+                 "--clock-mode", a.clock_mode, "--tp-comm", a.tp_comm, "--comm-backend", a.comm_backend,
+                 "--out", str(Path(a.workdir)), "--keep-process-group"] + (["--run-dir", run_dir] if run_dir else []) + (["--no-recompute"] if a.no_recompute else [])
         run_train.main(argv2)
     if world > 1:
         dist.barrier()

@@ -41,6 +41,9 @@ def main(argv=None) -> int:
     ap.add_argument("--pfo-url", default=None, help="http://MASTER_ADDR:7787 of a running plan server")
     ap.add_argument("--clock-mode", default="advisory", choices=["off", "advisory", "locked"])
     ap.add_argument("--out", default="nemo_experiments")
+    ap.add_argument("--run-dir", default=None,
+                    help="write this run's files exactly here instead of <out>/<model>/<layout>/<method> "
+                         "(frontier runs: <method>/frontier/pipeline_NNNNN)")
     ap.add_argument("--enable-power-monitor", action="store_true")
     ap.add_argument("--enable-timers", action="store_true")
     ap.add_argument("--recompute-layers", type=int, default=4)
@@ -91,7 +94,7 @@ def main(argv=None) -> int:
     tc = TrainConfig(micro_batch_size=a.mbs, global_batch_size=a.gbs, seq_len=a.seq,
                      dtype="bf16" if cuda else "fp32")
     tag = f"cp{a.cp}_tp{a.tp}_mbs{a.mbs}_seq{a.seq}"
-    out = Path(a.out) / a.model / tag / a.method
+    out = Path(a.run_dir) if a.run_dir else Path(a.out) / a.model / tag / a.method
     out.mkdir(parents=True, exist_ok=True)
     # without a GPU the windows are still written, against the simulated NVML (the flow of drivers, the
     # comparison tool and the tests need the files; the joules then mean nothing)

@@ -96,6 +96,14 @@ def test_run_kareus_end_to_end_cpu(tmp_path, capsys):
     assert "planned 12 frontier points" in out and "step 1 loss" in out
     plans = tmp_path / "exp" / "tiny" / "cp1_tp1_mbs2_seq32" / "kareus" / "lowtime"
     assert (plans / "freqs_pipeline_00011.py").exists() and (plans / "scheds_pipeline_00011.py").exists()
+    # frontier mode: one run per sampled plan, each in <method>/frontier/pipeline_NNNNN/
+    rc = run_kareus.main(["--model", "tiny", "--mbs", "2", "--gbs", "4", "--seq", "32", "--steps", "2",
+                          "--bayesian-dir", str(tmp_path / "bo"), "--workdir", str(tmp_path / "exp"),
+                          "--skip-planning", "--frontier", "--comm-backend", "nccl"])
+    assert rc == 0
+    runs = sorted((tmp_path / "exp" / "tiny" / "cp1_tp1_mbs2_seq32" / "kareus" / "frontier").iterdir())
+    assert runs and all(r.name.startswith("pipeline_") for r in runs)
+    assert all((r / "zeus_monitor_global_rank-0_local_rank-0.txt").exists() for r in runs)
 
 
 def test_pretrain_from_yaml(tmp_path, capsys):

@@ -93,6 +93,31 @@ class Channel:
         return self.counter.value
 
 
+def node_identity() -> str:
+    """Something that is equal for two processes exactly when they run on the same machine."""
+    import socket
+    boot = ""
+    try:
+        with open("/proc/sys/kernel/random/boot_id") as f:
+            boot = f.read().strip()
+    except OSError:
+        pass
+    return f"{socket.gethostname()}/{boot}"
+
+
+def require_one_node(group, world: int) -> None:
+    """Peer mappings (CUDA IPC) exist between GPUs of one machine only: the ranks of a heap — a tensor- or
+    context-parallel group — must not span nodes (put pipeline and data parallelism across nodes instead, as
+    the reference's launch scripts do).  Collective over ``group``."""
+    if world <= 1 or not dist.is_initialized():
+        return
+    ids = [None] * world
+    dist.all_gather_object(ids, node_identity(), group=group)
+    if len(set(ids)) > 1:
+        raise RuntimeError(f"the {world} ranks of this peer-memory group run on {len(set(ids))} different machines; "
+                           "tensor/context-parallel groups that use the kernel backend must stay inside one node")
+
+
 class SymmetricHeap:
     def __init__(self, group, rank: int, world: int, device, size_bytes: int):
         self.group, self.rank, self.world = group, rank, world
@@ -137,6 +162,7 @@ class SymmetricHeap:
         world = dist.get_world_size(group) if dist.is_initialized() else 1
         if world > MAX_PEERS:
             raise ValueError(f"at most {MAX_PEERS} ranks per heap")
+        require_one_node(group, world)
         return cls(group, rank, world, device, size_bytes)
 
     def _declare(self) -> None:

@@ -188,3 +188,21 @@ def test_guard_words_between_heap_buffers_name_the_overrun():
     assert g.check(heap) == []
     heap[6144 + 2048 + 5] = 1                       # one byte past the end of buffer 1
     assert g.check(heap) == ["buffer 1"]
+
+
+def _node_worker(rank, world):
+    from kareus_b200.parallel import symm_heap
+    import pytest as _pytest
+    symm_heap.require_one_node(None, world)                       # both ranks on this machine: fine
+    real = symm_heap.node_identity
+    symm_heap.node_identity = lambda: f"node{rank}/boot"          # pretend the ranks sit on two machines
+    try:
+        with _pytest.raises(RuntimeError, match="different machines"):
+            symm_heap.require_one_node(None, world)
+    finally:
+        symm_heap.node_identity = real
+
+
+def test_peer_memory_groups_must_stay_inside_one_node():
+    from dist_utils import run_distributed
+    run_distributed(_node_worker, 2)

@@ -256,3 +256,64 @@ def test_fused_path_partitions_fold_into_the_reference_keys():
     assert got[("attn_0", "none", 16, 1024)] == (0.9 + 0.4, 11.0 + 6.0)          # child's faster point at sm 16
     assert ("attn_0", "none", 32, 1024) not in got                                # child never measured at 32
     assert out["fwd_mlp"] == maps["fwd_mlp"]                                      # no child logs: unchanged
+
+
+def _fake_run(d, times, energies, ranks=2):
+    d.mkdir(parents=True, exist_ok=True)
+    for r in range(ranks):
+        with (d / f"zeus_monitor_global_rank-{r}_local_rank-{r}.txt").open("w") as f:
+            f.write("start_time,window_name,elapsed_time,gpu0_energy\n")
+            for t, e in zip(times, energies):
+                f.write(f"0.0,training_step_fwd_bwd_step_call,{t},{e / ranks}\n")
+
+
+def test_results_tree_tables_and_measured_frontiers(tmp_path):
+    """The comparison over a whole results tree: per configuration every method against the one-nanobatch run,
+    and the measured frontier runs of each method against the frequency-only method's frontier."""
+    from kareus_b200.compose.compare import format_table, iso_reductions, load_frontier_runs, results_table
+    cfg = tmp_path / "llama3.2_3b" / "cp1_tp8_mbs8_seq4096"
+    _fake_run(cfg / "megatron", [1.0] * 4, [1000.0] * 4)
+    _fake_run(cfg / "perseus", [1.0] * 4, [900.0] * 4)
+    _fake_run(cfg / "kareus", [0.8] * 4, [700.0] * 4)
+    (tmp_path / "llama3.2_3b" / "notes").mkdir()                      # not a layout directory: ignored
+    rows = results_table(tmp_path, skip=1, take=3)
+    assert rows[0][:2] == ["model", "layout"] and len(rows) == 2
+    line = dict(zip(rows[0], rows[1]))
+    assert line["kareus time"] == "+20.0%" and line["kareus energy"] == "+30.0%" and line["perseus energy"] == "+10.0%"
+    assert line["nanobatch_perseus time"] == "n/a"
+    assert format_table(rows).splitlines()[1].startswith("|---|")
+    # measured frontiers: perseus spans (1.0 s, 900 J) .. (1.3 s, 700 J)
+    for i, (t, e) in enumerate([(1.0, 900.0), (1.15, 780.0), (1.3, 700.0)]):
+        _fake_run(cfg / "perseus" / "frontier" / f"pipeline_{i:05d}", [t] * 4, [e] * 4)
+    for i, (t, e) in enumerate([(0.8, 800.0), (0.95, 650.0), (1.2, 600.0)]):
+        _fake_run(cfg / "kareus" / "frontier" / f"pipeline_{i:05d}", [t] * 4, [e] * 4)
+    ref = load_frontier_runs(cfg / "perseus", 1, 3)
+    ours = load_frontier_runs(cfg / "kareus", 1, 3, expected=3)
+    r = iso_reductions(ours, ref)
+    # as fast as perseus' fastest run (1.0 s): kareus' cheapest such run uses 650 J instead of 900 J
+    assert abs(r["iso_time_energy_reduction_pct"] - 100 * (900 - 650) / 900) < 1e-9
+    # no more energy than perseus' most frugal run (700 J): kareus' fastest such run takes 0.95 s instead of 1.3 s
+    assert abs(r["iso_energy_time_reduction_pct"] - 100 * (1.3 - 0.95) / 1.3) < 1e-9
+    rows = results_table(tmp_path, 1, 3, frontier=True)
+    line = dict(zip(rows[0], rows[1]))
+    assert line["kareus iso-time energy"] == "+27.8%" and line["nanobatch_perseus iso-energy time"] == "n/a"
+    import pytest
+    with pytest.raises(ValueError):
+        load_frontier_runs(cfg / "kareus", 1, 3, expected=10)
+
+
+def test_frontier_runner_trains_under_every_sampled_plan(tmp_path):
+    from kareus_b200.cli import compare, run_frontier
+    from kareus_b200.plan.freqs import emit_freqs_text
+    plans = tmp_path / "plans"
+    plans.mkdir()
+    for i, f in enumerate([900, 1200, 1500]):
+        (plans / f"freqs_pipeline_{i:05d}.py").write_text(
+            emit_freqs_text([[("forward", f), ("backward", f), ("forward", f), ("backward", f)]], iteration=i,
+                            cost_change=0.0, total_cost=1.0, total_cost_p2p=2.0))
+    rc = run_frontier.main(["--method", "perseus", "--plans-dir", str(plans), "--model", "tiny", "--mbs", "2", "--gbs",
+                            "4", "--seq", "32", "--steps", "3", "--out", str(tmp_path / "exp"), "--comm-backend", "nccl"])
+    assert rc == 0
+    runs = sorted((tmp_path / "exp" / "tiny" / "cp1_tp1_mbs2_seq32" / "perseus" / "frontier").iterdir())
+    assert [r.name for r in runs] == ["pipeline_00001", "pipeline_00002"]          # positions 0 dropped, last kept
+    assert compare.main(["--root", str(tmp_path / "exp"), "--frontier", "--skip", "1", "--take", "2"]) == 0

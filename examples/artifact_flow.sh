@@ -15,7 +15,7 @@ MODEL=${MODEL:-llama3.2_3b}; NPROC=${NPROC:-8}; TP=${TP:-$NPROC}; PP=${PP:-1}; C
 MBS=${MBS:-8}; GBS=${GBS:-64}; SEQ=${SEQ:-4096}; STEPS=${STEPS:-30}
 WORK=${WORK:-kareus_runs}; GPU_TYPE=${GPU_TYPE:-B200}; CLOCK_MODE=${CLOCK_MODE:-advisory}
 TP_COMM=${TP_COMM:-sp_fused}; MASTER_PORT=${MASTER_PORT:-6000}; QUICK=${QUICK:-0}
-SKIP_PROFILING=${SKIP_PROFILING:-false}
+SKIP_PROFILING=${SKIP_PROFILING:-false}; FRONTIER=${FRONTIER:-false}
 PERSEUS_METHODS=${PERSEUS_METHODS:-"perseus nanobatch_perseus"}      # frequency-only plans: one / two nanobatches
 # with context parallelism the partition plan covers the all-reduce flavour of tensor parallelism
 [ "$CP" -gt 1 ] && TP_COMM=allreduce
@@ -25,12 +25,13 @@ RUN="python -m torch.distributed.run --nnodes=1 --nproc-per-node ${NPROC} --mast
 NPROF=$((TP * CP))
 RUNP="python -m torch.distributed.run --nnodes=1 --nproc-per-node ${NPROF} --master-addr 127.0.0.1 --master-port ${MASTER_PORT}"
 DP=$((NPROC / (TP * CP * PP))); NUM_MBS=$((GBS / (MBS * DP)))
+COMM_BACKEND=kernel
 if [ "$QUICK" = "1" ]; then      # a few configurations per partition, short measurements
   BO_ARGS="--n-init 3 --batches 1 --acq-batch 1 --measure-s 0.05 --cooldown-s 0 --freqs 1500 1200"
   PERSEUS_ARGS="--freqs 1500 1200 --steps 2 --skip 1"; SKIP=1; TAKE=$((STEPS - 1)); MAXIT="--max-iterations 30"
   if [ "$(python -c 'import torch; print(int(torch.cuda.is_available()))')" = "0" ]; then
     [ "$TP_COMM" = "sp_fused" ] && TP_COMM=sp          # the fused kernels need GPUs
-    BO_ARGS="$BO_ARGS --comm-backend nccl"
+    BO_ARGS="$BO_ARGS --comm-backend nccl"; COMM_BACKEND=nccl
   fi
 else
   BO_ARGS=""; PERSEUS_ARGS=""; SKIP=10; TAKE=20; MAXIT=""
@@ -73,6 +74,11 @@ for METHOD in $PERSEUS_METHODS; do
       --gbs "$GBS" --seq "$SEQ" --steps "$STEPS" --tp-comm "$TP_COMM" --clock-mode "$CLOCK_MODE" --freqs "$FREQS" \
       --out "$WORK/runs"
   COMPARE="$COMPARE $WORK/runs/$MODEL/$TAG/$METHOD"
+  if [ "$FRONTIER" = "true" ]; then     # one more run per sampled plan: <method>/frontier/pipeline_NNNNN
+    $RUN -m kareus_b200.cli.run_frontier --method $METHOD --plans-dir "$WORK/${METHOD}_plans" --model "$MODEL" --tp "$TP" \
+        --pp "$PP" --cp "$CP" --mbs "$MBS" --gbs "$GBS" --seq "$SEQ" --steps "$STEPS" --tp-comm "$TP_COMM" \
+        --comm-backend "$COMM_BACKEND" --clock-mode "$CLOCK_MODE" --out "$WORK/runs"
+  fi
 done
 if [ "$TP" -gt 1 ]; then
   echo "== 4b. compose the partition frontiers, plan, train under the max-throughput plan"
@@ -85,3 +91,8 @@ fi
 echo "== 5. energy and time of each method against the one-nanobatch baseline"
 python -m kareus_b200.cli.compare --base "$WORK/runs/$MODEL/$TAG/megatron" --runs $COMPARE --skip "$SKIP" --take "$TAKE" \
     --num_stages "$PP" --gpu_type "$GPU_TYPE"
+python -m kareus_b200.cli.compare --root "$WORK/runs" --skip "$SKIP" --take "$TAKE"
+if [ "$FRONTIER" = "true" ]; then
+  echo "== 6. measured frontiers against the frequency-only frontier"
+  python -m kareus_b200.cli.compare --root "$WORK/runs" --frontier --skip "$SKIP" --take "$TAKE"
+fi

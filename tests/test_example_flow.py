@@ -8,6 +8,14 @@ from pathlib import Path
 import pytest
 
 ROOT = Path(__file__).resolve().parents[1]
+
+
+def _free_port() -> str:
+    import socket
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return str(s.getsockname()[1])
+
 # the two-rank tensor-parallel flow always runs; the other layouts take another minute each
 long_tests = pytest.mark.skipif(os.environ.get("KAREUS_LONG_TESTS", "0") != "1",
                                 reason="set KAREUS_LONG_TESTS=1 for the pipeline-only and TP x CP flows")
@@ -15,7 +23,7 @@ long_tests = pytest.mark.skipif(os.environ.get("KAREUS_LONG_TESTS", "0") != "1",
 
 def test_artifact_flow_on_two_cpu_ranks(tmp_path):
     env = dict(os.environ, NPROC="2", TP="2", MODEL="tiny", SEQ="32", MBS="4", GBS="8", STEPS="4", QUICK="1",
-               WORK=str(tmp_path / "w"), MASTER_PORT="29961", CUDA_VISIBLE_DEVICES="")
+               WORK=str(tmp_path / "w"), MASTER_PORT=_free_port(), CUDA_VISIBLE_DEVICES="")
     r = subprocess.run(["bash", str(ROOT / "examples" / "artifact_flow.sh")], cwd=ROOT, env=env, capture_output=True,
                        text=True, timeout=900)
     assert r.returncode == 0, r.stdout[-3000:] + "\n" + r.stderr[-3000:]
@@ -34,7 +42,7 @@ def test_artifact_flow_with_pipeline_stages_only(tmp_path):
     """Two pipeline stages, no tensor parallelism: nothing to profile per partition, the frequency-only plan is
     the whole story."""
     env = dict(os.environ, NPROC="2", TP="1", PP="2", MODEL="tiny", SEQ="32", MBS="2", GBS="8", STEPS="4", QUICK="1",
-               WORK=str(tmp_path / "w"), MASTER_PORT="29963", CUDA_VISIBLE_DEVICES="")
+               WORK=str(tmp_path / "w"), MASTER_PORT=_free_port(), CUDA_VISIBLE_DEVICES="")
     r = subprocess.run(["bash", str(ROOT / "examples" / "artifact_flow.sh")], cwd=ROOT, env=env, capture_output=True,
                        text=True, timeout=900)
     assert r.returncode == 0, r.stdout[-3000:] + "\n" + r.stderr[-3000:]
@@ -48,7 +56,7 @@ def test_artifact_flow_with_tensor_and_context_parallelism(tmp_path):
     """TP2 x CP2 on four ranks: the twelve context-parallel partitions are profiled, composed into the
     context-parallel profile CSV, planned, and the run executes the 5 + 12 entry plan."""
     env = dict(os.environ, NPROC="4", TP="2", CP="2", MODEL="tiny", SEQ="64", MBS="2", GBS="4", STEPS="4", QUICK="1",
-               WORK=str(tmp_path / "w"), MASTER_PORT="29965", CUDA_VISIBLE_DEVICES="")
+               WORK=str(tmp_path / "w"), MASTER_PORT=_free_port(), CUDA_VISIBLE_DEVICES="")
     r = subprocess.run(["bash", str(ROOT / "examples" / "artifact_flow.sh")], cwd=ROOT, env=env, capture_output=True,
                        text=True, timeout=1200)
     assert r.returncode == 0, r.stdout[-3000:] + "\n" + r.stderr[-3000:]

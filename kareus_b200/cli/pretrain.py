@@ -60,8 +60,10 @@ def main(argv=None) -> int:
         argv2.append("--no-recompute")
     if sw.data_prefix:
         from pathlib import Path
-        if Path(sw.data_prefix + ".idx").exists():
-            argv2 += ["--data-path", sw.data_prefix, "--data-split", sw.data_split, "--data-seed", str(train.seed)]
+        blend = list(sw.data_blend) if len(sw.data_blend) > 2 else [sw.data_prefix]
+        prefixes = blend[1::2] if len(blend) > 1 else blend
+        if all(Path(p + ".idx").exists() for p in prefixes):
+            argv2 += ["--data-path", *blend, "--data-split", sw.data_split, "--data-seed", str(train.seed)]
             if sw.eod_mask_loss and a.eod_token is not None:
                 argv2 += ["--eod-token", str(a.eod_token)]
         else:

@@ -54,8 +54,9 @@ def main(argv=None) -> int:
                     help="open the CUDA profiler capture range at this step (nsys --capture-range=cudaProfilerApi)")
     ap.add_argument("--profile-end-step", type=int, default=None)
     ap.add_argument("--profile-ranks", type=int, nargs="*", default=[0])
-    ap.add_argument("--data-path", default=None,
-                    help="prefix of a Megatron-format indexed token file (<prefix>.bin/.idx); default: synthetic tokens")
+    ap.add_argument("--data-path", default=None, nargs="+",
+                    help="prefix of a Megatron-format indexed token file (<prefix>.bin/.idx), or a weighted blend "
+                         "`w0 prefix0 w1 prefix1 ...`; default: synthetic tokens")
     ap.add_argument("--data-split", default="949,50,1", help="train,validation,test weights over the documents")
     ap.add_argument("--data-seed", type=int, default=1234)
     ap.add_argument("--eod-token", type=int, default=None, help="mask the loss on this end-of-document token")
@@ -144,26 +145,43 @@ def main(argv=None) -> int:
             print(f"resumed from {a.load} at step {first}", flush=True)
     batches = None
     if a.data_path:
-        from ..data import GPTDataset, GPTDatasetConfig, IndexedDataset, PretrainingBatches, split_documents
-        tokens = IndexedDataset(a.data_path)
-        train_docs = split_documents(tokens.num_documents, [float(w) for w in a.data_split.split(",")])[0]
-        ds = GPTDataset(tokens, GPTDatasetConfig(seq_len=a.seq, num_samples=a.steps * a.gbs, seed=a.data_seed,
-                                                 documents=train_docs, eod_token=a.eod_token,
-                                                 vocab_size=cfg.vocab_size))
+        from ..data import (BlendedDataset, GPTDataset, GPTDatasetConfig, IndexedDataset, PretrainingBatches,
+                            split_documents)
+        if len(a.data_path) == 1:
+            weights, prefixes = [1.0], list(a.data_path)
+        elif len(a.data_path) % 2 == 0:
+            weights = [float(w) for w in a.data_path[0::2]]
+            prefixes = list(a.data_path[1::2])
+        else:
+            raise SystemExit("--data-path takes one prefix or pairs `weight prefix`")
+        files = [IndexedDataset(p) for p in prefixes]
+        split_w = [float(w) for w in a.data_split.split(",")]
+
+        def make_split(part: int, num_samples: int, shuffle: bool = True):
+            """Blend of the given share (0 train, 1 validation) of every file's documents."""
+            def one(d: int, n: int):
+                docs = split_documents(files[d].num_documents, split_w)[part]
+                return GPTDataset(files[d], GPTDatasetConfig(seq_len=a.seq, num_samples=n, seed=a.data_seed + d,
+                                                             documents=docs, eod_token=a.eod_token,
+                                                             vocab_size=cfg.vocab_size, shuffle_samples=shuffle))
+            if len(files) == 1:
+                return one(0, num_samples)
+            return BlendedDataset(weights, one, num_samples)
+
+        tokens = files[0]
+        ds = make_split(0, a.steps * a.gbs)
         # the run resumes at the sample where the checkpointed step count left off
         batches = PretrainingBatches(ds, a.mbs, M, dp_rank=mesh.dp_rank, dp_size=dp, consumed_samples=first * a.gbs,
                                      cp=a.cp, cp_rank=mesh.cp_rank)
         if rank == 0:
-            print(f"data: {a.data_path}: {tokens.num_documents} documents, {tokens.num_tokens} tokens, "
-                  f"{ds.num_epochs} epoch(s) for {a.steps} steps", flush=True)
+            for p, f_ in zip(prefixes, files):
+                print(f"data: {p}: {f_.num_documents} documents, {f_.num_tokens} tokens", flush=True)
     val_ds = None
     if a.data_path and a.eval_interval > 0:
-        val_docs = split_documents(tokens.num_documents, [float(w) for w in a.data_split.split(",")])[1]
-        if val_docs[1] > val_docs[0]:
+        if all(split_documents(f_.num_documents, split_w)[1][1] > split_documents(f_.num_documents, split_w)[1][0]
+               for f_ in files):
             # the same held-out batches at every evaluation, in file order
-            val_ds = GPTDataset(tokens, GPTDatasetConfig(seq_len=a.seq, num_samples=a.eval_iters * a.gbs, seed=a.data_seed,
-                                                         documents=val_docs, eod_token=a.eod_token,
-                                                         vocab_size=cfg.vocab_size, shuffle_samples=False))
+            val_ds = make_split(1, a.eval_iters * a.gbs, shuffle=False)
         elif rank == 0:
             print("the validation share of --data-split is empty: evaluating on synthetic tokens", flush=True)
 

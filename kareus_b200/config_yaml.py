@@ -35,6 +35,7 @@ class RunSwitches:
     nsys_ranks: Tuple[int, ...] = (0,)
     # model.data.{data_prefix,splits_string,eod_mask_loss}: the (first) indexed token file of the blend
     data_prefix: Optional[str] = None
+    data_blend: Tuple[str, ...] = ()       # the whole blend as `--data-path` takes it: (w0, prefix0, w1, prefix1, ...)
     data_split: str = "900,50,50"
     eod_mask_loss: bool = False
 
@@ -121,8 +122,10 @@ def load_run_config(path, overrides: Iterable[str] = (), world_size: Optional[in
     data = m.get("data") or {}
     prefix = data.get("data_prefix")
     if isinstance(prefix, (list, tuple)):
-        # a blend is written [weight, prefix, weight, prefix, ...]; this runtime reads its first file
+        # a blend is written [weight, prefix, weight, prefix, ...]
         paths = [p for p in prefix if isinstance(p, str)]
+        if len(prefix) == 2 * len(paths) and paths:
+            sw.data_blend = tuple(str(x) for x in prefix)
         prefix = paths[0] if paths else None
     if isinstance(prefix, dict):
         train_part = prefix.get("train")

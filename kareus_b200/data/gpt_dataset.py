@@ -148,3 +148,56 @@ class GPTDataset(torch.utils.data.Dataset):
         if self.cfg.eod_token is not None:
             mask[tokens == self.cfg.eod_token] = 0.0
         return {"tokens": tokens, "labels": labels, "loss_mask": mask}
+
+
+def build_blend_index(weights: Sequence[float], num_samples: int, native: Optional[bool] = None):
+    """``(dataset of sample i, index of that sample inside its dataset)`` for a weighted blend: every sample goes
+    to the dataset that is furthest behind its share.  Native when the kernel library is built."""
+    w = np.asarray(weights, dtype=np.float64)
+    if w.ndim != 1 or len(w) == 0 or (w < 0).any() or w.sum() <= 0:
+        raise ValueError(f"bad blend weights {weights}")
+    w = np.ascontiguousarray(w / w.sum())
+    ds = np.empty(num_samples, dtype=np.int16)
+    pos = np.empty(num_samples, dtype=np.int64)
+    lib = None
+    if native is not False:
+        try:
+            from ..kernels import build as _build
+            if _build.LIB.exists():
+                lib = ctypes.CDLL(str(_build.LIB))
+                lib.kb_build_blend_index.restype = ctypes.c_int
+        except (OSError, AttributeError):
+            lib = None
+        if lib is None and native:
+            raise RuntimeError("the native library is not built (python -m kareus_b200.kernels.build)")
+    if lib is not None:
+        P = ctypes.c_void_p
+        rc = lib.kb_build_blend_index(P(w.ctypes.data), ctypes.c_int(len(w)), ctypes.c_int64(num_samples),
+                                      P(ds.ctypes.data), P(pos.ctypes.data))
+        if rc:
+            raise ValueError(f"bad arguments to the blend index builder (code {rc})")
+        return ds, pos
+    taken = np.zeros(len(w), dtype=np.int64)
+    for i in range(num_samples):
+        d = int(np.argmax(w * (i + 1) - taken))
+        ds[i], pos[i] = d, taken[d]
+        taken[d] += 1
+    return ds, pos
+
+
+class BlendedDataset(torch.utils.data.Dataset):
+    """Weighted mix of GPT datasets (``model.data.data_prefix: [w0, prefix0, w1, prefix1, ...]`` of the
+    reference's run configs; Megatron's ``BlendedDataset``).  ``make(d, n)`` builds dataset ``d`` with room for
+    ``n`` samples; each one is asked for as many samples as the blend takes from it."""
+
+    def __init__(self, weights: Sequence[float], make, num_samples: int, native: Optional[bool] = None):
+        self.ds_index, self.pos_index = build_blend_index(weights, num_samples, native)
+        counts = np.bincount(self.ds_index, minlength=len(weights))
+        self.datasets = [make(d, int(c)) if c > 0 else None for d, c in enumerate(counts)]
+        self.num_samples = num_samples
+
+    def __len__(self) -> int:
+        return self.num_samples
+
+    def __getitem__(self, i: int):
+        return self.datasets[int(self.ds_index[i])][int(self.pos_index[i])]

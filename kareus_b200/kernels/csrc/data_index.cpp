@@ -41,3 +41,28 @@ extern "C" int kb_build_sample_index(const int64_t* doc_len, const int64_t* doc_
   }
   return 0;
 }
+
+// Blend of several datasets: sample i of the blend comes from the dataset that is furthest behind its share
+// (largest weight[d] * (i + 1) - taken[d]); out_ds[i] is that dataset and out_pos[i] how many samples it had
+// given before.  Deterministic, and every prefix of the blend holds each dataset within one sample of its
+// share.  Same role as Megatron's build_blending_indices (megatron/core/datasets/helpers.cpp).
+extern "C" int kb_build_blend_index(const double* weights, int n_ds, int64_t n, int16_t* out_ds, int64_t* out_pos) {
+  if (n_ds <= 0 || n_ds > 32767 || n < 0) return 7;
+  int64_t taken[64];
+  if (n_ds > 64) return 7;
+  for (int d = 0; d < n_ds; ++d) taken[d] = 0;
+  for (int64_t i = 0; i < n; ++i) {
+    int best = 0;
+    double best_err = -1e300;
+    for (int d = 0; d < n_ds; ++d) {
+      const double err = weights[d] * static_cast<double>(i + 1) - static_cast<double>(taken[d]);
+      if (err > best_err) {
+        best_err = err;
+        best = d;
+      }
+    }
+    out_ds[i] = static_cast<int16_t>(best);
+    out_pos[i] = taken[best]++;
+  }
+  return 0;
+}

@@ -249,3 +249,42 @@ def test_metrics_log(tmp_path):
     assert [r["step"] for r in steps] == [0, 1, 2] and steps[-1]["consumed_samples"] == 12
     assert all(r["grad_norm"] > 0 and r["lr"] > 0 and r["tokens_per_s"] > 0 for r in steps)
     assert [r for r in rows if "validation_loss" in r][0]["step"] == 2
+
+
+def test_weighted_blend_of_two_files(tmp_path, capsys):
+    from kareus_b200.data import BlendedDataset, build_blend_index
+    ds, pos = build_blend_index([1.0, 3.0], 400)
+    counts = np.bincount(ds)
+    assert counts.tolist() == [100, 300]
+    # every prefix of the blend keeps each dataset within one sample of its share
+    run = np.cumsum(ds == 0)
+    assert np.all(np.abs(run - 0.25 * np.arange(1, 401)) <= 1.0)
+    assert pos[ds == 0].tolist() == list(range(100)) and pos[ds == 1].tolist() == list(range(300))
+    a, b = build_blend_index([1.0, 3.0], 400, native=False)
+    np.testing.assert_array_equal(a, ds)
+    np.testing.assert_array_equal(b, pos)
+
+    class Const(torch.utils.data.Dataset):
+        def __init__(self, v, n):
+            self.v, self.n = v, n
+
+        def __len__(self):
+            return self.n
+
+        def __getitem__(self, i):
+            assert 0 <= i < self.n
+            return (self.v, i)
+
+    blend = BlendedDataset([1.0, 3.0], lambda d, n: Const(d, n), 40)
+    got = [blend[i] for i in range(40)]
+    assert sum(1 for v, _ in got if v == 0) == 10 and got[0][1] == 0
+    # through the driver: two files, 1:3
+    from kareus_b200.cli import run_train
+    (tmp_path / "a").mkdir(); (tmp_path / "b").mkdir()
+    pa, _ = _corpus(tmp_path / "a", n_docs=200, vocab=100, seed=1)
+    pb, _ = _corpus(tmp_path / "b", n_docs=200, vocab=100, seed=2)
+    rc = run_train.main(["--model", "tiny", "--mbs", "2", "--gbs", "4", "--seq", "32", "--method", "megatron", "--steps",
+                         "2", "--data-path", "1", pa, "3", pb, "--data-split", "9,1,0", "--eval-interval", "2", "--out",
+                         str(tmp_path / "runs"), "--keep-process-group"])
+    out = capsys.readouterr().out
+    assert rc == 0 and out.count("data: ") == 2 and "validation loss" in out

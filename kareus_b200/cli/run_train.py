@@ -145,43 +145,24 @@ def main(argv=None) -> int:
             print(f"resumed from {a.load} at step {first}", flush=True)
     batches = None
     if a.data_path:
-        from ..data import (BlendedDataset, GPTDataset, GPTDatasetConfig, IndexedDataset, PretrainingBatches,
-                            split_documents)
-        if len(a.data_path) == 1:
-            weights, prefixes = [1.0], list(a.data_path)
-        elif len(a.data_path) % 2 == 0:
-            weights = [float(w) for w in a.data_path[0::2]]
-            prefixes = list(a.data_path[1::2])
-        else:
-            raise SystemExit("--data-path takes one prefix or pairs `weight prefix`")
-        files = [IndexedDataset(p) for p in prefixes]
-        split_w = [float(w) for w in a.data_split.split(",")]
-
-        def make_split(part: int, num_samples: int, shuffle: bool = True):
-            """Blend of the given share (0 train, 1 validation) of every file's documents."""
-            def one(d: int, n: int):
-                docs = split_documents(files[d].num_documents, split_w)[part]
-                return GPTDataset(files[d], GPTDatasetConfig(seq_len=a.seq, num_samples=n, seed=a.data_seed + d,
-                                                             documents=docs, eod_token=a.eod_token,
-                                                             vocab_size=cfg.vocab_size, shuffle_samples=shuffle))
-            if len(files) == 1:
-                return one(0, num_samples)
-            return BlendedDataset(weights, one, num_samples)
-
-        tokens = files[0]
-        ds = make_split(0, a.steps * a.gbs)
+        from ..data import PretrainingBatches
+        from ..data.factory import TRAIN, VALIDATION, TokenData
+        try:
+            data = TokenData(a.data_path, a.data_split, a.seq, a.data_seed, a.eod_token, cfg.vocab_size)
+        except ValueError as e:
+            raise SystemExit(str(e))
+        ds = data.dataset(TRAIN, a.steps * a.gbs)
         # the run resumes at the sample where the checkpointed step count left off
         batches = PretrainingBatches(ds, a.mbs, M, dp_rank=mesh.dp_rank, dp_size=dp, consumed_samples=first * a.gbs,
                                      cp=a.cp, cp_rank=mesh.cp_rank)
         if rank == 0:
-            for p, f_ in zip(prefixes, files):
-                print(f"data: {p}: {f_.num_documents} documents, {f_.num_tokens} tokens", flush=True)
+            for line in data.describe():
+                print("data: " + line, flush=True)
     val_ds = None
     if a.data_path and a.eval_interval > 0:
-        if all(split_documents(f_.num_documents, split_w)[1][1] > split_documents(f_.num_documents, split_w)[1][0]
-               for f_ in files):
+        if data.has_share(VALIDATION):
             # the same held-out batches at every evaluation, in file order
-            val_ds = make_split(1, a.eval_iters * a.gbs, shuffle=False)
+            val_ds = data.dataset(VALIDATION, a.eval_iters * a.gbs, shuffle=False)
         elif rank == 0:
             print("the validation share of --data-split is empty: evaluating on synthetic tokens", flush=True)
 

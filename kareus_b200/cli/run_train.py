@@ -46,6 +46,8 @@ def main(argv=None) -> int:
                          "(frontier runs: <method>/frontier/pipeline_NNNNN)")
     ap.add_argument("--enable-power-monitor", action="store_true")
     ap.add_argument("--enable-timers", action="store_true")
+    ap.add_argument("--nano", type=int, default=None,
+                    help="nanobatches per microbatch (default: 1 for megatron / perseus, 2 for the other methods)")
     ap.add_argument("--recompute-layers", type=int, default=4)
     ap.add_argument("--no-recompute", action="store_true",
                     help="keep all activations (the reference's activations_checkpoint_granularity: null); overlap plans "
@@ -86,7 +88,9 @@ def main(argv=None) -> int:
     if cuda:
         torch.cuda.set_device(device)
     dp = world // (a.tp * a.cp * a.pp)
-    nano = 1 if a.method in ("megatron", "perseus") else 2
+    nano = a.nano if a.nano else (1 if a.method in ("megatron", "perseus") else 2)
+    if a.mbs % nano and a.seq % nano:
+        raise SystemExit(f"{nano} nanobatches divide neither the micro batch ({a.mbs}) nor the sequence ({a.seq})")
     tp_comm = a.tp_comm if a.tp > 1 else "allreduce"
     par = ParallelConfig(tp=a.tp, cp=a.cp, pp=a.pp, dp=dp, num_nanobatches=nano, tp_comm=tp_comm,
                          comm_backend=a.comm_backend if cuda else "nccl", recompute=not a.no_recompute)

@@ -230,3 +230,22 @@ def test_plan_server_process_serves_a_training_run(tmp_path, capsys):
     finally:
         proc.terminate()
         proc.wait(timeout=10)
+
+
+def test_nanobatch_count_of_a_run(tmp_path, capsys):
+    """`--nano 4`: four nanobatches along the batch, or along the sequence when the micro batch is 1; same first
+    loss as the two-nanobatch run of the same batch (the split changes the schedule, not the math)."""
+    from kareus_b200.cli import run_train
+    losses = {}
+    for tag, extra in {"n2": ["--mbs", "4", "--gbs", "8"], "n4": ["--mbs", "4", "--gbs", "8", "--nano", "4"],
+                       "seq4": ["--mbs", "1", "--gbs", "2", "--nano", "4"]}.items():
+        rc = run_train.main(["--method", "nanobatch", "--model", "tiny", "--seq", "32", "--steps", "1", "--out",
+                             str(tmp_path / tag), "--keep-process-group"] + extra)
+        assert rc == 0
+        losses[tag] = float(capsys.readouterr().out.split("step 0 loss")[1].split()[0])
+    assert abs(losses["n2"] - losses["n4"]) < 1e-3
+    assert 6.5 < losses["seq4"] < 7.5
+    import pytest
+    with pytest.raises(SystemExit):
+        run_train.main(["--method", "nanobatch", "--model", "tiny", "--mbs", "3", "--gbs", "3", "--seq", "33", "--nano", "2",
+                        "--steps", "1", "--out", str(tmp_path / "bad"), "--keep-process-group"])

@@ -36,6 +36,8 @@ def main(argv=None) -> int:
     ap.add_argument("--frontier", action="store_true", default=os.environ.get("FRONTIER", "false").lower() == "true")
     ap.add_argument("--skip-planning", action="store_true")
     ap.add_argument("--no-recompute", action="store_true", help="plan and train without activation recompute")
+    ap.add_argument("--nano", type=int, default=2,
+                    help="nanobatches per microbatch: composes the measurements taken with this split and trains with it")
     ap.add_argument("--max-iterations", type=int, default=None)
     ap.add_argument("--clock-mode", default="advisory", choices=["off", "advisory", "locked"])
     ap.add_argument("--tp-comm", default="allreduce")
@@ -56,7 +58,7 @@ def main(argv=None) -> int:
     num_mbs = a.gbs // (a.mbs * max(1, world // (a.tp * a.cp * a.pp)))
     if rank == 0 and not a.skip_planning:
         csv_path = generate_profile_csv(a.model, a.tp, a.cp, a.pp, a.mbs, a.seq, a.bayesian_dir, None, str(base),
-                                        a.gpu_type, not a.no_recompute, True)
+                                        a.gpu_type, not a.no_recompute, True, a.nano)
         summary = run_optimization(csv_path, plans, a.pp, num_mbs, a.gpu_type, max_iterations=a.max_iterations,
                                    use_activation_checkpointing=not a.no_recompute)
         print(f"planned {len(summary)} frontier points: T {summary[0]['time_s']:.3f}s → {summary[-1]['time_s']:.3f}s")
@@ -83,7 +85,7 @@ def main(argv=None) -> int:
                  "--mbs", str(a.mbs), "--gbs", str(a.gbs), "--seq", str(a.seq), "--steps", str(a.steps),
                  "--freqs", str(src), "--scheds", str(src.parent / name.replace("freqs", "scheds")),
                  "--clock-mode", a.clock_mode, "--tp-comm", a.tp_comm, "--comm-backend", a.comm_backend,
-                 "--out", str(Path(a.workdir)), "--keep-process-group"] + (["--run-dir", run_dir] if run_dir else []) + (["--no-recompute"] if a.no_recompute else [])
+                 "--out", str(Path(a.workdir)), "--keep-process-group", "--nano", str(a.nano)] + (["--run-dir", run_dir] if run_dir else []) + (["--no-recompute"] if a.no_recompute else [])
         run_train.main(argv2)
     if world > 1:
         dist.barrier()

@@ -36,8 +36,10 @@ def run_dir(base, model: str, cp: int, tp: int, bs: int, seq: int) -> Path:
     return Path(base) / "logs" / model / f"cp{cp}-tp{tp}-bs{bs}-seq{seq}"
 
 
-def read_bo_jsonl(path) -> Dict[int, List[Point]]:
-    """``{frequency: [((overlap_start, overlap_end, sm, block), (time_s, energy_j)), ...]}``"""
+def read_bo_jsonl(path, nano: Optional[int] = None) -> Dict[int, List[Point]]:
+    """``{frequency: [((overlap_start, overlap_end, sm, block), (time_s, energy_j)), ...]}``.  ``nano``: keep the
+    measurements taken with that many nanobatches (a search over the split count writes them into one file; a
+    row without the field was measured with two)."""
     out: Dict[int, List[Point]] = {}
     with open(path) as f:
         for line in f:
@@ -46,6 +48,8 @@ def read_bo_jsonl(path) -> Dict[int, List[Point]]:
                 continue
             try:
                 row = json.loads(line)
+                if nano is not None and int(row.get("nano", 2)) != nano:
+                    continue
                 key = (row["overlap_start"], row["overlap_end"], int(row["sm"]), int(row["block"]))
                 out.setdefault(int(row["freq"]), []).append((key, (float(row["time_s"]), float(row["energy_j"]))))
             except (ValueError, KeyError, TypeError):
@@ -245,11 +249,11 @@ def generate_profile_csv(model_name: str, tp: int, cp: int, pp: int, batch_size:
     pre_base = run_dir(prepost_profile_dir or bayesian_profile_dir, model_name, cp, tp, batch_size, seq_len)
     context_parallel = cp > 1
     keys = (FWD_KEYS_CP + BWD_KEYS_CP) if context_parallel else (FWD_KEYS_TP + BWD_KEYS_TP)
-    maps = {k: read_bo_jsonl(base / k / "eval_results.jsonl") for k in keys}
+    maps = {k: read_bo_jsonl(base / k / "eval_results.jsonl", nanobatches) for k in keys}
     if not context_parallel:
         for child in FUSED_CHILD.values():          # logs of the fused sequence-parallel path, if profiled
             if (base / child / "eval_results.jsonl").exists():
-                maps[child] = read_bo_jsonl(base / child / "eval_results.jsonl")
+                maps[child] = read_bo_jsonl(base / child / "eval_results.jsonl", nanobatches)
         maps = merge_fused_partitions(maps)
     freqs = set.intersection(*(set(m) for m in maps.values()))
     prepost = read_prepost(pre_base, sorted(freqs))

@@ -317,3 +317,20 @@ def test_frontier_runner_trains_under_every_sampled_plan(tmp_path):
     runs = sorted((tmp_path / "exp" / "tiny" / "cp1_tp1_mbs2_seq32" / "perseus" / "frontier").iterdir())
     assert [r.name for r in runs] == ["pipeline_00001", "pipeline_00002"]          # positions 0 dropped, last kept
     assert compare.main(["--root", str(tmp_path / "exp"), "--frontier", "--skip", "1", "--take", "2"]) == 0
+
+
+def test_composer_reads_one_nanobatch_count_at_a_time(tmp_path):
+    """A search over the nanobatch split writes all counts into one log; composition takes one of them."""
+    from kareus_b200.compose.composer import read_bo_jsonl
+    f = tmp_path / "eval_results.jsonl"
+    rows = [{"freq": 1500, "overlap_start": "norm_0", "overlap_end": "none", "sm": 6, "block": 1024, "time_s": 1e-3,
+             "energy_j": 1.0},
+            {"freq": 1500, "overlap_start": "norm_0", "overlap_end": "none", "sm": 6, "block": 1024, "time_s": 2e-3,
+             "energy_j": 2.0, "nano": 1},
+            {"freq": 1500, "overlap_start": "norm_0", "overlap_end": "none", "sm": 9, "block": 1024, "time_s": 5e-4,
+             "energy_j": 0.5, "nano": 4}]
+    f.write_text("\n".join(json.dumps(r) for r in rows) + "\n")
+    assert len(read_bo_jsonl(f)[1500]) == 3
+    assert [p[1][0] for p in read_bo_jsonl(f, 2)[1500]] == [1e-3]
+    assert [p[0][2] for p in read_bo_jsonl(f, 4)[1500]] == [9]
+    assert read_bo_jsonl(f, 8) == {}

@@ -55,10 +55,18 @@ def main(argv=None) -> int:
         t = torch.zeros(1, device="cuda")
         dist.all_reduce(t)
         torch.cuda.synchronize()
-    watts = probe_p2p_power(a.duration)
+    monitor = None
+    if not torch.cuda.is_available():
+        # no GPU: the run only shows that the probe works; its watts come from the simulated NVML
+        from .nvml import FakeNVML
+        monitor = EnergyMonitor([0], nvml=FakeNVML(1))
+    watts = probe_p2p_power(a.duration, monitor=monitor)
     if rank == 0:
-        print(json.dumps({"p2p_wait_power_w": watts, "duration_s": a.duration,
-                          "gpu": torch.cuda.get_device_name(local) if torch.cuda.is_available() else "cpu"}), flush=True)
+        line = {"p2p_wait_power_w": watts, "duration_s": a.duration,
+                "gpu": torch.cuda.get_device_name(local) if torch.cuda.is_available() else "cpu"}
+        if monitor is not None:
+            line["simulated"] = True
+        print(json.dumps(line), flush=True)
     dist.barrier()
     dist.destroy_process_group()
     return 0

@@ -48,7 +48,8 @@ def main(argv=None) -> int:
         p = get_p2p_power(a.gpu_type)
         ours = frontier_from_plans(a.frontier_ours, a.num_stages, p)
         base = frontier_from_plans(a.frontier_base, a.num_stages, p)
-        print(json.dumps({**compare_frontiers(ours, base), "dominates": dominates(ours, base)}))
+        res = {k: (None if isinstance(v, float) and v != v else v) for k, v in compare_frontiers(ours, base).items()}
+        print(json.dumps({**res, "dominates": dominates(ours, base)}))      # frontiers that do not overlap: null
     return 0
 
 

@@ -164,7 +164,7 @@ class AttentionOp(GraphOperator):
             self.rs_kv = comm.make(ReduceScatterKV, "cp", f"{name}.rs_kv")
         # sequence-split nanobatches: nanobatch i holds rows [i·s/N, (i+1)·s/N) of every sequence and
         # attends to the keys of nanobatches 0..i, which they leave in this per-layer bank
-        self.seq_nano = 0
+        self._seq_nano = 0
         self._kv_bank = {}
         self._dkv_bank = {}
         self.ring = None
@@ -172,6 +172,18 @@ class AttentionOp(GraphOperator):
             from ..parallel.ring_attention import RingAttention
             self.ring = RingAttention(comm._args("cp")[0], self.cp, self.cp_rank, heap=getattr(comm, "heap_cp", None),
                                       name=f"{name}.ring")
+
+    @property
+    def seq_nano(self) -> int:
+        return self._seq_nano
+
+    @seq_nano.setter
+    def seq_nano(self, n: int) -> None:
+        self._seq_nano = int(n)
+        if self.cp > 1 and self.cp_comm != "ring":
+            # each nanobatch then gathers / reduces one half of the sequence (one chunk per rank)
+            for op in (self.ag_kv, self.rs_kv):
+                op.half_mode = self._seq_nano > 1
 
     # graph --------------------------------------------------------------------
     def forward_specs(self):
@@ -186,6 +198,11 @@ class AttentionOp(GraphOperator):
         compute = ComputeSpec(self, ("grad_main",), ("grad_main", "grad_key", "grad_value"), backward=True)
         if self.cp == 1 or self.cp_comm == "ring":
             return [compute]
+        if self.seq_nano > 1:
+            # sequence-split nanobatches keep the gathered K/V of their half: nothing to gather again
+            return [compute,
+                    CommSpec(self.rs_kv, CommKind.REDUCE_SCATTER_KV, ("grad_key", "grad_value"),
+                             ("grad_key", "grad_value"), "bwd_a_rs", backward=True, segment="a", short="rs")]
         # K/V are gathered again for backward by a schedulable collective of its own; it has no
         # graph input (it re-reads the local shards kept by the forward), so it is modelled as a
         # pass-through on grad_main that stashes the gathered tensors for the compute node.
@@ -228,9 +245,19 @@ class AttentionOp(GraphOperator):
             ctx.save_for_backward(q, k_loc, v_loc, out, lses[0], lses[1])
         return (out.reshape(s, b, -1),)
 
+    def _seq_split_window(self, i: int, chunk_rows: int):
+        """(absolute position of the nanobatch's first query, number of visible keys)."""
+        if self.cp == 1:
+            return i * chunk_rows, None
+        # dual-chunk ownership: nanobatch 0 is this rank's early chunk r, nanobatch 1 its late chunk 2cp-1-r;
+        # the keys at hand are the gathered halves 0..i of the sequence
+        cid = dual_chunk_ids(self.cp, self.cp_rank)[i]
+        return cid * chunk_rows, (cid + 1) * chunk_rows
+
     def _forward_seq_split(self, ctx, q, k, v):
-        if self.cp > 1:
-            raise NotImplementedError("sequence-split nanobatches with context parallelism")
+        if self.cp > 1 and (self.seq_nano != 2 or self.cp_comm != "all_gather"):
+            raise NotImplementedError("sequence-split nanobatches with context parallelism: two nanobatches and "
+                                      "cp_comm='all_gather' only")
         i, s, b = ctx.nb_index, q.shape[0], q.shape[1]
         self._kv_bank[i] = (k, v)
         if i > 0:
@@ -240,7 +267,11 @@ class AttentionOp(GraphOperator):
             k_all, v_all = k, v
         if i == self.seq_nano - 1:
             self._kv_bank.clear()
-        out, lse = K.attention_fwd(q, k_all, v_all, self.scale, causal=True, q_offset=i * s)
+        q_off, kv_len = self._seq_split_window(i, s)
+        if kv_len is None:
+            out, lse = K.attention_fwd(q, k_all, v_all, self.scale, causal=True, q_offset=q_off)
+        else:
+            out, lse = K.attention_fwd(q, k_all, v_all, self.scale, causal=True, q_offset=q_off, kv_len=kv_len)
         if ctx.requires_grad:
             ctx.save_for_backward(q, k_all, v_all, out, lse)
         return (out.reshape(s, b, -1),)
@@ -249,13 +280,19 @@ class AttentionOp(GraphOperator):
         q, k_all, v_all, out, lse = ctx.saved_tensors
         i, s, b = ctx.nb_index, q.shape[0], q.shape[1]
         do = dout.reshape(s, b, q_heads(q), self.d)
-        dq, dk_all, dv_all = K.attention_bwd(do, q, k_all, v_all, out, lse, self.scale, causal=True, q_offset=i * s)
-        dk, dv = dk_all[i * s:(i + 1) * s], dv_all[i * s:(i + 1) * s]
+        q_off, kv_len = self._seq_split_window(i, s)
+        if kv_len is None:
+            dq, dk_all, dv_all = K.attention_bwd(do, q, k_all, v_all, out, lse, self.scale, causal=True, q_offset=q_off)
+        else:
+            dq, dk_all, dv_all = K.attention_bwd(do, q, k_all, v_all, out, lse, self.scale, causal=True,
+                                                 q_offset=q_off, kv_len=kv_len)
+        w = s * self.cp                               # keys per nanobatch: its (gathered) part of the sequence
+        dk, dv = dk_all[i * w:(i + 1) * w], dv_all[i * w:(i + 1) * w]
         late = self._dkv_bank.pop(i, None)            # contributions of the nanobatches after this one
         if late is not None:
             dk, dv = dk + late[0], dv + late[1]
         for j in range(i):
-            part = (dk_all[j * s:(j + 1) * s], dv_all[j * s:(j + 1) * s])
+            part = (dk_all[j * w:(j + 1) * w], dv_all[j * w:(j + 1) * w])
             old = self._dkv_bank.get(j)
             self._dkv_bank[j] = part if old is None else (old[0] + part[0], old[1] + part[1])
         return dq, dk, dv

@@ -149,10 +149,25 @@ def to_rank_order(seq: torch.Tensor, cp: int) -> torch.Tensor:
     return torch.cat(out, dim=0)
 
 
+def half_to_sequence_order(gathered: torch.Tensor, cp: int, half: int) -> torch.Tensor:
+    """One chunk per rank (sequence-split nanobatch ``half`` of a dual-chunk layout): rank j contributed global
+    chunk j (half 0: already in sequence order) or 2cp-1-j (half 1: reverse the ranks).  Its own inverse."""
+    if half == 0:
+        return gathered
+    c = gathered.shape[0] // cp
+    chunks = gathered.reshape((cp, c) + tuple(gathered.shape[1:]))
+    return chunks.flip(0).reshape(gathered.shape)
+
+
 class AllGatherKV(CollectiveBase):
-    """CP all-gather of K and V into full-length, sequence-ordered tensors."""
+    """CP all-gather of K and V into full-length, sequence-ordered tensors.
+
+    ``half_mode`` (sequence-split nanobatches, two per microbatch): nanobatch ``nb`` carries one of this
+    rank's two chunks, so the gathered tensor is one half of the sequence: chunks 0..cp-1 for nanobatch 0,
+    cp..2cp-1 for nanobatch 1."""
 
     group_name = "cp"
+    half_mode = False
 
     def run(self, tensors, sm_num=None, block_size=None, backward=False, nb=0, ctx=None):
         k, v = tensors
@@ -168,15 +183,18 @@ class AllGatherKV(CollectiveBase):
             else:
                 g = torch.empty((t.shape[0] * self.world,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
                 dist.all_gather_into_tensor(g, t, group=self.group)
-            outs.append(to_sequence_order(g, self.world))
+            outs.append(half_to_sequence_order(g, self.world, nb) if self.half_mode
+                        else to_sequence_order(g, self.world))
         return tuple(outs)
 
 
 class ReduceScatterKV(CollectiveBase):
-    """CP reduce-scatter of full-length, sequence-ordered dK and dV."""
+    """CP reduce-scatter of full-length, sequence-ordered dK and dV (``half_mode``: of one half of the
+    sequence, see :class:`AllGatherKV`)."""
 
     group_name = "cp"
     staging_kind = "rs"
+    half_mode = False
 
     def reduce_rows(self, x, nb=0, sm_num=16, block_size=1024):
         """Plain dim-0 reduce-scatter of a tensor that is already in rank order (the chunked attention
@@ -203,7 +221,8 @@ class ReduceScatterKV(CollectiveBase):
             return (dk, dv)
         outs = []
         for t in (dk, dv):
-            t = to_rank_order(t, self.world).contiguous()
+            t = (half_to_sequence_order(t, self.world, nb) if self.half_mode
+                 else to_rank_order(t, self.world)).contiguous()
             if self._use_kernel(t, sm_num):
                 o = self.heap.reduce_scatter(t, nb=nb, sm_num=sm_num, block_size=block_size,
                                              tag=self.tag + ("_k" if t is dk else "_v"))

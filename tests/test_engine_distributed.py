@@ -6,7 +6,7 @@ import torch.distributed as dist
 from dist_utils import run_distributed
 
 
-def _worker(rank, world, tp, cp, tp_comm, n, recompute, with_plan, cp_comm="all_gather"):
+def _worker(rank, world, tp, cp, tp_comm, n, recompute, with_plan, cp_comm="all_gather", seq_split=False):
     from kareus_b200.config import ParallelConfig, get_model_config
     from kareus_b200.models.llama import GPTModel
     from kareus_b200.models.oracle import OracleLlama, load_from_shards, shard_of_oracle_grad
@@ -15,9 +15,11 @@ def _worker(rank, world, tp, cp, tp_comm, n, recompute, with_plan, cp_comm="all_
     from kareus_b200.plan import PipelineCommScheduler, uniform_schedule, CommConfig
 
     cfg = get_model_config("tiny")
-    par = ParallelConfig(tp=tp, cp=cp, num_nanobatches=n, tp_comm=tp_comm, recompute=recompute, cp_comm=cp_comm)
+    par = ParallelConfig(tp=tp, cp=cp, num_nanobatches=n, tp_comm=tp_comm, recompute=recompute, cp_comm=cp_comm,
+                         nano_split_dim="seq" if seq_split else "auto")
     mesh = Mesh(tp=tp, cp=cp)
     model = GPTModel(cfg, par, mesh=mesh, dtype="fp64", seed=0)
+    assert model.seq_split == seq_split
     if with_plan:
         plan = uniform_schedule(1, ["forward", "backward"], CommConfig(("linear_0", "none"), (4, 256)),
                                 context_parallel=False)
@@ -147,3 +149,12 @@ def _cp_keys_worker(rank, world):
 
 def test_cp_plan_keys_match_reference_vocabulary():
     run_distributed(_cp_keys_worker, 4)
+
+
+@pytest.mark.parametrize("tp,recompute", [(1, True), (1, False), (2, True)])
+def test_sequence_split_nanobatches_with_context_parallelism(tp, recompute):
+    """Two nanobatches along the sequence on top of dual-chunk context parallelism (micro batches that cannot be
+    split along the batch, e.g. one 16k sequence): nanobatch 0 is every rank's early chunk and gathers the first
+    half of the keys, nanobatch 1 the late chunk and sees both halves; its backward hands the first half's dK/dV
+    to nanobatch 0 before that one's reduce-scatter.  Loss and every gradient equal the unpartitioned oracle."""
+    run_distributed(_worker, tp * 2, tp, 2, "allreduce", 2, recompute, False, "all_gather", True)
